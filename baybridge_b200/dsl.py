@@ -1,0 +1,470 @@
+"""The DSL entry points a kernel body calls.
+
+This is the slice of upstream ``frontend.py`` / ``math.py`` that the b200 hot
+path exercises: ``kernel``/``jit`` decorators and launch objects
+(``frontend.py:756-864``), topology builtins (``:2038-2117``), scalar
+``load``/``store`` with optional predicates (``:2931-3019``), whole-tensor
+``copy`` (``:3357-3415``), ``where`` (``:2538-2600``), the ``math`` namespace
+(``math.py:13-76``), and the explicit ops ``gemm``/``mma`` (``frontend.py:3684-3740,
+4052-4091``), ``rmsnorm`` (``:3828-3874``) and ``attention`` (``:3877-3968``).
+
+Upstream entry points are dual-mode (emit IR while tracing, otherwise execute
+on the CPU).  Here they are trace-only; calling one with host tensors outside
+``compile`` raises, because results are only ever produced by the b200 device
+kernels.  The exception is *launching*: ``kernel(args).launch(grid=..,
+block=..)`` and calling a ``@jit`` wrapper outside a trace compile for the
+``b200`` backend (memoised) and run on the device.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Any, Callable
+
+from .errors import BackendNotImplementedError, CompilationError
+from .host_values import RuntimeScalar, RuntimeTensor, normalize_runtime_argument
+from .portable_ir import AddressSpace, LaunchConfig, ScalarSpec, TensorSpec
+from .trace import ScalarValue, TensorValue, active_builder, broadcast_shapes, coerce_scalar, require_builder
+
+
+# ---------------------------------------------------------------------------------------------
+# kernel definitions and launches
+# ---------------------------------------------------------------------------------------------
+@dataclass(frozen=True)
+class KernelDefinition:
+    fn: Callable[..., Any]
+    kind: str  # "kernel" (device body) | "jit" (host wrapper)
+    launch: LaunchConfig
+
+    @property
+    def __name__(self) -> str:  # type: ignore[override]
+        return self.fn.__name__
+
+    def __call__(self, *args: Any, **kwargs: Any) -> Any:
+        args = tuple(normalize_runtime_argument(arg) for arg in args)
+        kwargs = {name: normalize_runtime_argument(value) for name, value in kwargs.items()}
+        if self.kind == "kernel":
+            return KernelLaunch(self, args, kwargs)
+        if active_builder() is not None:
+            return self.fn(*args, **kwargs)
+        # a @jit wrapper called eagerly: compile for the device and run
+        from .driver import run_on_device
+
+        return run_on_device(self, args, kwargs)
+
+    def set_name_prefix(self, prefix: str) -> None:
+        del prefix
+
+
+class TraceKernelLaunch(CompilationError):
+    """Raised by ``.launch()`` under tracing so ``compile`` can re-trace the launched kernel."""
+
+    def __init__(self, definition: KernelDefinition, args: tuple[Any, ...], kwargs: dict[str, Any], launch: LaunchConfig):
+        super().__init__("kernel launch tracing is being handled by baybridge compile")
+        self.definition, self.args, self.kwargs, self.launch = definition, args, kwargs, launch
+
+
+@dataclass(frozen=True)
+class KernelLaunch:
+    definition: KernelDefinition
+    args: tuple[Any, ...]
+    kwargs: dict[str, Any]
+
+    def launch(self, *, grid, block, cluster=(1, 1, 1), shared_mem_bytes: int = 0, cooperative: bool = False,
+               stream: Any | None = None) -> None:
+        config = LaunchConfig(tuple(grid), tuple(block), tuple(cluster), shared_mem_bytes, cooperative)
+        if active_builder() is not None:
+            raise TraceKernelLaunch(self.definition, self.args, self.kwargs, config)
+        from .driver import run_on_device
+
+        run_on_device(KernelDefinition(self.definition.fn, "kernel", config), self.args, self.kwargs, stream=stream)
+
+
+def _decorator(kind: str):
+    def decorate(fn: Callable[..., Any] | None = None, *, launch: LaunchConfig | None = None):
+        chosen = launch or LaunchConfig()
+        if fn is None:
+            return lambda inner: KernelDefinition(fn=inner, kind=kind, launch=chosen)
+        return KernelDefinition(fn=fn, kind=kind, launch=chosen)
+
+    decorate.__name__ = kind
+    return decorate
+
+
+kernel = _decorator("kernel")
+jit = _decorator("jit")
+
+
+# ---------------------------------------------------------------------------------------------
+# topology builtins
+# ---------------------------------------------------------------------------------------------
+def _topology(op: str):
+    def builtin(axis: str = "x") -> ScalarValue:
+        if axis not in ("x", "y", "z"):
+            raise ValueError("axis must be one of: x, y, z")
+        return require_builder().emit_scalar(op, spec=ScalarSpec("index"), attrs={"axis": axis}, name_hint=f"{op}_{axis}")
+
+    builtin.__name__ = op
+    return builtin
+
+
+program_id = _topology("program_id")
+block_idx = _topology("block_idx")
+thread_idx = _topology("thread_idx")
+block_dim = _topology("block_dim")
+grid_dim = _topology("grid_dim")
+
+
+def lane_id() -> ScalarValue:
+    return require_builder().emit_scalar("lane_id", spec=ScalarSpec("index"), name_hint="lane_id")
+
+
+class _ArchNamespace:
+    """``cute.arch.thread_idx()`` … return (x, y, z) triples; each component is its own IR op."""
+
+    @staticmethod
+    def _triple(builtin) -> tuple[ScalarValue, ScalarValue, ScalarValue]:
+        return builtin("x"), builtin("y"), builtin("z")
+
+    def thread_idx(self):
+        return self._triple(thread_idx)
+
+    def block_idx(self):
+        return self._triple(block_idx)
+
+    def block_dim(self):
+        return self._triple(block_dim)
+
+    def grid_dim(self):
+        return self._triple(grid_dim)
+
+    @staticmethod
+    def lane_id():
+        return lane_id()
+
+
+arch = _ArchNamespace()
+
+
+def dim(tensor: TensorValue | RuntimeTensor, axis: int) -> ScalarValue | int:
+    rank = tensor.ndim
+    if not 0 <= axis < rank:
+        raise ValueError(f"axis {axis} is out of range for tensor rank {rank}")
+    if isinstance(tensor, RuntimeTensor):
+        return tensor.shape[axis]
+    return require_builder().emit_scalar(
+        "tensor_dim",
+        tensor,
+        spec=ScalarSpec("index"),
+        attrs={"axis": axis, "value": tensor.spec.shape[axis]},
+        name_hint=f"{tensor.name}_dim_{axis}",
+    )
+
+
+# ---------------------------------------------------------------------------------------------
+# scalar element access
+# ---------------------------------------------------------------------------------------------
+def _index_operands(tensor: TensorValue, index: Any, what: str) -> tuple[ScalarValue, ...]:
+    if not isinstance(tensor, TensorValue):
+        raise BackendNotImplementedError(
+            f"{what} on a host tensor would execute on the host; baybridge_b200 has no CPU runtime"
+        )
+    builder = require_builder()
+    operands = []
+    for item in index if isinstance(index, tuple) else (index,):
+        if isinstance(item, ScalarValue):
+            operands.append(item)
+        elif isinstance(item, int) and not isinstance(item, bool):
+            operands.append(builder.constant(item))
+        else:
+            raise TypeError("indices must be ScalarValue, int, or tuples of those values")
+    if len(operands) != tensor.ndim:
+        raise ValueError(f"{what} expects {tensor.ndim} indices for tensor rank {tensor.ndim}")
+    return tuple(operands)
+
+
+def _checked_predicate(predicate: ScalarValue | None) -> ScalarValue | None:
+    if predicate is not None and predicate.spec.dtype != "i1":
+        raise ValueError("predicate values must have dtype i1")
+    return predicate
+
+
+def load(tensor: TensorValue, index: Any, *, predicate: ScalarValue | None = None,
+         else_value: ScalarValue | int | float | None = None) -> ScalarValue:
+    operands = _index_operands(tensor, index, "load")
+    guard = _checked_predicate(predicate)
+    builder = require_builder()
+    dtype = tensor.spec.dtype
+    if guard is None:
+        return builder.emit_scalar(
+            "load", tensor, *operands, spec=ScalarSpec(dtype), attrs={"rank": len(operands)}, name_hint=f"{tensor.name}_val"
+        )
+    fallback = else_value if else_value is not None else 0
+    if not isinstance(fallback, ScalarValue):
+        fallback = builder.constant(fallback, dtype=dtype)
+    if fallback.spec.dtype != dtype:
+        raise ValueError(f"else_value dtype mismatch: value has {fallback.spec.dtype}, tensor expects {dtype}")
+    return builder.emit_scalar(
+        "masked_load", tensor, *operands, guard, fallback,
+        spec=ScalarSpec(dtype), attrs={"rank": len(operands)}, name_hint=f"{tensor.name}_val",
+    )
+
+
+def store(value: ScalarValue, tensor: TensorValue, index: Any, *, predicate: ScalarValue | None = None) -> None:
+    operands = _index_operands(tensor, index, "store")
+    if not isinstance(value, ScalarValue):
+        raise TypeError("traced store values must be baybridge scalar expressions")
+    if value.spec.dtype != tensor.spec.dtype:
+        raise ValueError(f"store dtype mismatch: value has {value.spec.dtype}, tensor expects {tensor.spec.dtype}")
+    guard = _checked_predicate(predicate)
+    builder = require_builder()
+    if guard is None:
+        builder.emit_void("store", value, tensor, *operands, attrs={"rank": len(operands)})
+    else:
+        builder.emit_void("masked_store", value, tensor, *operands, guard, attrs={"rank": len(operands)})
+
+
+def copy(src: TensorValue, dst: TensorValue, *, vector_bytes: int | None = None) -> None:
+    """Whole-tensor copy op; ``vector_bytes`` is recorded as an attribute exactly as upstream does."""
+    if not (isinstance(src, TensorValue) and isinstance(dst, TensorValue)):
+        raise BackendNotImplementedError("copy on host tensors would execute on the host; baybridge_b200 has no CPU runtime")
+    require_builder().emit_void("copy", src, dst, attrs={"vector_bytes": vector_bytes})
+
+
+def make_tensor(name: str, shape: tuple[int, ...] | None = None, dtype: str | None = None, *,
+                layout=None, address_space: AddressSpace | str = AddressSpace.REGISTER) -> TensorValue:
+    if not isinstance(name, str):
+        raise TypeError("make_tensor expects a tensor name")
+    if shape is None or dtype is None:
+        raise TypeError("make_tensor(name, ...) requires shape=... and dtype=...")
+    builder = require_builder()
+    taken = {argument.name for argument in builder.arguments}
+    for operation in builder.operations:
+        taken.update(operation.outputs)
+    unique = f"{name}_{builder.next_temp()}" if name in taken else name
+    return builder.make_tensor(unique, TensorSpec(tuple(shape), dtype, layout, address_space))
+
+
+# ---------------------------------------------------------------------------------------------
+# select and math
+# ---------------------------------------------------------------------------------------------
+def where(predicate: Any, true_value: Any, false_value: Any, *, loc: Any = None, ip: Any = None) -> Any:
+    del loc, ip
+    builder = require_builder()
+    if isinstance(predicate, ScalarValue):
+        if predicate.spec.dtype != "i1":
+            raise ValueError("where requires an i1 predicate")
+        if isinstance(true_value, ScalarValue):
+            chosen = true_value
+        else:
+            hint = false_value.spec.dtype if isinstance(false_value, ScalarValue) else None
+            chosen = builder.constant(true_value, dtype=hint)
+        other = false_value if isinstance(false_value, ScalarValue) else builder.constant(false_value, dtype=chosen.spec.dtype)
+        if chosen.spec.dtype != other.spec.dtype:
+            raise ValueError("where requires the true and false branches to have the same dtype")
+        return builder.emit_scalar("select", predicate, chosen, other, spec=ScalarSpec(chosen.spec.dtype), name_hint="select")
+    if isinstance(predicate, TensorValue):
+        if predicate.spec.dtype != "i1":
+            raise ValueError("where requires an i1 predicate tensor")
+        required = next((v.spec.dtype for v in (true_value, false_value) if isinstance(v, (TensorValue, ScalarValue))), None)
+
+        def branch(value: Any) -> Any:
+            if isinstance(value, TensorValue):
+                value = value.broadcast_to(predicate.spec.shape)
+            elif not isinstance(value, ScalarValue):
+                value = builder.constant(value, dtype=required)
+            if required is not None and value.spec.dtype != required:
+                raise ValueError(f"where branch dtype must match {required}, got {value.spec.dtype}")
+            return value
+
+        chosen, other = branch(true_value), branch(false_value)
+        return builder.emit_tensor(
+            "select", predicate, chosen, other,
+            spec=TensorSpec(predicate.spec.shape, chosen.spec.dtype, address_space=AddressSpace.REGISTER),
+            name_hint="select",
+        )
+    raise BackendNotImplementedError("where on host values would execute on the host; baybridge_b200 has no CPU runtime")
+
+
+def _float_only(value: Any, op: str, what: str) -> None:
+    if not value.spec.dtype.startswith("f"):
+        raise TypeError(f"{op} requires a floating-point {what}")
+
+
+def _unary_math(op: str):
+    def apply(value: Any) -> Any:
+        if isinstance(value, ScalarValue):
+            _float_only(value, op, "scalar")
+            return require_builder().emit_scalar(op, value, spec=ScalarSpec(value.spec.dtype), name_hint=op)
+        if isinstance(value, TensorValue):
+            _float_only(value, op, "tensor")
+            return require_builder().emit_tensor(
+                op, value, spec=TensorSpec(value.spec.shape, value.spec.dtype, address_space=AddressSpace.REGISTER), name_hint=op
+            )
+        raise BackendNotImplementedError(f"{op} on host values would execute on the host; baybridge_b200 has no CPU runtime")
+
+    apply.__name__ = op[len("math_"):]
+    return apply
+
+
+def _tensor_pair(lhs: Any, rhs: Any, op: str) -> TensorValue:
+    builder = require_builder()
+    if isinstance(lhs, TensorValue) and isinstance(rhs, TensorValue):
+        if lhs.spec.dtype != rhs.spec.dtype:
+            raise TypeError(f"{op} requires matching tensor dtypes")
+        shape = broadcast_shapes(lhs.spec.shape, rhs.spec.shape)
+        operands = (lhs.broadcast_to(shape), rhs.broadcast_to(shape))
+        dtype = lhs.spec.dtype
+    else:
+        tensor = lhs if isinstance(lhs, TensorValue) else rhs
+        scalar = rhs if isinstance(lhs, TensorValue) else lhs
+        if not isinstance(scalar, ScalarValue):
+            scalar = builder.constant(scalar, dtype=tensor.spec.dtype)
+        if scalar.spec.dtype != tensor.spec.dtype:
+            raise TypeError(f"{op} requires matching tensor/scalar dtypes")
+        operands = (tensor, scalar) if isinstance(lhs, TensorValue) else (scalar, tensor)
+        shape, dtype = tensor.spec.shape, tensor.spec.dtype
+    return builder.emit_tensor(op, *operands, spec=TensorSpec(shape, dtype, address_space=AddressSpace.REGISTER), name_hint=op)
+
+
+def _extrema(scalar_op: str, tensor_op: str):
+    def apply(lhs: Any, rhs: Any) -> Any:
+        if isinstance(lhs, TensorValue) or isinstance(rhs, TensorValue):
+            tensor = lhs if isinstance(lhs, TensorValue) else rhs
+            if tensor.spec.dtype not in ("f32", "i32"):
+                raise TypeError(f"{tensor_op} requires tensor dtype f32 or i32")
+            return _tensor_pair(lhs, rhs, tensor_op)
+        if isinstance(lhs, ScalarValue) or isinstance(rhs, ScalarValue):
+            left = lhs if isinstance(lhs, ScalarValue) else coerce_scalar(lhs, rhs.spec.dtype)
+            right = rhs if isinstance(rhs, ScalarValue) else coerce_scalar(rhs, left.spec.dtype)
+            if left.spec.dtype not in ("f32", "i32"):
+                raise TypeError(f"{scalar_op} requires scalar dtype f32 or i32")
+            if left.spec.dtype != right.spec.dtype:
+                raise TypeError(f"{scalar_op} requires matching scalar dtypes")
+            return require_builder().emit_scalar(scalar_op, left, right, spec=ScalarSpec(left.spec.dtype), name_hint=scalar_op)
+        pick = max if scalar_op == "max" else min
+        unwrap = lambda v: v.value if isinstance(v, RuntimeScalar) else v  # noqa: E731
+        return pick(unwrap(lhs), unwrap(rhs))
+
+    apply.__name__ = "maximum" if scalar_op == "max" else "minimum"
+    return apply
+
+
+def _atan2(lhs: Any, rhs: Any) -> Any:
+    if isinstance(lhs, ScalarValue) and isinstance(rhs, ScalarValue):
+        _float_only(lhs, "math_atan2", "scalar")
+        _float_only(rhs, "math_atan2", "scalar")
+        if lhs.spec.dtype != rhs.spec.dtype:
+            raise TypeError("math_atan2 requires matching scalar dtypes")
+        return require_builder().emit_scalar("math_atan2", lhs, rhs, spec=ScalarSpec(lhs.spec.dtype), name_hint="math_atan2")
+    if isinstance(lhs, TensorValue) or isinstance(rhs, TensorValue):
+        for value in (lhs, rhs):
+            if isinstance(value, TensorValue):
+                _float_only(value, "math_atan2", "tensor")
+        return _tensor_pair(lhs, rhs, "math_atan2")
+    raise BackendNotImplementedError("atan2 on host values would execute on the host; baybridge_b200 has no CPU runtime")
+
+
+UNARY_MATH = ("round", "floor", "ceil", "trunc", "acos", "asin", "atan", "sqrt", "rsqrt", "exp", "sin", "cos",
+              "exp2", "log", "log2", "log10", "erf")
+
+
+class _MathNamespace:
+    atan2 = staticmethod(_atan2)
+    maximum = staticmethod(_extrema("max", "tensor_max"))
+    minimum = staticmethod(_extrema("min", "tensor_min"))
+
+
+for _name in UNARY_MATH:
+    setattr(_MathNamespace, _name, staticmethod(_unary_math(f"math_{_name}")))
+math = _MathNamespace()
+maximum, minimum, atan2 = math.maximum, math.minimum, math.atan2
+(round, floor, ceil, trunc, acos, asin, atan, sqrt, rsqrt, exp, sin, cos, exp2, log, log2, log10, erf) = (
+    getattr(math, _name) for _name in UNARY_MATH
+)
+
+
+# ---------------------------------------------------------------------------------------------
+# explicit ops: GEMM, RMSNorm, attention
+# ---------------------------------------------------------------------------------------------
+def _all_traced(values: tuple[Any, ...], what: str) -> None:
+    if all(isinstance(value, RuntimeTensor) for value in values):
+        raise BackendNotImplementedError(
+            f"baybridge.{what} on host tensors would execute on the host; baybridge_b200 has no CPU runtime — "
+            "compile the kernel with backend='b200'"
+        )
+    if not all(isinstance(value, TensorValue) for value in values):
+        raise TypeError(f"baybridge.{what} expects all arguments to be runtime tensors or all to be traced tensors")
+
+
+def mma(a: TensorValue, b: TensorValue, c: TensorValue | None = None, *, tile: tuple[int, ...] | None = None,
+        accumulate: bool = True, accumulator_dtype: str | None = None, transpose_a: bool = False,
+        transpose_b: bool = False) -> TensorValue:
+    if a.spec.dtype != b.spec.dtype and {a.spec.dtype, b.spec.dtype} != {"fp8", "bf8"}:
+        raise ValueError(f"mma currently requires matching operand dtypes, got {a.spec.dtype} and {b.spec.dtype}")
+    if c is None:
+        default = "f32" if a.spec.dtype in ("f16", "bf16", "f32", "fp8", "bf8") else a.spec.dtype
+        c = make_tensor("acc", shape=a.spec.shape, dtype=accumulator_dtype or default, address_space="register")
+    elif accumulator_dtype is not None and accumulator_dtype != c.spec.dtype:
+        raise ValueError(
+            f"mma accumulator_dtype={accumulator_dtype} does not match explicit accumulator tensor dtype {c.spec.dtype}"
+        )
+    require_builder().emit_void(
+        "mma", a, b, c,
+        attrs={"tile": list(tile) if tile else None, "accumulate": accumulate,
+               "transpose_a": transpose_a, "transpose_b": transpose_b},
+    )
+    return c
+
+
+def gemm(a: Any, b: Any, c: Any, *, transpose_a: bool = False, transpose_b: bool = False) -> Any:
+    """``C[m, n] = sum_k A[m, k] * B[k, n]`` with optional operand transposes; C is overwritten."""
+    _all_traced((a, b, c), "gemm")
+    if not (a.ndim == b.ndim == c.ndim == 2):
+        raise ValueError("traced baybridge.gemm currently requires rank-2 tensors")
+    k, m = a.spec.shape if transpose_a else a.spec.shape[::-1]
+    n, kb = b.spec.shape if transpose_b else b.spec.shape[::-1]
+    if kb != k or c.spec.shape != (m, n):
+        raise ValueError(f"gemm shape mismatch: {a.spec.shape} x {b.spec.shape} -> {c.spec.shape}")
+    return mma(a, b, c, tile=(m, n, k), accumulator_dtype=c.spec.dtype, transpose_a=transpose_a, transpose_b=transpose_b)
+
+
+def rmsnorm(x: Any, out: Any, gamma: Any, *, epsilon: float = 1e-5) -> Any:
+    """``out = x * rsqrt(mean(x**2 over the last axis) + epsilon) * gamma``."""
+    _all_traced((x, out, gamma), "rmsnorm")
+    if x.spec.shape != out.spec.shape:
+        raise ValueError("baybridge.rmsnorm requires x and out to have matching shapes")
+    if x.ndim < 1:
+        raise ValueError("baybridge.rmsnorm requires rank >= 1 tensors")
+    hidden = x.spec.shape[-1]
+    if gamma.spec.shape not in {(hidden,), x.spec.shape}:
+        raise ValueError(f"baybridge.rmsnorm expects gamma shape {(hidden,)} or {x.spec.shape}, got {gamma.spec.shape}")
+    if gamma.spec.dtype != x.spec.dtype or out.spec.dtype != x.spec.dtype:
+        raise ValueError("baybridge.rmsnorm requires matching tensor dtypes")
+    require_builder().emit_void("rmsnorm", x, out, gamma, attrs={"epsilon": float(epsilon)})
+    return out
+
+
+def attention(q: Any, k: Any, v: Any, out: Any, lse: Any, *, causal: bool = False) -> Any:
+    """Softmax attention on ``[batch, seq, heads, head_dim]`` tensors, scale ``1/sqrt(head_dim)``;
+    ``lse`` (``[batch, heads, 1, seq]`` or ``[batch, heads, seq]``) receives the natural-log row sums."""
+    _all_traced((q, k, v, out, lse), "attention")
+    if not (q.ndim == k.ndim == v.ndim == out.ndim == 4):
+        raise ValueError("baybridge.attention requires rank-4 q, k, v, and out tensors")
+    if q.spec.shape != out.spec.shape:
+        raise ValueError("baybridge.attention requires q and out to have matching shapes")
+    bsz, seqlen, heads, head_dim = q.spec.shape
+    kv_batch, kv_len, kv_heads, kv_dim = k.spec.shape
+    if v.spec.shape != k.spec.shape:
+        raise ValueError("baybridge.attention requires k and v to have matching shapes")
+    if (kv_batch, kv_len, kv_dim) != (bsz, seqlen, head_dim):
+        raise ValueError("baybridge.attention requires compatible q/k/v shapes")
+    if heads % kv_heads:
+        raise ValueError("baybridge.attention requires q heads to be divisible by kv heads")
+    if lse.spec.shape not in {(bsz, heads, 1, seqlen), (bsz, heads, seqlen)}:
+        raise ValueError(
+            f"baybridge.attention expects lse shape {(bsz, heads, 1, seqlen)} or {(bsz, heads, seqlen)}, got {lse.spec.shape}"
+        )
+    if any(value.spec.dtype != q.spec.dtype for value in (k, v, out)):
+        raise ValueError("baybridge.attention requires matching q/k/v/out dtypes")
+    require_builder().emit_void("attention", q, k, v, out, lse, attrs={"causal": bool(causal)})
+    return out

@@ -1,0 +1,320 @@
+#!/usr/bin/env python3
+"""Regenerate the golden fixtures in this directory from the UPSTREAM package.
+
+Usage (only where an upstream checkout exists; the fixtures it writes are
+committed so tests never need the checkout):
+
+    python tests/golden/make_golden.py /path/to/upstream/src
+
+What it writes
+--------------
+``ir_<case>.json``   ``PortableKernelIR.to_dict()`` as traced by upstream's
+                     ``compile(..., backend="portable")`` plus the cache key
+                     upstream computes for backend name ``b200`` and
+                     ``NvidiaTarget("sm_100a", "8.8")``.
+``vec_<case>.npz``   seeded inputs and the outputs produced by upstream's CPU
+                     reference runtime (sequential thread emulation /
+                     ``gemm`` / ``rmsnorm`` / ``attention`` loops), stored as
+                     float64 exactly as upstream computed them (the CPU
+                     runtime never rounds to the tensor dtype).
+
+Inputs are drawn from ``numpy.random.default_rng(seed)`` and, for 16-bit
+dtypes, rounded to representable values *before* either side sees them.
+"""
+from __future__ import annotations
+
+import hashlib
+import json
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+import numpy as np
+
+HERE = Path(__file__).resolve().parent
+sys.path.insert(0, str(HERE.parent))
+
+
+def bf16_round(x: np.ndarray) -> np.ndarray:
+    """Round-to-nearest-even onto the bf16 grid, returned as float32."""
+    bits = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32).astype(np.uint64)
+    bias = ((bits >> 16) & 1) + 0x7FFF
+    out = (((bits + bias) >> 16) << 16).astype(np.uint32)
+    return out.view(np.float32)
+
+
+def f16_round(x: np.ndarray) -> np.ndarray:
+    return np.asarray(x, dtype=np.float32).astype(np.float16).astype(np.float32)
+
+
+ROUNDERS = {"f32": lambda x: np.asarray(x, dtype=np.float32), "bf16": bf16_round, "f16": f16_round}
+
+
+def main() -> None:
+    upstream_src = sys.argv[1] if len(sys.argv) > 1 else "/root/reference/src"
+    sys.path.insert(0, upstream_src)
+    import baybridge as bb  # noqa: E402  (upstream)
+    from baybridge.compiler import _cache_key, _trace_cache_payload  # noqa: E402
+
+    from kernel_zoo import build_zoo
+
+    zoo = build_zoo(bb)
+    target = bb.NvidiaTarget(sm="sm_100a", ptx_version="8.8")
+    cache = Path(tempfile.mkdtemp(prefix="bb_golden_"))
+
+    def rt(array: np.ndarray, dtype: str):
+        return bb.tensor(np.asarray(array, dtype=np.float64).tolist(), dtype=dtype)
+
+    def out_array(t) -> np.ndarray:
+        return np.asarray(t.tolist(), dtype=np.float64)
+
+    def dump_ir(case: str, kernel, *sample_args) -> None:
+        artifact = bb.compile(kernel, *sample_args, backend="portable", cache_dir=cache, target=target)
+        payload = {
+            "case": case,
+            "ir": artifact.ir.to_dict(),
+            "cache_key_b200_sm100a": _cache_key(_trace_cache_payload(artifact.ir, target, "b200")),
+        }
+        (HERE / f"ir_{case}.json").write_text(json.dumps(payload, indent=1, sort_keys=True) + "\n")
+
+    def run_case(case: str, kernel, arrays: dict[str, tuple[np.ndarray, str]], outputs: list[str], extra=()) -> None:
+        """Trace + execute on the upstream CPU runtime; store inputs and outputs."""
+        tensors = {name: rt(value, dtype) for name, (value, dtype) in arrays.items()}
+        args = list(tensors.values()) + list(extra)
+        dump_ir(case, kernel, *args)
+        started = time.perf_counter()
+        artifact = bb.compile(kernel, *args, backend="portable", cache_dir=cache, target=target)
+        artifact(*args)
+        elapsed = time.perf_counter() - started
+        blob = {f"in_{name}": np.asarray(value) for name, (value, _) in arrays.items() if name not in outputs}
+        for name in outputs:
+            blob[f"out_{name}"] = out_array(tensors[name])
+        np.savez_compressed(HERE / f"vec_{case}.npz", **blob)
+        print(f"{case}: upstream CPU runtime {elapsed:.2f}s")
+
+    # ---------------- config 1: 256x256 f32 indexed add (full size) ----------------------------
+    rng = np.random.default_rng(1001)
+    a = rng.uniform(-1, 1, (256, 256)).astype(np.float32)
+    b = rng.uniform(-1, 1, (256, 256)).astype(np.float32)
+    kernel = zoo.make_indexed_add_2d(256, 256)
+    tensors = [rt(a, "f32"), rt(b, "f32"), bb.zeros((256, 256), dtype="f32")]
+    dump_ir("c1_indexed_add_256x256_f32", kernel, *tensors)
+    artifact = bb.compile(kernel, *tensors, backend="portable", cache_dir=cache, target=target)
+    started = time.perf_counter()
+    artifact(*tensors)
+    print(f"c1: upstream CPU runtime {time.perf_counter() - started:.2f}s")
+    c = out_array(tensors[2])
+    digest = hashlib.sha256(a.tobytes() + b.tobytes()).hexdigest()
+    # inputs are re-derived from the seed by the tests; the digest guards the RNG stream
+    np.savez_compressed(
+        HERE / "vec_c1_indexed_add_256x256_f32.npz",
+        out_g_c=c.astype(np.float32),
+        exact_in_f32=np.array(bool(np.all(c.astype(np.float32).astype(np.float64) == c))),
+        input_sha256=np.array(digest),
+    )
+
+    # ---------------- config 2 (reduced): fused a*b+a, bf16, both IR forms -----------------------
+    rng = np.random.default_rng(1002)
+    n = 4096
+    a = bf16_round(rng.standard_normal(n, dtype=np.float32))
+    b = bf16_round(rng.standard_normal(n, dtype=np.float32))
+    run_case(
+        "c2_fused_indexed_4096_bf16",
+        zoo.make_fused_mul_add_indexed(n),
+        {"a": (a, "bf16"), "b": (b, "bf16"), "c": (np.zeros(n), "bf16")},
+        ["c"],
+    )
+    run_case(
+        "c2_fused_ssa_4096_bf16",
+        zoo.fused_mul_add_ssa,
+        {"a": (a, "bf16"), "b": (b, "bf16"), "c": (np.zeros(n), "bf16")},
+        ["c"],
+    )
+    # full-size IR listings (TensorSpec-free: shapes come from zero-filled handles would be
+    # too large, so trace with lightweight shape carriers)
+
+    class ShapeOnly:
+        """DLPack-looking carrier: lets upstream infer (dtype, shape) without data."""
+
+        def __init__(self, shape, dtype):
+            self.shape = tuple(shape)
+            self.dtype = dtype
+
+        def __dlpack__(self, stream=None):
+            return "capsule"
+
+        def __dlpack_device__(self):
+            return (2, 0)
+
+        def data_ptr(self):
+            return 0
+
+    big = 2**28
+    dump_ir(
+        "c2_fused_indexed_2p28_bf16",
+        zoo.make_fused_mul_add_indexed(big),
+        *[ShapeOnly((big,), "bfloat16") for _ in range(3)],
+    )
+    dump_ir("c2_fused_ssa_2p28_bf16", zoo.fused_mul_add_ssa, *[ShapeOnly((big,), "bfloat16") for _ in range(3)])
+
+    # ---------------- rank-1 families ----------------------------------------------------------
+    rng = np.random.default_rng(2001)
+    n = 1024
+    for dtype in ("f32", "bf16", "f16"):
+        x = ROUNDERS[dtype](rng.uniform(0.5, 2.0, n).astype(np.float32))
+        y = ROUNDERS[dtype](rng.uniform(0.5, 2.0, n).astype(np.float32))
+        for op in ("add", "sub", "mul", "div", "max", "min"):
+            if dtype != "f32" and op not in ("add", "mul", "sub"):
+                continue
+            run_case(
+                f"bin_{op}_{n}_{dtype}",
+                zoo.make_indexed_binary(op, n),
+                {"src": (x, dtype), "other": (y, dtype), "dst": (np.zeros(n), dtype)},
+                ["dst"],
+            )
+    x = rng.uniform(0.25, 3.0, 512).astype(np.float32)
+    for op in ("neg", "abs", "copy", "sqrt", "rsqrt", "exp", "log", "exp2", "log2", "sin", "cos", "erf", "floor", "ceil", "trunc"):
+        signed = x * np.where(np.arange(512) % 2 == 0, 1.0, -1.0).astype(np.float32)
+        src = x if op in ("sqrt", "rsqrt", "log", "log2") else signed
+        run_case(
+            f"un_{op}_512_f32",
+            zoo.make_indexed_unary(op, 512),
+            {"src": (src, "f32"), "dst": (np.zeros(512), "f32")},
+            ["dst"],
+        )
+    signed = (x - 1.5).astype(np.float32)
+    run_case(
+        "clamp_scale_512_f32",
+        zoo.make_indexed_clamp_scale(512),
+        {"src": (signed, "f32"), "dst": (np.zeros(512), "f32")},
+        ["dst"],
+        extra=(0.75,),
+    )
+    n = 1000
+    run_case(
+        "masked_add_1000_f32",
+        zoo.make_indexed_masked_add(n),
+        {
+            "src": (rng.uniform(-1, 1, n).astype(np.float32), "f32"),
+            "other": (rng.uniform(-1, 1, n).astype(np.float32), "f32"),
+            "dst": (np.zeros(n), "f32"),
+        },
+        ["dst"],
+    )
+    # tensor-SSA forms
+    p = rng.uniform(-1, 1, (8, 96)).astype(np.float32)
+    q = rng.uniform(-1, 1, (8, 96)).astype(np.float32)
+    run_case("ssa_add_8x96_f32", zoo.ssa_add, {"a": (p, "f32"), "b": (q, "f32"), "c": (np.zeros((8, 96)), "f32")}, ["c"])
+    run_case("ssa_scale_shift_8x96_f32", zoo.ssa_scale_shift, {"a": (p, "f32"), "c": (np.zeros((8, 96)), "f32")}, ["c"])
+    run_case(
+        "ssa_exp_max_8x96_f32", zoo.ssa_exp_max, {"a": (p, "f32"), "b": (q, "f32"), "c": (np.zeros((8, 96)), "f32")}, ["c"]
+    )
+
+    # ---------------- config 3 (reduced) + upstream's own known-answer GEMMs ---------------------
+    rng = np.random.default_rng(1003)
+    m, n_, k = 48, 40, 64
+    a = bf16_round((rng.standard_normal((m, k), dtype=np.float32) / np.sqrt(k)).astype(np.float32))
+    b = bf16_round((rng.standard_normal((n_, k), dtype=np.float32) / np.sqrt(k)).astype(np.float32))
+    run_case(
+        "c3_gemm_abt_48x40x64_bf16",
+        zoo.gemm_abt,
+        {"a": (a, "bf16"), "b": (b, "bf16"), "c": (np.zeros((m, n_)), "bf16")},
+        ["c"],
+    )
+    run_case(
+        "gemm_ab_48x40x64_bf16_f32out",
+        zoo.gemm_ab,
+        {"a": (a, "bf16"), "b": (np.ascontiguousarray(b.T), "bf16"), "c": (np.zeros((m, n_)), "f32")},
+        ["c"],
+    )
+    run_case(
+        "gemm_atb_48x40x64_bf16",
+        zoo.gemm_atb,
+        {"a": (np.ascontiguousarray(a.T), "bf16"), "b": (np.ascontiguousarray(b.T), "bf16"), "c": (np.zeros((m, n_)), "f32")},
+        ["c"],
+    )
+    run_case(
+        "gemm_atbt_48x40x64_bf16",
+        zoo.gemm_atbt,
+        {"a": (np.ascontiguousarray(a.T), "bf16"), "b": (b, "bf16"), "c": (np.zeros((m, n_)), "f32")},
+        ["c"],
+    )
+    # tests/test_backend_hipkittens_exec.py:47-57 — ramp A times identity block B, exact answer
+    ramp = np.array([[row * 16 + col + 1 for col in range(16)] for row in range(32)], dtype=np.float32)
+    eye = np.zeros((16, 32), dtype=np.float32)
+    eye[np.arange(16), np.arange(16)] = 1.0
+    run_case(
+        "gemm_ab_ramp_identity_32x32x16",
+        zoo.gemm_ab,
+        {"a": (ramp, "bf16"), "b": (eye, "bf16"), "c": (np.zeros((32, 32)), "f32")},
+        ["c"],
+    )
+    dump_ir(
+        "c3_gemm_abt_8192_bf16",
+        zoo.gemm_abt,
+        *[ShapeOnly((8192, 8192), "bfloat16") for _ in range(3)],
+    )
+
+    # ---------------- config 4 (reduced) + upstream's rank-3 / full-gamma pattern -----------------
+    rng = np.random.default_rng(1004)
+    x = bf16_round(rng.standard_normal((6, 512), dtype=np.float32))
+    w = bf16_round((1 + 0.1 * rng.standard_normal(512, dtype=np.float32)).astype(np.float32))
+    run_case(
+        "c4_rmsnorm_6x512_bf16_eps1e-6",
+        zoo.make_rmsnorm(1e-6),
+        {"x": (x, "bf16"), "out": (np.zeros((6, 512)), "bf16"), "gamma": (w, "bf16")},
+        ["out"],
+    )
+    # tests/test_backend_hipkittens_exec_norm_attention.py:135-153
+    x3 = np.array(
+        [[[((bt * 4 + row) * 128 + col) % 23 / 8.0 for col in range(128)] for row in range(4)] for bt in range(2)],
+        dtype=np.float32,
+    )
+    g3 = np.array(
+        [[[1.0 + ((bt + row + col) % 9) / 64.0 for col in range(128)] for row in range(4)] for bt in range(2)],
+        dtype=np.float32,
+    )
+    run_case(
+        "rmsnorm_2x4x128_fullgamma_default_eps",
+        zoo.make_rmsnorm(None),
+        {"x": (bf16_round(x3), "bf16"), "out": (np.zeros((2, 4, 128)), "bf16"), "gamma": (bf16_round(g3), "bf16")},
+        ["out"],
+    )
+    dump_ir(
+        "c4_rmsnorm_65536x8192_bf16",
+        zoo.make_rmsnorm(1e-6),
+        ShapeOnly((65536, 8192), "bfloat16"),
+        ShapeOnly((65536, 8192), "bfloat16"),
+        ShapeOnly((8192,), "bfloat16"),
+    )
+
+    # ---------------- config 5 (reduced): causal / full, MHA and GQA ------------------------------
+    rng = np.random.default_rng(1005)
+
+    def attn_inputs(bsz, seq, heads, kv_heads, dim):
+        q = bf16_round(rng.standard_normal((bsz, seq, heads, dim), dtype=np.float32))
+        k = bf16_round(rng.standard_normal((bsz, seq, kv_heads, dim), dtype=np.float32))
+        v = bf16_round(rng.standard_normal((bsz, seq, kv_heads, dim), dtype=np.float32))
+        return {
+            "q": (q, "bf16"),
+            "k": (k, "bf16"),
+            "v": (v, "bf16"),
+            "out": (np.zeros((bsz, seq, heads, dim)), "bf16"),
+            "lse": (np.zeros((bsz, heads, 1, seq)), "f32"),
+        }
+
+    run_case("c5_attn_causal_b1s24h2d32", zoo.attention_causal, attn_inputs(1, 24, 2, 2, 32), ["out", "lse"])
+    run_case("attn_full_b1s24h2d32", zoo.attention_full, attn_inputs(1, 24, 2, 2, 32), ["out", "lse"])
+    run_case("attn_causal_gqa_b2s16h4kv2d16", zoo.attention_causal, attn_inputs(2, 16, 4, 2, 16), ["out", "lse"])
+    dump_ir(
+        "c5_attn_causal_b16s4096h32d128",
+        zoo.attention_causal,
+        *[ShapeOnly((16, 4096, 32, 128), "bfloat16") for _ in range(4)],
+        ShapeOnly((16, 32, 1, 4096), "float32"),
+    )
+    print("golden fixtures written to", HERE)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,223 @@
+"""Kernel zoo shared by the golden-vector generator and the parity tests.
+
+Every kernel here is written once against a DSL module handle ``cute`` so that
+the *same Python body* can be traced by the upstream package (when the golden
+vectors are generated) and by ``baybridge_b200`` (when the tests run).  The
+bodies follow the upstream samples: the indexed forms use the canonical
+``block_idx * block_dim + thread_idx`` prefix of
+``tools/backend_benchmark_kernels.py:691-697`` and the explicit-op kernels are
+the one-liners of ``tests/test_backend_hipkittens_exec.py`` /
+``tests/test_backend_hipkittens_exec_norm_attention.py``.
+"""
+from __future__ import annotations
+
+from types import SimpleNamespace
+
+
+def build_zoo(cute) -> SimpleNamespace:
+    zoo = SimpleNamespace()
+
+    # ---- config 1: rank-2 indexed f32 add, one thread per element -------------------------
+    def make_indexed_add_2d(rows: int, cols: int, block: int = 256):
+        @cute.kernel
+        def indexed_add_2d_kernel(g_a: cute.Tensor, g_b: cute.Tensor, g_c: cute.Tensor):
+            tidx, _, _ = cute.arch.thread_idx()
+            bidx, _, _ = cute.arch.block_idx()
+            bdim, _, _ = cute.arch.block_dim()
+            i = bidx * bdim + tidx
+            col = i % cols
+            row = i // cols
+            g_c[row, col] = g_a[row, col] + g_b[row, col]
+
+        @cute.jit
+        def indexed_add_2d(g_a: cute.Tensor, g_b: cute.Tensor, g_c: cute.Tensor):
+            indexed_add_2d_kernel(g_a, g_b, g_c).launch(
+                grid=((rows * cols + block - 1) // block, 1, 1), block=(block, 1, 1)
+            )
+
+        return indexed_add_2d
+
+    zoo.make_indexed_add_2d = make_indexed_add_2d
+
+    # ---- config 2: fused c = a*b + a, indexed and tensor-SSA forms ---------------------------
+    def make_fused_mul_add_indexed(n: int, block: int = 256):
+        @cute.kernel
+        def fused_mul_add_kernel(a: cute.Tensor, b: cute.Tensor, c: cute.Tensor):
+            tidx, _, _ = cute.arch.thread_idx()
+            bidx, _, _ = cute.arch.block_idx()
+            bdim, _, _ = cute.arch.block_dim()
+            i = bidx * bdim + tidx
+            c[i] = a[i] * b[i] + a[i]
+
+        @cute.jit
+        def fused_mul_add_indexed(a: cute.Tensor, b: cute.Tensor, c: cute.Tensor):
+            fused_mul_add_kernel(a, b, c).launch(grid=((n + block - 1) // block, 1, 1), block=(block, 1, 1))
+
+        return fused_mul_add_indexed
+
+    zoo.make_fused_mul_add_indexed = make_fused_mul_add_indexed
+
+    @cute.kernel
+    def fused_mul_add_ssa(a: cute.Tensor, b: cute.Tensor, c: cute.Tensor):
+        av = a.load()
+        bv = b.load()
+        c.store(av * bv + av)
+
+    zoo.fused_mul_add_ssa = fused_mul_add_ssa
+
+    # ---- rank-1 indexed binary family (upstream PTX conformance shape) --------------------------
+    def make_indexed_binary(op: str, n: int, block: int = 128):
+        def body(lhs, rhs):
+            if op == "add":
+                return lhs + rhs
+            if op == "sub":
+                return lhs - rhs
+            if op == "mul":
+                return lhs * rhs
+            if op == "div":
+                return lhs / rhs
+            if op == "max":
+                return cute.maximum(lhs, rhs)
+            if op == "min":
+                return cute.minimum(lhs, rhs)
+            raise ValueError(op)
+
+        @cute.kernel(launch=cute.LaunchConfig(grid=((n + block - 1) // block, 1, 1), block=(block, 1, 1)))
+        def indexed_binary_kernel(src: cute.Tensor, other: cute.Tensor, dst: cute.Tensor):
+            tidx, _, _ = cute.arch.thread_idx()
+            bidx, _, _ = cute.arch.block_idx()
+            bdim, _, _ = cute.arch.block_dim()
+            idx = bidx * bdim + tidx
+            dst[idx] = body(src[idx], other[idx])
+
+        return indexed_binary_kernel
+
+    zoo.make_indexed_binary = make_indexed_binary
+
+    def make_indexed_unary(op: str, n: int, block: int = 128):
+        @cute.kernel(launch=cute.LaunchConfig(grid=((n + block - 1) // block, 1, 1), block=(block, 1, 1)))
+        def indexed_unary_kernel(src: cute.Tensor, dst: cute.Tensor):
+            idx = cute.program_id("x") * cute.block_dim("x") + cute.thread_idx("x")
+            value = cute.load(src, idx)
+            if op == "neg":
+                result = -value
+            elif op == "abs":
+                result = abs(value)
+            elif op == "copy":
+                result = value
+            else:
+                result = getattr(cute.math, op)(value)
+            cute.store(result, dst, idx)
+
+        return indexed_unary_kernel
+
+    zoo.make_indexed_unary = make_indexed_unary
+
+    # relu-like: compare → select, with a literal constant operand
+    def make_indexed_clamp_scale(n: int, block: int = 128):
+        @cute.kernel(launch=cute.LaunchConfig(grid=((n + block - 1) // block, 1, 1), block=(block, 1, 1)))
+        def indexed_clamp_scale_kernel(src: cute.Tensor, dst: cute.Tensor, alpha: float):
+            tidx, _, _ = cute.arch.thread_idx()
+            bidx, _, _ = cute.arch.block_idx()
+            bdim, _, _ = cute.arch.block_dim()
+            idx = bidx * bdim + tidx
+            value = src[idx]
+            dst[idx] = cute.where(value > 0.0, value * alpha, 0.0)
+
+        return indexed_clamp_scale_kernel
+
+    zoo.make_indexed_clamp_scale = make_indexed_clamp_scale
+
+    # over-provisioned grid guarded by a predicate (masked load / masked store)
+    def make_indexed_masked_add(n: int, block: int = 128):
+        grid = (n + block - 1) // block
+
+        @cute.kernel(launch=cute.LaunchConfig(grid=(grid, 1, 1), block=(block, 1, 1)))
+        def indexed_masked_add_kernel(src: cute.Tensor, other: cute.Tensor, dst: cute.Tensor):
+            tidx, _, _ = cute.arch.thread_idx()
+            bidx, _, _ = cute.arch.block_idx()
+            bdim, _, _ = cute.arch.block_dim()
+            idx = bidx * bdim + tidx
+            inside = idx < n
+            lhs = cute.load(src, idx, predicate=inside, else_value=0.0)
+            rhs = cute.load(other, idx, predicate=inside, else_value=0.0)
+            cute.store(lhs + rhs, dst, idx, predicate=inside)
+
+        return indexed_masked_add_kernel
+
+    zoo.make_indexed_masked_add = make_indexed_masked_add
+
+    # tensor-SSA pointwise forms
+    @cute.kernel
+    def ssa_add(a: cute.Tensor, b: cute.Tensor, c: cute.Tensor):
+        c.store(a.load() + b.load())
+
+    zoo.ssa_add = ssa_add
+
+    @cute.kernel
+    def ssa_scale_shift(a: cute.Tensor, c: cute.Tensor):
+        c.store(a.load() * 0.5 - 2.0)
+
+    zoo.ssa_scale_shift = ssa_scale_shift
+
+    @cute.kernel
+    def ssa_exp_max(a: cute.Tensor, b: cute.Tensor, c: cute.Tensor):
+        c.store(cute.maximum(cute.math.exp(a.load()), b.load()))
+
+    zoo.ssa_exp_max = ssa_exp_max
+
+    # ---- explicit single-op kernels ---------------------------------------------------------------
+    @cute.kernel
+    def gemm_abt(a: cute.Tensor, b: cute.Tensor, c: cute.Tensor):
+        cute.gemm(a, b, c, transpose_b=True)
+
+    zoo.gemm_abt = gemm_abt
+
+    @cute.kernel
+    def gemm_ab(a: cute.Tensor, b: cute.Tensor, c: cute.Tensor):
+        cute.gemm(a, b, c)
+
+    zoo.gemm_ab = gemm_ab
+
+    @cute.kernel
+    def gemm_atb(a: cute.Tensor, b: cute.Tensor, c: cute.Tensor):
+        cute.gemm(a, b, c, transpose_a=True)
+
+    zoo.gemm_atb = gemm_atb
+
+    @cute.kernel
+    def gemm_atbt(a: cute.Tensor, b: cute.Tensor, c: cute.Tensor):
+        cute.gemm(a, b, c, transpose_a=True, transpose_b=True)
+
+    zoo.gemm_atbt = gemm_atbt
+
+    def make_rmsnorm(epsilon: float | None = None):
+        if epsilon is None:
+
+            @cute.kernel
+            def rmsnorm_default_eps(x: cute.Tensor, out: cute.Tensor, gamma: cute.Tensor):
+                cute.rmsnorm(x, out, gamma)
+
+            return rmsnorm_default_eps
+
+        @cute.kernel
+        def rmsnorm_kernel(x: cute.Tensor, out: cute.Tensor, gamma: cute.Tensor):
+            cute.rmsnorm(x, out, gamma, epsilon=epsilon)
+
+        return rmsnorm_kernel
+
+    zoo.make_rmsnorm = make_rmsnorm
+
+    @cute.kernel
+    def attention_full(q: cute.Tensor, k: cute.Tensor, v: cute.Tensor, out: cute.Tensor, lse: cute.Tensor):
+        cute.attention(q, k, v, out, lse)
+
+    zoo.attention_full = attention_full
+
+    @cute.kernel
+    def attention_causal(q: cute.Tensor, k: cute.Tensor, v: cute.Tensor, out: cute.Tensor, lse: cute.Tensor):
+        cute.attention(q, k, v, out, lse, causal=True)
+
+    zoo.attention_causal = attention_causal
+
+    return zoo
