@@ -1,6 +1,313 @@
+"""``B200Backend`` — the backend object ``compile(..., backend="b200")`` resolves to.
+
+It implements the duck-typed backend contract of upstream ``backend.py:26-29``
+and ``compiler.py:646-689``: ``name``, ``artifact_extension``, ``lower(ir,
+target) -> LoweredModule``, ``build_launcher(ir, target, lowered_module,
+lowered_path) -> launcher(*args, stream=None)``, ``available(target)`` and
+``supports(ir, target)``.  The launcher follows upstream's executable backend
+(``ptx_exec.py:87-176``): positional arguments in IR argument order, host
+``RuntimeTensor`` arguments staged through device buffers that are cached per
+argument slot and released on error, ``TensorHandle`` / DLPack arguments used
+in place through their device pointer, synchronous completion by default.
+
+Every matched plan runs a hand-written sm_100a kernel through the C ABI of
+``libbb200.so``; when the library or a device is missing the launcher raises —
+there is no CPU path.
+"""
+from __future__ import annotations
+
+import ctypes
+import json
+import threading
+import warnings
+from dataclasses import asdict
+from pathlib import Path
+from typing import Any, Callable
+
+import numpy as np
+
+from ..errors import BackendNotImplementedError
+from ..host_values import DLPACK_CUDA, RuntimeScalar, RuntimeTensor, TensorHandle, from_dlpack
+from ..portable_ir import row_major_stride
+from ..scalar_types import DEVICE_NUMPY, byte_width, normalize_dtype_name
+from . import native
+from .elementwise import THREADS, UNROLL, compile_cubin, render
+from .matcher import AttentionPlan, ElementwisePlan, GemmPlan, RmsNormPlan, match
+
+_thread_state = threading.local()
+
+#: kernels launched through this module since import (bench.py reports it as ``gpu_launches``)
+LAUNCH_COUNTER = {"launches": 0}
+
+
+def _lowered_module_type():
+    from ..driver import LoweredModule
+
+    return LoweredModule
+
+
+def _bind_device(device_id: int) -> None:
+    """Make ``device_id``'s primary context current on this thread (once per thread/device)."""
+    if getattr(_thread_state, "device", None) != device_id:
+        native.call("bb200_init", device_id)
+        _thread_state.device = device_id
+
+
+class _StagedSlot:
+    """Device copy of one host tensor argument, reused while shape/dtype stay the same."""
+
+    def __init__(self, nbytes: int, signature: tuple):
+        self.signature = signature
+        self.nbytes = nbytes
+        self.pointer = ctypes.c_void_p()
+        native.call("bb200_mem_alloc", ctypes.byref(self.pointer), max(nbytes, 16))
+
+    def release(self) -> None:
+        if self.pointer:
+            native.library().bb200_mem_free(self.pointer)
+            self.pointer = ctypes.c_void_p()
+
+
 class B200Backend:
     name = "b200"
+    artifact_extension = ".b200.json"
+
+    def __init__(self, *, device: int = 0, synchronize: bool = True):
+        self.device = device
+        self.synchronize = synchronize
+
+    # -- contract: capability probes ---------------------------------------------------------------
+    def available(self, target: Any = None) -> bool:
+        if target is not None and getattr(target, "arch", "") not in ("sm_100a", "sm_100"):
+            return False
+        return native.device_available()
+
+    def supports(self, ir: Any, target: Any = None) -> bool:
+        try:
+            match(ir)
+        except BackendNotImplementedError:
+            return False
+        return True
+
+    def supports_auto_selection(self, ir: Any, target: Any = None, sample_args: tuple = ()) -> bool:
+        return self.available(target) and self.supports(ir, target)
+
+    # -- contract: lowering ------------------------------------------------------------------------
+    def lower(self, ir: Any, target: Any):
+        arch = getattr(target, "arch", None)
+        if arch not in ("sm_100a", "sm_100"):
+            raise BackendNotImplementedError(f"b200 lowers for NvidiaTarget('sm_100a') only (got {arch!r})")
+        plan = match(ir)
+        record: dict[str, Any] = {"backend": self.name, "kernel": ir.name, "plan": plan.kind, "target": arch}
+        if isinstance(plan, ElementwisePlan):
+            rendered = render(plan, ir)
+            record.update(
+                mode=rendered.mode, compute=rendered.compute, vector_elements=rendered.vec, extent=plan.extent,
+                entry=rendered.entry, tensor_order=list(rendered.tensor_order), scalar_order=list(rendered.scalar_order),
+                scalar_ctypes=list(rendered.scalar_ctypes), source=rendered.source,
+            )
+        else:
+            record.update(asdict(plan))
+            record["entry"] = {"gemm": "bb200_gemm_bf16", "rmsnorm": "bb200_rmsnorm", "attention": "bb200_attention_fwd"}[plan.kind]
+        text = json.dumps(record, indent=1, sort_keys=True) + "\n"
+        return _lowered_module_type()(backend_name=self.name, entry_point=record["entry"], dialect="b200.plan", text=text)
+
+    # -- contract: launcher ------------------------------------------------------------------------
+    def build_launcher(self, ir: Any, target: Any, lowered_module: Any, lowered_path: Path | None = None) -> Callable[..., None]:
+        del lowered_path
+        plan = match(ir)
+        record = json.loads(lowered_module.text)
+        state: dict[str, Any] = {"slots": {}}
+        runner = {
+            "elementwise": self._elementwise_runner, "gemm": self._gemm_runner,
+            "rmsnorm": self._rmsnorm_runner, "attention": self._attention_runner,
+        }[plan.kind](ir, plan, record, state)
+        arguments = ir.arguments
+
+        def launcher(*args: Any, **kwargs: Any) -> None:
+            stream = kwargs.pop("stream", None)
+            if kwargs:
+                raise TypeError("b200 launcher only supports positional arguments and an optional stream=")
+            if len(args) != len(arguments):
+                raise TypeError(f"{ir.name} expects {len(arguments)} arguments, got {len(args)}")
+            native.require_device()
+            staged: list[tuple[RuntimeTensor, _StagedSlot]] = []
+            stream_handle = native.stream_handle(stream)
+            try:
+                pointers: dict[int, int] = {}
+                scalars: dict[int, Any] = {}
+                device_id = self._device_of(args)
+                _bind_device(device_id)
+                for position, (argument, value) in enumerate(zip(arguments, args)):
+                    if argument.kind == "tensor":
+                        pointers[position] = self._tensor_pointer(position, argument, value, stream, stream_handle, state, staged)
+                    else:
+                        scalars[position] = self._scalar_value(argument, value)
+                runner(pointers, scalars, stream_handle)
+                LAUNCH_COUNTER["launches"] += 1
+                if staged or self.synchronize:
+                    native.call("bb200_stream_synchronize", stream_handle)
+                for tensor, slot in staged:
+                    image = np.empty(tensor.numel, dtype=DEVICE_NUMPY[tensor.dtype])
+                    native.call("bb200_memcpy_d2h", image.ctypes.data_as(ctypes.c_void_p), slot.pointer, slot.nbytes, stream_handle)
+                    native.call("bb200_stream_synchronize", stream_handle)
+                    tensor.absorb_device_image(image)
+            except Exception:
+                for slot in state.pop("slots", {}).values():
+                    slot.release()
+                state["slots"] = {}
+                raise
+
+        launcher.plan = plan  # type: ignore[attr-defined]
+        return launcher
+
+    # -- argument marshalling ------------------------------------------------------------------------
+    def _device_of(self, args: tuple[Any, ...]) -> int:
+        devices = {int(value.device_id) for value in args if isinstance(value, TensorHandle)}
+        if len(devices) > 1:
+            raise BackendNotImplementedError(f"b200: tensor arguments live on different devices {sorted(devices)}")
+        return devices.pop() if devices else self.device
+
+    def _tensor_pointer(self, position, argument, value, stream, stream_handle, state, staged) -> int:
+        spec = argument.spec
+        if not isinstance(value, (RuntimeTensor, TensorHandle)) and hasattr(value, "__dlpack__") and hasattr(value, "__dlpack_device__"):
+            value = from_dlpack(value, stream=stream)
+        if isinstance(value, TensorHandle):
+            if int(value.device_type) != DLPACK_CUDA:
+                raise BackendNotImplementedError(f"b200 currently requires CUDA TensorHandle inputs for tensor argument '{argument.name}'")
+            if tuple(value.shape) != tuple(spec.shape) or normalize_dtype_name(value.dtype) != spec.dtype:
+                raise TypeError(
+                    f"b200 tensor argument '{argument.name}' expects {spec.dtype}{list(spec.shape)}, got {value.dtype}{list(value.shape)}"
+                )
+            if value.stride is not None and tuple(value.stride) != row_major_stride(value.shape):
+                raise BackendNotImplementedError(
+                    f"b200 currently requires contiguous CUDA TensorHandle inputs for tensor argument '{argument.name}'"
+                )
+            pointer = value.data_ptr() or value.raw_address
+            if not pointer:
+                raise TypeError(f"b200 tensor handle for argument '{argument.name}' does not expose a usable data_ptr()")
+            return int(pointer)
+        if isinstance(value, RuntimeTensor):
+            if tuple(value.shape) != tuple(spec.shape) or value.dtype != spec.dtype:
+                raise TypeError(
+                    f"b200 tensor argument '{argument.name}' expects {spec.dtype}{list(spec.shape)}, got {value.dtype}{list(value.shape)}"
+                )
+            if not state.get("warned_staging"):
+                warnings.warn(
+                    f"b200 is staging RuntimeTensor argument '{argument.name}' through host memory; pass CUDA TensorHandle "
+                    "values (or DLPack-capable device tensors) to avoid host-copy dominated timings",
+                    RuntimeWarning, stacklevel=4,
+                )
+                state["warned_staging"] = True
+            image = value.device_image()
+            signature = (value.shape, value.dtype)
+            slot = state["slots"].get(position)
+            if slot is None or slot.signature != signature:
+                if slot is not None:
+                    slot.release()
+                slot = state["slots"][position] = _StagedSlot(image.nbytes, signature)
+            native.call("bb200_memcpy_h2d", slot.pointer, image.ctypes.data_as(ctypes.c_void_p), image.nbytes, stream_handle)
+            native.call("bb200_stream_synchronize", stream_handle)  # `image` is pageable and about to go out of scope
+            staged.append((value, slot))
+            return int(slot.pointer.value)
+        raise TypeError(
+            "b200 currently expects RuntimeTensor values, CUDA TensorHandle values, or CUDA DLPack-capable tensor objects "
+            f"for tensor argument '{argument.name}', got {type(value).__name__}"
+        )
+
+    @staticmethod
+    def _scalar_value(argument, value: Any) -> Any:
+        if isinstance(value, RuntimeScalar):
+            if normalize_dtype_name(value.dtype) != argument.spec.dtype:
+                raise TypeError(f"b200 scalar argument '{argument.name}' expects dtype {argument.spec.dtype}, got {value.dtype}")
+            return value.value
+        if not isinstance(value, (bool, int, float)):
+            raise TypeError(f"b200 scalar argument '{argument.name}' expects a number, got {type(value).__name__}")
+        return value
+
+    # -- per-plan runners ----------------------------------------------------------------------------
+    def _elementwise_runner(self, ir, plan: ElementwisePlan, record: dict[str, Any], state: dict[str, Any]):
+        cubin_path = compile_cubin(record["source"])  # nvcc runs here, at compile() time, GPU or not
+        tensor_order, scalar_order = record["tensor_order"], record["scalar_order"]
+        ctype_of = {"double": ctypes.c_double, "int32_t": ctypes.c_int32, "int64_t": ctypes.c_int64}
+        scalar_ctypes = [ctype_of[name] for name in record["scalar_ctypes"]]
+        flat = record["mode"] == "flat"
+        extent = int(record["extent"])
+        if flat:
+            tile = THREADS * int(record["vector_elements"]) * UNROLL
+            grid = native.U3(max(1, -(-extent // tile)), 1, 1)
+            block = native.U3(THREADS, 1, 1)
+        else:
+            grid, block = native.U3(*ir.launch.grid), native.U3(*ir.launch.block)
+        cluster = native.U3(1, 1, 1)
+        entry = record["entry"].encode()
+
+        def run(pointers: dict[int, int], scalars: dict[int, Any], stream_handle) -> None:
+            function = state.get("function")
+            if function is None:
+                image = cubin_path.read_bytes()
+                module = ctypes.c_void_p()
+                native.call("bb200_module_load", image, len(image), ctypes.byref(module))
+                function = ctypes.c_void_p()
+                native.call("bb200_get_function", module, entry, ctypes.byref(function))
+                state["module"], state["function"] = module, function
+            values: list[Any] = [ctypes.c_void_p(pointers[position]) for position in tensor_order]
+            values += [ctype(scalars[position]) for position, ctype in zip(scalar_order, scalar_ctypes)]
+            if flat:
+                aligned = all(pointers[position] % 16 == 0 for position in tensor_order)
+                values += [ctypes.c_size_t(extent), ctypes.c_int(1 if aligned else 0)]
+            params = (ctypes.c_void_p * len(values))(*[ctypes.cast(ctypes.byref(v), ctypes.c_void_p) for v in values])
+            native.call("bb200_launch", function, grid, block, cluster, 0, stream_handle, params)
+
+        return run
+
+    def _rmsnorm_runner(self, ir, plan: RmsNormPlan, record, state):
+        code = native.DTYPE_CODES[plan.dtype]
+
+        def run(pointers, scalars, stream_handle) -> None:
+            native.call("bb200_rmsnorm", code, pointers[plan.x], pointers[plan.gamma], pointers[plan.out], plan.rows,
+                        plan.hidden, 1 if plan.gamma_is_full else 0, plan.epsilon, stream_handle)
+
+        return run
+
+    def _gemm_runner(self, ir, plan: GemmPlan, record, state):
+        c_code = native.DTYPE_CODES[plan.c_dtype]
+
+        def run(pointers, scalars, stream_handle) -> None:
+            native.call("bb200_gemm_bf16", pointers[plan.a], pointers[plan.b], pointers[plan.c], plan.m, plan.n, plan.k,
+                        int(plan.transpose_a), int(plan.transpose_b), c_code, stream_handle)
+
+        return run
+
+    def _attention_runner(self, ir, plan: AttentionPlan, record, state):
+        def run(pointers, scalars, stream_handle) -> None:
+            native.call("bb200_attention_fwd", pointers[plan.q], pointers[plan.k], pointers[plan.v], pointers[plan.out],
+                        pointers[plan.lse], plan.batch, plan.seq, plan.heads, plan.kv_heads, plan.head_dim,
+                        int(plan.causal), stream_handle)
+
+        return run
 
 
-def install_into_upstream():
-    raise NotImplementedError
+def install_into_upstream(module: Any = None) -> None:
+    """Register ``"b200"`` inside an importable upstream ``baybridge`` package.
+
+    Upstream resolves backend names with a hard-coded chain (``compiler.py:127-162``); this wraps
+    that resolver so ``baybridge.compile(kernel, ..., backend="b200", target=NvidiaTarget("sm_100a"))``
+    returns an artifact that launches through this backend.  Idempotent.
+    """
+    if module is None:
+        import importlib
+
+        module = importlib.import_module("baybridge")
+    compiler = module.compiler if hasattr(module, "compiler") else __import__("baybridge.compiler", fromlist=["compiler"])
+    original = compiler._resolve_backend
+    if getattr(original, "_bb200_installed", False):
+        return
+
+    def resolve(backend):
+        if backend == "b200":
+            return "b200", B200Backend()
+        return original(backend)
+
+    resolve._bb200_installed = True  # type: ignore[attr-defined]
+    compiler._resolve_backend = resolve

@@ -1,0 +1,684 @@
+"""Portable-IR pattern matcher of the b200 backend.
+
+``match(ir)`` classifies a traced kernel as one of
+
+* ``GemmPlan`` / ``RmsNormPlan`` / ``AttentionPlan`` — a single explicit op whose
+  operands are kernel arguments (the "single explicit op" rule of upstream
+  ``hipkittens_ref.py:88-275`` and ``hipkittens_exec.py:631-894``), or
+* ``ElementwisePlan`` — a load / scalar-expression / store body, in the indexed
+  scalar form or the tensor-SSA form,
+
+and raises ``BackendNotImplementedError`` for anything else (no CPU fallback).
+
+Unlike upstream's positional matcher (``ptx_bridge.py:542-586`` requires an
+exact op sequence), elementwise matching here is dataflow based: every value is
+resolved through the op graph, repeated loads of one tensor are merged, and the
+index of every access is analysed symbolically.  When every access provably hits
+linear offset ``i`` for the global thread id ``i`` — e.g. ``g[i // C, i % C]``
+on a row-major ``[R, C]`` tensor — the kernel is a *flat map* and may be
+re-gridded into 128-bit vector steps.  Otherwise it is lowered *literally*: one
+device thread per traced thread with the traced index arithmetic and a bounds
+guard on every access (the guard upstream's PTX emits, ``ptx_bridge.py:5846``).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any
+
+from ..errors import BackendNotImplementedError
+from ..portable_ir import row_major_stride
+
+FLOAT_DTYPES = ("f32", "bf16", "f16")
+STORAGE_DTYPES = ("f32", "bf16", "f16", "i32", "i64", "index", "i8", "i1")
+
+UNARY_OPS = {
+    "neg", "abs", "bitnot", "cast",
+    "math_round", "math_floor", "math_ceil", "math_trunc", "math_acos", "math_asin", "math_atan", "math_sqrt",
+    "math_rsqrt", "math_exp", "math_sin", "math_cos", "math_exp2", "math_log", "math_log2", "math_log10", "math_erf",
+}
+BINARY_OPS = {
+    "add", "sub", "mul", "div", "floordiv", "mod", "max", "min", "math_atan2",
+    "cmp_lt", "cmp_le", "cmp_gt", "cmp_ge", "cmp_eq", "cmp_ne",
+    "and", "or", "xor", "bitand", "bitor", "bitxor",
+}
+TENSOR_OP_ALIASES = {
+    "tensor_add": "add", "tensor_sub": "sub", "tensor_mul": "mul", "tensor_div": "div", "tensor_max": "max",
+    "tensor_min": "min", "tensor_neg": "neg", "tensor_abs": "abs", "tensor_bitand": "bitand", "tensor_bitor": "bitor",
+    "tensor_bitxor": "bitxor", "tensor_bitnot": "bitnot",
+}
+TOPOLOGY_OPS = {"thread_idx", "block_idx", "program_id", "block_dim", "grid_dim"}
+
+
+def _unsupported(message: str) -> BackendNotImplementedError:
+    return BackendNotImplementedError(f"b200: {message}")
+
+
+# ---------------------------------------------------------------------------------------------
+# plans
+# ---------------------------------------------------------------------------------------------
+@dataclass(frozen=True)
+class GemmPlan:
+    a: int  # positions in ir.arguments
+    b: int
+    c: int
+    m: int
+    n: int
+    k: int
+    transpose_a: bool
+    transpose_b: bool
+    operand_dtype: str
+    c_dtype: str
+    kind: str = "gemm"
+
+    @property
+    def flops(self) -> int:
+        return 2 * self.m * self.n * self.k
+
+
+@dataclass(frozen=True)
+class RmsNormPlan:
+    x: int
+    out: int
+    gamma: int
+    rows: int
+    hidden: int
+    gamma_is_full: bool
+    epsilon: float
+    dtype: str
+    kind: str = "rmsnorm"
+
+
+@dataclass(frozen=True)
+class AttentionPlan:
+    q: int
+    k: int
+    v: int
+    out: int
+    lse: int
+    batch: int
+    seq: int
+    heads: int
+    kv_heads: int
+    head_dim: int
+    causal: bool
+    dtype: str
+    kind: str = "attention"
+
+
+@dataclass(frozen=True)
+class Node:
+    """One value of the per-element expression graph."""
+
+    name: str
+    op: str  # "input" | "scalar_arg" | "constant" | "index" | unary/binary op | "select"
+    dtype: str
+    operands: tuple[str, ...] = ()
+    attrs: dict[str, Any] = field(default_factory=dict)
+
+
+@dataclass(frozen=True)
+class ElementwisePlan:
+    """``mode == "flat"``: ``nodes`` computes, for linear element ``i < extent``, the values stored by
+    ``stores`` = ((tensor argument position, value name), …); ``inputs`` are the tensor argument
+    positions that are read (each exactly once per element).
+
+    ``mode == "literal"``: ``nodes`` additionally contains the traced index arithmetic; loads and
+    stores carry explicit per-axis index operands and optional predicates, and the launch is the
+    traced launch."""
+
+    mode: str
+    nodes: tuple[Node, ...]
+    inputs: tuple[int, ...]
+    stores: tuple[tuple[Any, ...], ...]
+    scalars: tuple[int, ...]
+    extent: int
+    kind: str = "elementwise"
+
+
+# ---------------------------------------------------------------------------------------------
+# explicit single-op kernels
+# ---------------------------------------------------------------------------------------------
+def _argument_positions(ir) -> dict[str, int]:
+    return {argument.name: position for position, argument in enumerate(ir.arguments)}
+
+
+def _tensor_arg(ir, positions: dict[str, int], name: str, what: str):
+    if name not in positions or ir.arguments[positions[name]].kind != "tensor":
+        raise _unsupported(f"{what} operands must be kernel tensor arguments (got '{name}')")
+    spec = ir.arguments[positions[name]].spec
+    if not spec.resolved_layout().is_row_major or spec.address_space.value != "global":
+        raise _unsupported(f"{what} operand '{name}' must be a row-major global tensor")
+    return positions[name], spec
+
+
+def _match_gemm(ir, op) -> GemmPlan:
+    positions = _argument_positions(ir)
+    (a, a_spec), (b, b_spec), (c, c_spec) = (_tensor_arg(ir, positions, name, "gemm") for name in op.inputs)
+    if not (len(a_spec.shape) == len(b_spec.shape) == len(c_spec.shape) == 2):
+        raise _unsupported("gemm requires rank-2 operands")
+    transpose_a, transpose_b = bool(op.attrs.get("transpose_a")), bool(op.attrs.get("transpose_b"))
+    k, m = a_spec.shape if transpose_a else a_spec.shape[::-1]
+    n, kb = b_spec.shape if transpose_b else b_spec.shape[::-1]
+    if kb != k or c_spec.shape != (m, n):
+        raise _unsupported(f"gemm shape mismatch: {a_spec.shape} x {b_spec.shape} -> {c_spec.shape}")
+    tile = op.attrs.get("tile")
+    if tile is not None and tuple(tile) != (m, n, k):
+        raise _unsupported("mma with a tile smaller than the operands (a sub-tile of a larger kernel) is not a whole-GEMM op")
+    if a_spec.dtype != "bf16" or b_spec.dtype != "bf16":
+        raise _unsupported(f"gemm operands must be bf16 (got {a_spec.dtype}, {b_spec.dtype})")
+    if c_spec.dtype not in ("bf16", "f32"):
+        raise _unsupported(f"gemm output must be bf16 or f32 (got {c_spec.dtype})")
+    return GemmPlan(a, b, c, m, n, k, transpose_a, transpose_b, "bf16", c_spec.dtype)
+
+
+def _match_rmsnorm(ir, op) -> RmsNormPlan:
+    positions = _argument_positions(ir)
+    (x, x_spec), (out, out_spec), (gamma, gamma_spec) = (_tensor_arg(ir, positions, name, "rmsnorm") for name in op.inputs)
+    if x_spec.shape != out_spec.shape or not x_spec.shape:
+        raise _unsupported("rmsnorm requires x and out of equal, non-scalar shape")
+    hidden = x_spec.shape[-1]
+    if gamma_spec.shape not in ((hidden,), x_spec.shape):
+        raise _unsupported(f"rmsnorm gamma shape must be {(hidden,)} or {x_spec.shape}")
+    if not (x_spec.dtype == out_spec.dtype == gamma_spec.dtype) or x_spec.dtype not in FLOAT_DTYPES:
+        raise _unsupported("rmsnorm requires x, out and gamma of one dtype among f32/bf16/f16")
+    vector = 4 if x_spec.dtype == "f32" else 8
+    if hidden % vector:
+        raise _unsupported(f"rmsnorm hidden size {hidden} must be a multiple of {vector} for {x_spec.dtype}")
+    full = gamma_spec.shape == x_spec.shape and len(x_spec.shape) > 1
+    return RmsNormPlan(x, out, gamma, x_spec.numel // hidden, hidden, full, float(op.attrs.get("epsilon", 1e-5)), x_spec.dtype)
+
+
+def _match_attention(ir, op) -> AttentionPlan:
+    positions = _argument_positions(ir)
+    (q, q_spec), (k, k_spec), (v, v_spec), (out, out_spec), (lse, lse_spec) = (
+        _tensor_arg(ir, positions, name, "attention") for name in op.inputs
+    )
+    if not (len(q_spec.shape) == len(k_spec.shape) == len(v_spec.shape) == len(out_spec.shape) == 4):
+        raise _unsupported("attention requires rank-4 q, k, v and out")
+    batch, seq, heads, head_dim = q_spec.shape
+    if out_spec.shape != q_spec.shape or k_spec.shape != v_spec.shape:
+        raise _unsupported("attention requires q/out and k/v of matching shapes")
+    kv_batch, kv_seq, kv_heads, kv_dim = k_spec.shape
+    if (kv_batch, kv_seq, kv_dim) != (batch, seq, head_dim) or heads % kv_heads:
+        raise _unsupported("attention requires compatible q/k/v shapes and heads divisible by kv heads")
+    if lse_spec.shape not in ((batch, heads, 1, seq), (batch, heads, seq)) or lse_spec.dtype != "f32":
+        raise _unsupported("attention lse must be f32 of shape [batch, heads, 1, seq] or [batch, heads, seq]")
+    if any(spec.dtype != "bf16" for spec in (q_spec, k_spec, v_spec, out_spec)):
+        raise _unsupported("attention operands must be bf16")
+    if head_dim not in (64, 128):
+        raise _unsupported(f"attention head_dim must be 64 or 128 (got {head_dim})")
+    return AttentionPlan(q, k, v, out, lse, batch, seq, heads, kv_heads, head_dim, bool(op.attrs.get("causal")), "bf16")
+
+
+# ---------------------------------------------------------------------------------------------
+# symbolic index analysis
+# ---------------------------------------------------------------------------------------------
+@dataclass(frozen=True)
+class Digit:
+    """``(i // div) % mod`` of the global linear thread id ``i`` (``mod is None`` = no wrap)."""
+
+    div: int
+    mod: int | None
+
+
+class Sym:
+    """Integer-valued expression ``const + Σ coef · digit`` (``None`` terms = not analysable)."""
+
+    __slots__ = ("terms", "const")
+
+    def __init__(self, terms: dict[Digit, int] | None = None, const: int = 0):
+        self.terms = {digit: coef for digit, coef in (terms or {}).items() if coef}
+        self.const = const
+
+    @property
+    def is_const(self) -> bool:
+        return not self.terms
+
+    def single_digit(self) -> Digit | None:
+        if self.const == 0 and len(self.terms) == 1:
+            (digit, coef), = self.terms.items()
+            if coef == 1:
+                return digit
+        return None
+
+    def plus(self, other: "Sym", sign: int = 1) -> "Sym":
+        merged = dict(self.terms)
+        for digit, coef in other.terms.items():
+            merged[digit] = merged.get(digit, 0) + sign * coef
+        return Sym(merged, self.const + sign * other.const)
+
+    def scaled(self, factor: int) -> "Sym":
+        return Sym({digit: coef * factor for digit, coef in self.terms.items()}, self.const * factor)
+
+    def equals_linear_id(self, threads: int) -> bool:
+        """True iff the expression equals ``i`` for every ``0 <= i < threads`` (digits tile exactly)."""
+        if self.const != 0 or not self.terms:
+            return False
+        expected_div = 1
+        ordered = sorted(self.terms.items(), key=lambda item: item[0].div)
+        for position, (digit, coef) in enumerate(ordered):
+            if digit.div != expected_div or coef != expected_div:
+                return False
+            last = position == len(ordered) - 1
+            if digit.mod is None:
+                return last
+            if last:
+                return digit.div * digit.mod >= threads
+            expected_div = digit.div * digit.mod
+        return False
+
+
+class _Elementwise:
+    """Walks the op list once, building the per-element expression graph and the access list."""
+
+    def __init__(self, ir):
+        self.ir = ir
+        self.positions = _argument_positions(ir)
+        self.launch = ir.launch
+        self.nodes: dict[str, Node] = {}
+        self.order: list[str] = []
+        self.sym: dict[str, Sym | None] = {}
+        self.accesses: list[dict[str, Any]] = []  # loads and stores in program order
+        self.bound: int | None = None  # i < bound predicate shared by all masked accesses
+        self.flat_ok = True
+        self.flat_reason = ""
+        one_d = self.launch.grid[1:] == (1, 1) and self.launch.block[1:] == (1, 1)
+        self.one_d = one_d
+
+    # -- node helpers ---------------------------------------------------------------------------
+    def add(self, node: Node) -> None:
+        self.nodes[node.name] = node
+        self.order.append(node.name)
+
+    def not_flat(self, reason: str) -> None:
+        if self.flat_ok:
+            self.flat_ok, self.flat_reason = False, reason
+
+    def dtype_of(self, name: str) -> str:
+        return self.nodes[name].dtype
+
+    # -- scalar (indexed) form ------------------------------------------------------------------
+    def topology(self, op) -> None:
+        axis = op.attrs["axis"]
+        name = op.outputs[0]
+        index = "xyz".index(axis)
+        if op.op == "block_dim":
+            value = self.launch.block[index]
+            self.add(Node(name, "constant", "index", attrs={"value": value}))
+            self.sym[name] = Sym(const=value)
+            return
+        if op.op == "grid_dim":
+            value = self.launch.grid[index]
+            self.add(Node(name, "constant", "index", attrs={"value": value}))
+            self.sym[name] = Sym(const=value)
+            return
+        kind = "thread_idx" if op.op == "thread_idx" else "block_idx"
+        self.add(Node(name, "index", "index", attrs={"builtin": kind, "axis": axis}))
+        extent = (self.launch.block if kind == "thread_idx" else self.launch.grid)[index]
+        if extent == 1:
+            self.sym[name] = Sym(const=0)
+        elif axis == "x" and self.one_d:
+            block = self.launch.block[0]
+            # i = block_idx.x * block + thread_idx.x  ⇒  thread_idx.x = i % block, block_idx.x = i // block
+            self.sym[name] = Sym({Digit(1, block): 1}) if kind == "thread_idx" else Sym({Digit(block, None): 1})
+        else:
+            self.sym[name] = None
+
+    def scalar_arith(self, op) -> None:
+        name = op.outputs[0]
+        dtype = op.attrs["result"]["dtype"]
+        base = op.op
+        attrs = {k: v for k, v in op.attrs.items() if k != "result"}
+        self.add(Node(name, base, dtype, tuple(op.inputs), attrs))
+        syms = [self.sym.get(operand) for operand in op.inputs]
+        result: Sym | None = None
+        if dtype in ("index", "i32", "i64") and all(s is not None for s in syms):
+            if base == "add":
+                result = syms[0].plus(syms[1])
+            elif base == "sub":
+                result = syms[0].plus(syms[1], -1)
+            elif base == "mul":
+                if syms[0].is_const:
+                    result = syms[1].scaled(syms[0].const)
+                elif syms[1].is_const:
+                    result = syms[0].scaled(syms[1].const)
+            elif base in ("floordiv", "mod") and syms[1].is_const and syms[1].const > 0:
+                divisor = syms[1].const
+                if syms[0].is_const:
+                    result = Sym(const=syms[0].const // divisor if base == "floordiv" else syms[0].const % divisor)
+                else:
+                    result = self._divmod(syms[0], divisor, base)
+        self.sym[name] = result
+
+    @staticmethod
+    def _divmod(value: Sym, divisor: int, op: str) -> Sym | None:
+        # reassemble "i // d" style sums (e.g. block_idx*block + thread_idx) into a single digit first
+        digit = value.single_digit()
+        if digit is None:
+            probe = Sym(dict(value.terms), value.const)
+            if probe.const == 0 and probe.equals_linear_id(1 << 62):
+                digit = Digit(1, None)
+        if digit is None:
+            return None
+        if op == "floordiv":
+            if digit.mod is None:
+                return Sym({Digit(digit.div * divisor, None): 1})
+            if digit.mod % divisor == 0:
+                return Sym({Digit(digit.div * divisor, digit.mod // divisor): 1})
+            return None
+        if digit.mod is None or digit.mod % divisor == 0:
+            return Sym({Digit(digit.div, divisor): 1})
+        if divisor % digit.mod == 0:
+            return Sym({digit: 1})
+        return None
+
+    def access(self, op) -> None:
+        rank = op.attrs["rank"]
+        masked = op.op.startswith("masked_")
+        is_load = op.op.endswith("load")
+        operands = list(op.inputs)
+        value = None if is_load else operands.pop(0)
+        tensor = operands.pop(0)
+        indices = operands[:rank]
+        predicate = operands[rank] if masked else None
+        fallback = operands[rank + 1] if masked and is_load else None
+        if tensor not in self.positions or self.ir.arguments[self.positions[tensor]].kind != "tensor":
+            raise _unsupported(f"{op.op} on '{tensor}', which is not a kernel tensor argument")
+        spec = self.ir.arguments[self.positions[tensor]].spec
+        if spec.dtype not in STORAGE_DTYPES or spec.address_space.value != "global":
+            raise _unsupported(f"tensor '{tensor}' has unsupported dtype/address space {spec.dtype}/{spec.address_space.value}")
+        stride = spec.resolved_layout().stride
+        offset: Sym | None = Sym()
+        for index_name, step in zip(indices, stride):
+            part = self.sym.get(index_name)
+            if part is None:
+                offset = None
+                break
+            offset = offset.plus(part.scaled(step))
+        record = {
+            "kind": "load" if is_load else "store", "tensor": self.positions[tensor], "indices": tuple(indices),
+            "predicate": predicate, "fallback": fallback, "value": value, "offset": offset, "numel": spec.numel,
+            "result": op.outputs[0] if is_load else None, "dtype": spec.dtype, "shape": spec.shape, "stride": stride,
+        }
+        self.accesses.append(record)
+        if is_load:
+            self.add(Node(op.outputs[0], "load", spec.dtype, attrs={"access": len(self.accesses) - 1}))
+        if predicate is not None:
+            bound = self._predicate_bound(predicate)
+            if bound is None:
+                self.not_flat("a predicate that is not `linear_id < constant`")
+            elif self.bound is not None and self.bound != bound:
+                self.not_flat("accesses guarded by different bounds")
+            else:
+                self.bound = bound
+
+    def _predicate_bound(self, name: str) -> int | None:
+        node = self.nodes.get(name)
+        if node is None or node.op != "cmp_lt":
+            return None
+        lhs, rhs = (self.sym.get(operand) for operand in node.operands)
+        if lhs is None or rhs is None or not rhs.is_const:
+            return None
+        return rhs.const if lhs.equals_linear_id(1 << 62) else None
+
+    # -- classification -------------------------------------------------------------------------
+    def finish_scalar(self) -> ElementwisePlan:
+        if not any(access["kind"] == "store" for access in self.accesses):
+            raise _unsupported("the kernel body stores nothing")
+        threads = self.launch.threads
+        if not self.one_d:
+            self.not_flat("a multi-dimensional launch")
+        for access in self.accesses:
+            if access["offset"] is None or not access["offset"].equals_linear_id(threads):
+                self.not_flat("an access whose offset is not provably the linear thread id")
+        scalars = tuple(position for position, argument in enumerate(self.ir.arguments) if argument.kind == "scalar")
+        if self.flat_ok:
+            return self._flat_plan(threads, scalars)
+        return self._literal_plan(scalars)
+
+    def _flat_plan(self, threads: int, scalars: tuple[int, ...]) -> ElementwisePlan:
+        extent = min([threads] + [access["numel"] for access in self.accesses] + ([self.bound] if self.bound is not None else []))
+        current: dict[int, str] = {}  # tensor position → value name that a later load must observe
+        alias: dict[str, str] = {}
+        inputs: list[int] = []
+        first_load: dict[int, str] = {}
+        stores: dict[int, str] = {}
+        for access in self.accesses:
+            tensor = access["tensor"]
+            if access["kind"] == "load":
+                if tensor in current:
+                    alias[access["result"]] = current[tensor]  # store→load forwarding inside one thread
+                elif tensor in first_load:
+                    alias[access["result"]] = first_load[tensor]  # CSE of repeated loads
+                else:
+                    first_load[tensor] = access["result"]
+                    inputs.append(tensor)
+            else:
+                current[tensor] = access["value"]
+                stores[tensor] = access["value"]
+
+        def resolve(name: str) -> str:
+            while name in alias:
+                name = alias[name]
+            return name
+
+        # with every access inside `i < extent`, masked loads never take their fallback
+        live = _live_set(self.nodes, [resolve(value) for value in stores.values()], resolve)
+        nodes: list[Node] = []
+        for name in self.order:
+            if name not in live:
+                continue
+            node = self.nodes[name]
+            if node.op == "load":
+                access = self.accesses[node.attrs["access"]]
+                nodes.append(Node(name, "input", node.dtype, attrs={"tensor": access["tensor"]}))
+            elif node.op == "index":
+                raise _unsupported("a stored value depends on the thread index itself (iota-style bodies are not lowered yet)")
+            else:
+                nodes.append(Node(name, node.op, node.dtype, tuple(resolve(operand) for operand in node.operands), node.attrs))
+        return ElementwisePlan(
+            mode="flat", nodes=tuple(nodes), inputs=tuple(inputs),
+            stores=tuple((tensor, resolve(value)) for tensor, value in stores.items()),
+            scalars=tuple(s for s in scalars if self.ir.arguments[s].name in live), extent=extent,
+        )
+
+    def _literal_plan(self, scalars: tuple[int, ...]) -> ElementwisePlan:
+        nodes: list[Node] = []
+        stores: list[tuple[Any, ...]] = []
+        for name in self.order:
+            node = self.nodes[name]
+            if node.op == "load":
+                access = self.accesses[node.attrs["access"]]
+                nodes.append(Node(name, "load", node.dtype, access["indices"], {
+                    "tensor": access["tensor"], "predicate": access["predicate"], "fallback": access["fallback"],
+                    "shape": access["shape"], "stride": access["stride"]}))
+            else:
+                nodes.append(node)
+        for access in self.accesses:
+            if access["kind"] == "store":
+                stores.append((access["tensor"], access["value"], access["indices"], access["predicate"],
+                               access["shape"], access["stride"]))
+        inputs = tuple(dict.fromkeys(access["tensor"] for access in self.accesses if access["kind"] == "load"))
+        return ElementwisePlan(mode="literal", nodes=tuple(nodes), inputs=inputs, stores=tuple(stores), scalars=scalars,
+                               extent=self.launch.threads)
+
+
+def _live_set(nodes: dict[str, Node], roots: list[str], resolve) -> set[str]:
+    live: set[str] = set()
+    stack = list(roots)
+    while stack:
+        name = resolve(stack.pop())
+        if name in live:
+            continue
+        live.add(name)
+        node = nodes.get(name)
+        if node is not None:
+            stack.extend(node.operands)
+    return live
+
+
+def _match_scalar_elementwise(ir) -> ElementwisePlan:
+    walker = _Elementwise(ir)
+    for position, argument in enumerate(ir.arguments):
+        if argument.kind == "scalar":
+            walker.add(Node(argument.name, "scalar_arg", argument.spec.dtype, attrs={"position": position}))
+            walker.sym[argument.name] = None
+    for op in ir.operations:
+        if op.op in TOPOLOGY_OPS:
+            walker.topology(op)
+        elif op.op == "constant":
+            dtype = op.attrs["result"]["dtype"]
+            walker.add(Node(op.outputs[0], "constant", dtype, attrs={"value": op.attrs["value"]}))
+            value = op.attrs["value"]
+            walker.sym[op.outputs[0]] = Sym(const=int(value)) if dtype in ("index", "i32", "i64") and not isinstance(value, float) else None
+        elif op.op == "tensor_dim":
+            walker.add(Node(op.outputs[0], "constant", "index", attrs={"value": op.attrs["value"]}))
+            walker.sym[op.outputs[0]] = Sym(const=int(op.attrs["value"]))
+        elif op.op in ("load", "store", "masked_load", "masked_store"):
+            walker.access(op)
+        elif op.op in UNARY_OPS or op.op in BINARY_OPS or op.op == "select":
+            walker.scalar_arith(op)
+        else:
+            raise _unsupported(f"op '{op.op}' is not part of an elementwise load/op/store body")
+    return walker.finish_scalar()
+
+
+# ---------------------------------------------------------------------------------------------
+# tensor-SSA form
+# ---------------------------------------------------------------------------------------------
+def _match_ssa_elementwise(ir) -> ElementwisePlan:
+    positions = _argument_positions(ir)
+    nodes: list[Node] = []
+    known: dict[str, str] = {}  # SSA tensor/scalar name → node name holding its per-element value
+    shapes: dict[str, tuple[int, ...]] = {}
+    dtypes: dict[str, str] = {}
+    register_buffers: dict[str, dict[str, Any]] = {}
+    inputs: list[int] = []
+    stores: dict[int, str] = {}
+    shape: tuple[int, ...] | None = None
+
+    def element_shape(candidate: tuple[int, ...]) -> None:
+        nonlocal shape
+        if shape is None:
+            shape = tuple(candidate)
+        elif tuple(candidate) != shape:
+            raise _unsupported(f"tensor-SSA operands of different shapes ({shape} vs {tuple(candidate)}; broadcasting is not lowered yet)")
+
+    def global_tensor(name: str):
+        spec = ir.arguments[positions[name]].spec
+        if not spec.resolved_layout().is_row_major or spec.address_space.value != "global" or spec.dtype not in STORAGE_DTYPES:
+            raise _unsupported(f"tensor '{name}' must be a row-major global tensor of a supported dtype")
+        return spec
+
+    for argument in ir.arguments:
+        if argument.kind == "scalar":
+            nodes.append(Node(argument.name, "scalar_arg", argument.spec.dtype, attrs={"position": positions[argument.name]}))
+            known[argument.name] = argument.name
+            dtypes[argument.name] = argument.spec.dtype
+
+    for op in ir.operations:
+        if op.op == "make_tensor":
+            if op.attrs.get("address_space") != "register":
+                raise _unsupported("tensor-SSA bodies may only stage through register tensors")
+            register_buffers[op.outputs[0]] = op.attrs
+        elif op.op == "copy":
+            source, destination = op.inputs
+            if source in positions and ir.arguments[positions[source]].kind == "tensor":
+                spec = global_tensor(source)
+                element_shape(spec.shape)
+                if destination in positions:  # global → global copy
+                    node = f"{source}__elem"
+                    if positions[source] not in inputs:
+                        inputs.append(positions[source])
+                        nodes.append(Node(node, "input", spec.dtype, attrs={"tensor": positions[source]}))
+                    global_tensor(destination)
+                    stores[positions[destination]] = node
+                    continue
+                if destination not in register_buffers:
+                    raise _unsupported(f"copy into unknown tensor '{destination}'")
+                tensor_position = positions[source]
+                if tensor_position in stores:
+                    known[destination] = stores[tensor_position]  # reads observe the earlier whole-tensor store
+                else:
+                    node = f"{source}__elem"
+                    if tensor_position not in inputs:
+                        inputs.append(tensor_position)
+                        nodes.append(Node(node, "input", spec.dtype, attrs={"tensor": tensor_position}))
+                    known[destination] = node
+                dtypes[destination], shapes[destination] = spec.dtype, spec.shape
+            elif source in known:
+                if destination in positions:
+                    spec = global_tensor(destination)
+                    element_shape(spec.shape)
+                    if tuple(shapes.get(source, spec.shape)) != tuple(spec.shape):
+                        raise _unsupported("whole-tensor store of a value whose shape differs from the destination")
+                    stores[positions[destination]] = known[source]
+                elif destination in register_buffers:
+                    known[destination] = known[source]
+                    dtypes[destination], shapes[destination] = dtypes[source], shapes.get(source, ())
+                else:
+                    raise _unsupported(f"copy into unknown tensor '{destination}'")
+            else:
+                raise _unsupported(f"copy from unknown value '{source}'")
+        elif op.op == "constant":
+            dtype = op.attrs["result"]["dtype"]
+            nodes.append(Node(op.outputs[0], "constant", dtype, attrs={"value": op.attrs["value"]}))
+            known[op.outputs[0]] = op.outputs[0]
+            dtypes[op.outputs[0]] = dtype
+        elif op.op in TENSOR_OP_ALIASES or op.op in UNARY_OPS or op.op in BINARY_OPS or op.op == "select":
+            base = TENSOR_OP_ALIASES.get(op.op, op.op)
+            result = op.attrs["result"]
+            if result.get("kind") != "tensor":
+                raise _unsupported(f"scalar op '{op.op}' inside a tensor-SSA body")
+            element_shape(tuple(result["shape"]))
+            operands = []
+            for operand in op.inputs:
+                if operand not in known:
+                    raise _unsupported(f"op '{op.op}' consumes unknown value '{operand}'")
+                operands.append(known[operand])
+            nodes.append(Node(op.outputs[0], base, result["dtype"], tuple(operands),
+                              {k: v for k, v in op.attrs.items() if k != "result"}))
+            known[op.outputs[0]] = op.outputs[0]
+            dtypes[op.outputs[0]], shapes[op.outputs[0]] = result["dtype"], tuple(result["shape"])
+        else:
+            raise _unsupported(f"op '{op.op}' is not part of a tensor-SSA elementwise body")
+    if not stores or shape is None:
+        raise _unsupported("the kernel body stores nothing")
+    by_name = {node.name: node for node in nodes}
+    live = _live_set(by_name, list(stores.values()), lambda name: name)
+    extent = 1
+    for dim in shape:
+        extent *= dim
+    kept = tuple(node for node in nodes if node.name in live)
+    return ElementwisePlan(
+        mode="flat", nodes=kept, inputs=tuple(position for position in inputs if f"{ir.arguments[position].name}__elem" in live),
+        stores=tuple(stores.items()),
+        scalars=tuple(node.attrs["position"] for node in kept if node.op == "scalar_arg"), extent=extent,
+    )
+
+
+# ---------------------------------------------------------------------------------------------
+# entry point
+# ---------------------------------------------------------------------------------------------
+EXPLICIT = {"mma": _match_gemm, "rmsnorm": _match_rmsnorm, "attention": _match_attention}
+
+
+def match(ir):
+    """Classify ``ir`` (a ``PortableKernelIR`` from this package or from upstream) into a plan."""
+    operations = ir.operations
+    if not operations:
+        raise _unsupported("the kernel body is empty")
+    explicit = [op for op in operations if op.op in EXPLICIT]
+    if explicit:
+        if len(operations) != 1:
+            raise _unsupported(
+                f"'{explicit[0].op}' must be the only op of the kernel (found {len(operations)} ops); "
+                "fusing explicit ops with other work is not lowered"
+            )
+        return EXPLICIT[explicit[0].op](ir, explicit[0])
+    names = {op.op for op in operations}
+    if names & {"load", "store", "masked_load", "masked_store"}:
+        return _match_scalar_elementwise(ir)
+    if "copy" in names:
+        return _match_ssa_elementwise(ir)
+    raise _unsupported("no load/store or whole-tensor copy found; not an elementwise, gemm, rmsnorm or attention kernel")

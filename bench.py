@@ -1,0 +1,587 @@
+#!/usr/bin/env python3
+"""Benchmark of the b200 hot path.  Prints ONE JSON line (rank 0).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
+
+Workloads (``--workload``; default ``fused_mul_add``, the bandwidth config the headline metric is
+quoted on):
+
+    fused_mul_add   c = a*b + a, bf16, 2^28 elements per GPU          HBM GB/s   (6 B / element)
+    rmsnorm         bf16 [65536, 8192] per GPU, eps 1e-6               HBM GB/s   (4 B / element + weight)
+    gemm            C = A·B^T, bf16, M=N=K=8192 per GPU, bf16 out      TFLOP/s    (2·M·N·K)
+    attention       causal fwd, bf16, B16 H32 S4096 D128 per GPU      TFLOP/s    (4·B·H·D·S(S+1)/2)
+
+A step is one pass of the kernel over one batch of seeded synthetic input resident in HBM.  With
+N > 1 (launched under torchrun, one rank per GPU) every rank owns an equal shard of an N-times
+larger problem (weak scaling, no data-path collective); the NCCL all-gather of the output shards
+is timed separately and reported under ``allgather``.  Timing: CUDA events on the launching
+stream, bracketed by barrier + synchronize, max over ranks.  The working sets (1.6 GB / 2.1 GB /
+0.4 GB / 2.1 GB) exceed the 126 MB L2 except for GEMM, whose timed loop flushes L2 between steps
+outside the event pairs.
+
+``--impl reference`` times the CPU port of upstream's reference runtime (``oracle/``) on a bounded
+sample of the same workload, on rank 0 only.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import math
+import os
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+for entry in (str(ROOT), str(ROOT / "tests")):
+    if entry not in sys.path:
+        sys.path.insert(0, entry)
+
+L2_FLUSH_BYTES = 256 << 20
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def load_peaks() -> tuple[dict, str]:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        try:
+            return json.loads(path.read_text()), "measured"
+        except ValueError:
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+# ---------------------------------------------------------------------------------------------
+# clocks: sampled through NVML while the timed region runs (read-only queries)
+# ---------------------------------------------------------------------------------------------
+class ClockSampler:
+    REASONS = {
+        0x1: "gpu_idle", 0x2: "applications_clocks_setting", 0x4: "sw_power_cap", 0x8: "hw_slowdown",
+        0x10: "sync_boost", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown", 0x80: "hw_power_brake_slowdown",
+        0x100: "display_clock_setting",
+    }
+
+    def __init__(self, device_index: int, period_s: float = 0.004):
+        self.samples: list[tuple[int, int, int]] = []
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        self._period = period_s
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            physical = device_index
+            if visible:
+                entries = [item.strip() for item in visible.split(",") if item.strip()]
+                if device_index < len(entries) and entries[device_index].isdigit():
+                    physical = int(entries[device_index])
+            self._nvml = pynvml
+            self._handle = pynvml.nvmlDeviceGetHandleByIndex(physical)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self._handle, pynvml.NVML_CLOCK_SM))
+        except Exception:  # NVML missing: the line reports clocks as unavailable
+            self._nvml = None
+
+    def _loop(self) -> None:
+        nvml = self._nvml
+        while not self._stop.is_set():
+            try:
+                mhz = int(nvml.nvmlDeviceGetClockInfo(self._handle, nvml.NVML_CLOCK_SM))
+                reasons = int(nvml.nvmlDeviceGetCurrentClocksEventReasons(self._handle))
+                util = int(nvml.nvmlDeviceGetUtilizationRates(self._handle).gpu)
+                self.samples.append((mhz, reasons, util))
+            except Exception:
+                pass
+            self._stop.wait(self._period)
+
+    def __enter__(self):
+        if self._nvml is not None:
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join(timeout=2)
+
+    def summary(self) -> dict:
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0}
+        clocks = sorted(sample[0] for sample in self.samples)
+        mask = 0
+        for _, reasons, _ in self.samples:
+            mask |= reasons
+        names = sorted(name for bit, name in self.REASONS.items() if mask & bit and name != "gpu_idle")
+        return {"sm_mhz": clocks[len(clocks) // 2], "sm_max_mhz": self.max_mhz, "reasons": names, "samples": len(clocks)}
+
+
+# ---------------------------------------------------------------------------------------------
+# workloads
+# ---------------------------------------------------------------------------------------------
+class Workload:
+    name = ""
+    unit = ""
+    dtype = "bf16"
+    bound = "hbm"
+    needs_l2_flush = False
+
+    def work_per_step(self) -> float:  # algorithmic bytes (hbm) or flops (tensor) one rank processes per step
+        raise NotImplementedError
+
+    def setup(self, torch, cute, zoo, rank: int, cache_dir: str) -> None:
+        raise NotImplementedError
+
+    def step(self) -> None:
+        raise NotImplementedError
+
+    def output(self):
+        raise NotImplementedError
+
+    def e2e_step(self, torch) -> None:
+        raise NotImplementedError
+
+    def config(self) -> dict:
+        raise NotImplementedError
+
+
+class FusedMulAdd(Workload):
+    name, unit, bound = "fused_mul_add", "GB/s", "hbm"
+    n = 2**28
+
+    def work_per_step(self) -> float:
+        return 6.0 * self.n  # read a, read b, write c at 2 B each
+
+    def setup(self, torch, cute, zoo, rank, cache_dir):
+        generator = torch.Generator(device="cuda").manual_seed(1002 + rank)
+        self.a = torch.randn(self.n, device="cuda", dtype=torch.float32, generator=generator).to(torch.bfloat16)
+        self.b = torch.randn(self.n, device="cuda", dtype=torch.float32, generator=generator).to(torch.bfloat16)
+        self.c = torch.empty_like(self.a)
+        from baybridge_b200 import B200Backend
+
+        self.artifact = cute.compile(zoo.make_fused_mul_add_indexed(self.n), self.a, self.b, self.c,
+                                     backend=B200Backend(synchronize=False), cache_dir=cache_dir)
+        self.args = tuple(cute.from_dlpack(t) for t in (self.a, self.b, self.c))
+        self.stream = torch.cuda.current_stream().cuda_stream
+        self.a_host = self.a.cpu().pin_memory()
+        self.b_host = self.b.cpu().pin_memory()
+        self.c_host = torch.empty_like(self.a_host).pin_memory()
+        self.h2d_bytes = 2 * self.n * 2
+        self.d2h_bytes = self.n * 2
+
+    def step(self):
+        self.artifact(*self.args, stream=self.stream)
+
+    def output(self):
+        return self.c
+
+    def e2e_step(self, torch):
+        self.a.copy_(self.a_host, non_blocking=True)
+        self.b.copy_(self.b_host, non_blocking=True)
+        self.artifact(*self.args, stream=self.stream)
+        self.c_host.copy_(self.c, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    def config(self):
+        return {"workload": "fused_mul_add c=a*b+a bf16 2^28 elements per GPU (6 B/element), indexed IR form",
+                "l2": "working set 1.6 GB > 126 MB L2, no flush"}
+
+    # CPU port leg -------------------------------------------------------------------------------
+    sample_n = 2**24
+
+    def cpu_sample(self):
+        rng = np.random.default_rng(1002)
+        from oracle import cpu_runtime as oracle
+
+        a = oracle.bf16_round(rng.standard_normal(self.sample_n, dtype=np.float32)).astype(np.float64)
+        b = oracle.bf16_round(rng.standard_normal(self.sample_n, dtype=np.float32)).astype(np.float64)
+        ir = {
+            "launch": {"grid": [1, 1, 1], "block": [1, 1, 1]},
+            "arguments": [{"name": n, "kind": "tensor"} for n in "abc"],
+            "operations": [
+                {"op": "make_tensor", "inputs": [], "outputs": ["a_load_1"], "attrs": {"shape": [self.sample_n]}},
+                {"op": "copy", "inputs": ["a", "a_load_1"], "outputs": [], "attrs": {}},
+                {"op": "make_tensor", "inputs": [], "outputs": ["b_load_2"], "attrs": {"shape": [self.sample_n]}},
+                {"op": "copy", "inputs": ["b", "b_load_2"], "outputs": [], "attrs": {}},
+                {"op": "tensor_mul", "inputs": ["a_load_1", "b_load_2"], "outputs": ["t3"], "attrs": {}},
+                {"op": "tensor_add", "inputs": ["t3", "a_load_1"], "outputs": ["t4"], "attrs": {}},
+                {"op": "copy", "inputs": ["t4", "c"], "outputs": [], "attrs": {}},
+            ],
+        }
+        arguments = {"a": a, "b": b, "c": np.zeros(self.sample_n)}
+        return (lambda: oracle.run_kernel_ir(ir, arguments)), 6.0 * self.sample_n, f"{self.sample_n} of {self.n} elements, numpy f64 port of the tensor-SSA CPU runtime path"
+
+
+class RmsNorm(Workload):
+    name, unit, bound = "rmsnorm", "GB/s", "hbm"
+    rows, hidden = 65536, 8192
+
+    def work_per_step(self) -> float:
+        return 2.0 * self.rows * self.hidden * 2 + self.hidden * 2
+
+    def setup(self, torch, cute, zoo, rank, cache_dir):
+        generator = torch.Generator(device="cuda").manual_seed(1004 + rank)
+        self.x = torch.randn((self.rows, self.hidden), device="cuda", dtype=torch.float32, generator=generator).to(torch.bfloat16)
+        self.w = (1 + 0.1 * torch.randn((self.hidden,), device="cuda", dtype=torch.float32, generator=generator)).to(torch.bfloat16)
+        self.out = torch.empty_like(self.x)
+        from baybridge_b200 import B200Backend
+
+        self.artifact = cute.compile(zoo.make_rmsnorm(1e-6), self.x, self.out, self.w,
+                                     backend=B200Backend(synchronize=False), cache_dir=cache_dir)
+        self.args = tuple(cute.from_dlpack(t) for t in (self.x, self.out, self.w))
+        self.stream = torch.cuda.current_stream().cuda_stream
+        self.x_host = self.x.cpu().pin_memory()
+        self.out_host = torch.empty_like(self.x_host).pin_memory()
+        self.h2d_bytes = self.rows * self.hidden * 2
+        self.d2h_bytes = self.rows * self.hidden * 2
+
+    def step(self):
+        self.artifact(*self.args, stream=self.stream)
+
+    def output(self):
+        return self.out
+
+    def e2e_step(self, torch):
+        self.x.copy_(self.x_host, non_blocking=True)
+        self.artifact(*self.args, stream=self.stream)
+        self.out_host.copy_(self.out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    def config(self):
+        return {"workload": "rmsnorm bf16 [65536, 8192] per GPU, weight [8192], eps 1e-6",
+                "l2": "working set 2.1 GB > 126 MB L2, no flush"}
+
+    def cpu_sample(self):
+        from oracle import cpu_runtime as oracle
+
+        rng = np.random.default_rng(1004)
+        rows = 512
+        x = oracle.bf16_round(rng.standard_normal((rows, self.hidden), dtype=np.float32)).astype(np.float64)
+        w = oracle.bf16_round((1 + 0.1 * rng.standard_normal(self.hidden)).astype(np.float32)).astype(np.float64)
+        return (lambda: oracle.rmsnorm(x, w, 1e-6)), 2.0 * rows * self.hidden * 2 + self.hidden * 2, f"{rows} of {self.rows} rows, numpy f64 port"
+
+
+class Gemm(Workload):
+    name, unit, bound = "gemm", "TFLOP/s", "tensor"
+    m = n = k = 8192
+    needs_l2_flush = True
+
+    def work_per_step(self) -> float:
+        return 2.0 * self.m * self.n * self.k
+
+    def setup(self, torch, cute, zoo, rank, cache_dir):
+        generator = torch.Generator(device="cuda").manual_seed(1003 + rank)
+        scale = 1.0 / math.sqrt(self.k)
+        self.a = (torch.randn((self.m, self.k), device="cuda", dtype=torch.float32, generator=generator) * scale).to(torch.bfloat16)
+        self.b = (torch.randn((self.n, self.k), device="cuda", dtype=torch.float32, generator=generator) * scale).to(torch.bfloat16)
+        self.c = torch.empty((self.m, self.n), device="cuda", dtype=torch.bfloat16)
+        from baybridge_b200 import B200Backend
+
+        self.artifact = cute.compile(zoo.gemm_abt, self.a, self.b, self.c, backend=B200Backend(synchronize=False), cache_dir=cache_dir)
+        self.args = tuple(cute.from_dlpack(t) for t in (self.a, self.b, self.c))
+        self.stream = torch.cuda.current_stream().cuda_stream
+        self.a_host = self.a.cpu().pin_memory()
+        self.b_host = self.b.cpu().pin_memory()
+        self.c_host = torch.empty((self.m, self.n), dtype=torch.bfloat16).pin_memory()
+        self.h2d_bytes = (self.m * self.k + self.n * self.k) * 2
+        self.d2h_bytes = self.m * self.n * 2
+
+    def step(self):
+        self.artifact(*self.args, stream=self.stream)
+
+    def output(self):
+        return self.c
+
+    def e2e_step(self, torch):
+        self.a.copy_(self.a_host, non_blocking=True)
+        self.b.copy_(self.b_host, non_blocking=True)
+        self.artifact(*self.args, stream=self.stream)
+        self.c_host.copy_(self.c, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    def config(self):
+        return {"workload": "gemm C=A·B^T bf16 M=N=K=8192 per GPU, fp32 accumulate, bf16 out",
+                "l2": "384 MB working set; 256 MB L2 flush write between timed steps (outside the event pairs)"}
+
+    def cpu_sample(self):
+        from oracle import cpu_runtime as oracle
+
+        rng = np.random.default_rng(1003)
+        size = 2048
+        a = oracle.bf16_round((rng.standard_normal((size, size)) / math.sqrt(size)).astype(np.float32)).astype(np.float64)
+        b = oracle.bf16_round((rng.standard_normal((size, size)) / math.sqrt(size)).astype(np.float32)).astype(np.float64)
+        return (lambda: oracle.gemm(a, b, transpose_b=True)), 2.0 * size**3, f"M=N=K={size} (of 8192), numpy f64 BLAS port"
+
+
+class Attention(Workload):
+    name, unit, bound = "attention", "TFLOP/s", "tensor"
+    batch, heads, seq, dim = 16, 32, 4096, 128
+
+    def work_per_step(self) -> float:
+        return 4.0 * self.batch * self.heads * self.dim * self.seq * (self.seq + 1) / 2
+
+    def setup(self, torch, cute, zoo, rank, cache_dir):
+        generator = torch.Generator(device="cuda").manual_seed(1005 + rank)
+        shape = (self.batch, self.seq, self.heads, self.dim)
+        self.q, self.k, self.v = (torch.randn(shape, device="cuda", dtype=torch.float32, generator=generator).to(torch.bfloat16) for _ in range(3))
+        self.o = torch.empty_like(self.q)
+        self.lse = torch.empty((self.batch, self.heads, 1, self.seq), device="cuda", dtype=torch.float32)
+        from baybridge_b200 import B200Backend
+
+        self.artifact = cute.compile(zoo.attention_causal, self.q, self.k, self.v, self.o, self.lse,
+                                     backend=B200Backend(synchronize=False), cache_dir=cache_dir)
+        self.args = tuple(cute.from_dlpack(t) for t in (self.q, self.k, self.v, self.o, self.lse))
+        self.stream = torch.cuda.current_stream().cuda_stream
+        self.hosts = [t.cpu().pin_memory() for t in (self.q, self.k, self.v)]
+        self.o_host = torch.empty_like(self.hosts[0]).pin_memory()
+        self.h2d_bytes = 3 * self.q.numel() * 2
+        self.d2h_bytes = self.q.numel() * 2
+
+    def step(self):
+        self.artifact(*self.args, stream=self.stream)
+
+    def output(self):
+        return self.o
+
+    def e2e_step(self, torch):
+        for device, host in zip((self.q, self.k, self.v), self.hosts):
+            device.copy_(host, non_blocking=True)
+        self.artifact(*self.args, stream=self.stream)
+        self.o_host.copy_(self.o, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    def config(self):
+        return {"workload": "causal attention fwd bf16 B16 H32 S4096 D128 per GPU (layout [B,S,H,D]), causal FLOPs",
+                "l2": "working set 2.1 GB > 126 MB L2, no flush"}
+
+    def cpu_sample(self):
+        from oracle import cpu_runtime as oracle
+
+        rng = np.random.default_rng(1005)
+        bsz, seq, heads = 1, 1024, 4
+        q, k, v = (oracle.bf16_round(rng.standard_normal((bsz, seq, heads, self.dim), dtype=np.float32)).astype(np.float64) for _ in range(3))
+        flops = 4.0 * bsz * heads * self.dim * seq * (seq + 1) / 2
+        return (lambda: oracle.attention(q, k, v, causal=True)), flops, f"B{bsz} H{heads} S{seq} D{self.dim}, numpy f64 port"
+
+
+WORKLOADS = {cls.name: cls for cls in (FusedMulAdd, RmsNorm, Gemm, Attention)}
+METRIC = {
+    "fused_mul_add": "elementwise HBM GB/s (fused c=a*b+a, bf16)", "rmsnorm": "RMSNorm HBM GB/s (bf16)",
+    "gemm": "BF16 GEMM TFLOP/s", "attention": "causal attention forward TFLOP/s (bf16)",
+}
+
+
+# ---------------------------------------------------------------------------------------------
+# CPU legs
+# ---------------------------------------------------------------------------------------------
+def time_cpu(workload: Workload, budget_s: float = 10.0, min_runs: int = 2) -> dict:
+    run, work, sample = workload.cpu_sample()
+    run()  # warm-up
+    durations = []
+    started = time.perf_counter()
+    while len(durations) < min_runs or (time.perf_counter() - started < budget_s and len(durations) < 50):
+        t0 = time.perf_counter()
+        run()
+        durations.append(time.perf_counter() - t0)
+    median = sorted(durations)[len(durations) // 2]
+    scale = 1e9 if workload.unit == "GB/s" else 1e12
+    threads = 1 if workload.name in ("fused_mul_add", "rmsnorm") else (os.cpu_count() or 1)
+    return {"value": work / median / scale, "unit": workload.unit, "cores": threads, "kind": "port",
+            "sample": sample, "seconds_per_sample": median, "runs": len(durations)}
+
+
+def reference_arm(args, workload: Workload) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    run, work, sample = workload.cpu_sample()
+    for _ in range(min(args.warmup, 2)):
+        run()
+    steps = max(1, min(args.steps, 20))
+    started = time.perf_counter()
+    for _ in range(steps):
+        run()
+    elapsed = time.perf_counter() - started
+    scale = 1e9 if workload.unit == "GB/s" else 1e12
+    value = work * steps / elapsed / scale
+    threads = 1 if workload.name in ("fused_mul_add", "rmsnorm") else (os.cpu_count() or 1)
+    line = {
+        "impl": "reference", "metric": METRIC[workload.name], "value": value, "unit": workload.unit,
+        "n_gpus": args.gpus, "steps": steps, "warmup": min(args.warmup, 2), "ms_per_step": elapsed / steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f64 (CPU runtime arithmetic)",
+        "data": "synthetic", "config": workload.config(),
+        "cpu_baseline": {"value": value, "unit": workload.unit, "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": workload.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------------------------
+def main() -> None:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=50)
+    parser.add_argument("--warmup", type=int, default=5)
+    parser.add_argument("--workload", default="fused_mul_add", choices=sorted(WORKLOADS))
+    parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--e2e-steps", type=int, default=3)
+    args = parser.parse_args()
+    workload = WORKLOADS[args.workload]()
+    if args.impl == "reference":
+        reference_arm(args, workload)
+        return
+
+    import torch
+
+    import baybridge_b200 as cute
+    from baybridge_b200.backend import b200 as backend_module
+    from baybridge_b200.backend import native
+    from kernel_zoo import build_zoo
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; the b200 backend has no CPU path")
+    torch.cuda.set_device(local_rank)
+    distributed = world > 1
+    if distributed:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    warmup = max(args.warmup, 3)
+    steps = max(args.steps, 1)
+    zoo = build_zoo(cute)
+    cache_dir = str(ROOT / "gpurun_out" / f"bench_cache_rank{rank}")
+    workload.setup(torch, cute, zoo, rank, cache_dir)
+    flush = torch.empty(L2_FLUSH_BYTES, device="cuda", dtype=torch.uint8) if workload.needs_l2_flush else None
+
+    def barrier() -> None:
+        if distributed:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(warmup):
+        workload.step()
+    barrier()
+
+    peaks, peak_source = load_peaks()
+    launches_before = backend_module.LAUNCH_COUNTER["launches"]
+    with ClockSampler(local_rank) as sampler:
+        if flush is None:
+            # back-to-back launches, one event pair around the K steps
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            barrier()
+            start.record()
+            for _ in range(steps):
+                workload.step()
+            stop.record()
+            barrier()
+            total_ms = start.elapsed_time(stop)
+        else:
+            # an event pair per step so the L2 flush between steps is not timed
+            pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+            barrier()
+            for begin, end in pairs:
+                flush.fill_(1)
+                begin.record()
+                workload.step()
+                end.record()
+            barrier()
+            total_ms = sum(begin.elapsed_time(end) for begin, end in pairs)
+        launches = backend_module.LAUNCH_COUNTER["launches"] - launches_before
+        # keep the device busy a little longer so NVML has samples under this load even when K is small
+        deadline = time.perf_counter() + 0.25
+        while time.perf_counter() < deadline:
+            for _ in range(10):
+                workload.step()
+            torch.cuda.synchronize()
+    clocks = sampler.summary()
+
+    if distributed:
+        slowest = torch.tensor([total_ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(slowest, op=dist.ReduceOp.MAX)
+        total_ms = float(slowest.item())
+    ms_per_step = total_ms / steps
+    scale = 1e9 if workload.unit == "GB/s" else 1e12
+    per_rank = workload.work_per_step() / (ms_per_step * 1e-3) / scale
+    value = per_rank * world
+
+    # end to end: pinned host inputs → device, kernel through the public artifact call, result → host
+    for _ in range(2):
+        workload.e2e_step(torch)
+    barrier()
+    e2e_started = time.perf_counter()
+    for _ in range(args.e2e_steps):
+        workload.e2e_step(torch)
+    e2e_seconds = (time.perf_counter() - e2e_started) / args.e2e_steps
+    if distributed:
+        worst = torch.tensor([e2e_seconds], device="cuda", dtype=torch.float64)
+        dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+        e2e_seconds = float(worst.item())
+    e2e_value = workload.work_per_step() * world / e2e_seconds / scale
+
+    allgather = None
+    if distributed:
+        out = workload.output()
+        gathered = torch.empty((world,) + tuple(out.shape), device="cuda", dtype=out.dtype)
+        for _ in range(2):
+            dist.all_gather_into_tensor(gathered, out)
+        barrier()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        reps = 5
+        for _ in range(reps):
+            dist.all_gather_into_tensor(gathered, out)
+        end.record()
+        barrier()
+        gather_ms = torch.tensor([begin.elapsed_time(end) / reps], device="cuda", dtype=torch.float64)
+        dist.all_reduce(gather_ms, op=dist.ReduceOp.MAX)
+        total_bytes = out.numel() * out.element_size() * world
+        allgather = {"ms": float(gather_ms.item()), "output_bytes_total": total_bytes,
+                     "bus_gbs": total_bytes * (world - 1) / world / (float(gather_ms.item()) * 1e-3) / 1e9,
+                     "kernel_plus_allgather_ms": ms_per_step + float(gather_ms.item())}
+
+    if rank == 0:
+        if workload.bound == "hbm":
+            peak, peak_unit = float(peaks["hbm_gbs"]), "GB/s"
+        else:
+            peak, peak_unit = float(peaks["bf16_tflops"]), "TFLOP/s"
+        roofline = {
+            "bound": workload.bound, "achieved": per_rank, "peak": peak, "unit": peak_unit, "frac": per_rank / peak,
+            "peak_source": f"{peak_source} ({'hbm_gbs' if workload.bound == 'hbm' else 'bf16_tflops burst'})",
+            "traffic": None, "kernel_ms": ms_per_step,
+        }
+        line = {
+            "metric": METRIC[workload.name], "value": value, "unit": workload.unit, "n_gpus": world, "steps": steps,
+            "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": workload.dtype, "data": "synthetic", "config": workload.config(),
+            "roofline": roofline, "clocks": clocks,
+            "e2e": {"value": e2e_value, "unit": workload.unit, "h2d_bytes_per_step": workload.h2d_bytes,
+                    "d2h_bytes_per_step": workload.d2h_bytes, "ms_per_step": e2e_seconds * 1e3},
+            "gpu_launches": launches,
+        }
+        if allgather is not None:
+            line["allgather"] = allgather
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = time_cpu(workload)
+        info = native.DeviceInfo()
+        if native.library().bb200_device_info_get(local_rank, ctypes.byref(info)) == 0:
+            line["device"] = {"name": info.name.decode(), "sm_count": info.sm_count}
+        print(json.dumps(line), flush=True)
+    if distributed:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

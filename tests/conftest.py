@@ -1,0 +1,40 @@
+"""Shared fixtures.  ``gpu``-marked tests need a B200 and the built CUDA library; everything else runs on CPU."""
+from __future__ import annotations
+
+import json
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+GOLDEN = ROOT / "tests" / "golden"
+for entry in (str(ROOT), str(ROOT / "tests")):
+    if entry not in sys.path:
+        sys.path.insert(0, entry)
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (B200) and the built libbb200.so")
+
+
+def golden_ir(case: str) -> dict:
+    return json.loads((GOLDEN / f"ir_{case}.json").read_text())
+
+
+def golden_vec(case: str) -> dict[str, np.ndarray]:
+    with np.load(GOLDEN / f"vec_{case}.npz") as blob:
+        return {name: blob[name] for name in blob.files}
+
+
+def golden_cases(prefix: str = "") -> list[str]:
+    return sorted(path.stem[len("vec_"):] for path in GOLDEN.glob(f"vec_{prefix}*.npz"))
+
+
+@pytest.fixture(scope="session")
+def zoo():
+    import baybridge_b200 as cute
+    from kernel_zoo import build_zoo
+
+    return build_zoo(cute)

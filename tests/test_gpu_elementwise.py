@@ -1,0 +1,184 @@
+"""GPU parity for the elementwise path: compile(..., backend="b200") and the C ABI vs the CPU oracle/golden vectors."""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+from conftest import golden_cases, golden_ir, golden_vec
+from gpu_util import current_stream, device_zeros, expect_rounded, to_device, to_host, void_p
+
+from oracle import cpu_runtime as oracle
+
+pytestmark = pytest.mark.gpu
+
+EXACT_OPS = {"add", "sub", "mul", "div", "max", "min", "neg", "abs", "copy", "sqrt", "floor", "ceil", "trunc"}
+
+
+def _kernel_for(case: str, zoo):
+    parts = case.split("_")
+    if case.startswith("bin_"):
+        return zoo.make_indexed_binary(parts[1], int(parts[2])), parts[1]
+    if case.startswith("un_"):
+        return zoo.make_indexed_unary(parts[1], int(parts[2])), parts[1]
+    if case.startswith("clamp_scale"):
+        return zoo.make_indexed_clamp_scale(512), "mul"
+    if case.startswith("masked_add"):
+        return zoo.make_indexed_masked_add(1000), "add"
+    if case.startswith("ssa_"):
+        return getattr(zoo, "_".join(parts[:-2])), "exp" if "exp" in case else "mul"
+    if case.startswith("c2_fused_indexed"):
+        return zoo.make_fused_mul_add_indexed(int(parts[3])), "fma"
+    if case.startswith("c2_fused_ssa"):
+        return zoo.fused_mul_add_ssa, "fma"
+    raise KeyError(case)
+
+
+ELEMENTWISE_CASES = [c for c in golden_cases() if c.startswith(("bin_", "un_", "clamp_", "masked_", "ssa_", "c2_"))]
+
+
+@pytest.mark.parametrize("case", ELEMENTWISE_CASES)
+def test_compiled_elementwise_matches_upstream_vectors(case: str, zoo, tmp_path):
+    import baybridge_b200 as cute
+
+    ir = golden_ir(case)["ir"]
+    vec = golden_vec(case)
+    kernel, op = _kernel_for(case, zoo)
+    args = []
+    outputs = {}
+    for argument in ir["arguments"]:
+        name, spec = argument["name"], argument["spec"]
+        if argument["kind"] == "scalar":
+            args.append(0.75)
+        elif f"in_{name}" in vec:
+            args.append(to_device(vec[f"in_{name}"], spec["dtype"]))
+        else:
+            outputs[name] = device_zeros(spec["shape"], spec["dtype"])
+            args.append(outputs[name])
+    artifact = cute.compile(kernel, *args, backend="b200", cache_dir=tmp_path)
+    assert json_equal(artifact.ir.to_dict(), ir)
+    artifact(*args)
+    for name, tensor in outputs.items():
+        dtype = next(a["spec"]["dtype"] for a in ir["arguments"] if a["name"] == name)
+        # arithmetic is bit-exact against the f64 reference rounded once; libm-style functions may differ
+        # from CPython's libm by one unit in the last place of the storage type
+        expect_rounded(to_host(tensor), vec[f"out_{name}"], dtype, max_ulp=0 if op in EXACT_OPS or op == "fma" and dtype == "f32" else 1)
+
+
+def json_equal(mine: dict, theirs: dict) -> bool:
+    import json
+
+    return json.loads(json.dumps(mine)) == theirs
+
+
+def test_config1_indexed_add_256x256_is_bit_exact(zoo, tmp_path):
+    import baybridge_b200 as cute
+
+    rng = np.random.default_rng(1001)
+    a = rng.uniform(-1, 1, (256, 256)).astype(np.float32)
+    b = rng.uniform(-1, 1, (256, 256)).astype(np.float32)
+    g_a, g_b, g_c = to_device(a, "f32"), to_device(b, "f32"), device_zeros((256, 256), "f32")
+    artifact = cute.compile(zoo.make_indexed_add_2d(256, 256), g_a, g_b, g_c, backend="b200", cache_dir=tmp_path)
+    artifact(g_a, g_b, g_c)
+    golden = golden_vec("c1_indexed_add_256x256_f32")["out_g_c"]
+    assert np.array_equal(g_c.cpu().numpy(), golden)  # upstream CPU runtime output, bit for bit
+    # eager launch path: kernel(...).launch(...) outside a trace compiles for b200 and runs on the device
+    g_c.zero_()
+    zoo.make_indexed_add_2d(256, 256)(g_a, g_b, g_c)
+    assert np.array_equal(g_c.cpu().numpy(), golden)
+
+
+@pytest.mark.parametrize("form", ["indexed", "ssa"])
+def test_config2_full_size_fused_mul_add(form: str, zoo, tmp_path):
+    """2^28 bf16 elements through compile(); checked chunk by chunk against the f64 oracle.
+
+    Tolerance: RNE(f64 reference) within 1 bf16 ulp (f32 intermediates can double-round) and rel-L2 <= 2e-3."""
+    import torch
+
+    import baybridge_b200 as cute
+
+    n = 2**28
+    rng = np.random.default_rng(1002)
+    a_host = oracle.bf16_round(rng.standard_normal(n, dtype=np.float32))
+    b_host = oracle.bf16_round(rng.standard_normal(n, dtype=np.float32))
+    a, b = to_device(a_host, "bf16"), to_device(b_host, "bf16")
+    c = device_zeros((n,), "bf16")
+    kernel = zoo.make_fused_mul_add_indexed(n) if form == "indexed" else zoo.fused_mul_add_ssa
+    artifact = cute.compile(kernel, a, b, c, backend="b200", cache_dir=tmp_path)
+    artifact(a, b, c)
+    got = c.to(torch.float32).cpu().numpy()
+    chunk = 2**24
+    worst, err2, ref2, exact = 0, 0.0, 0.0, 0
+    for start in range(0, n, chunk):
+        av = a_host[start:start + chunk].astype(np.float64)
+        bv = b_host[start:start + chunk].astype(np.float64)
+        reference = av * bv + av
+        expected = oracle.round_to_dtype(reference, "bf16")
+        piece = got[start:start + chunk].astype(np.float64)
+        from gpu_util import ulp_distance
+
+        distance = ulp_distance(piece, expected, "bf16")
+        worst = max(worst, int(distance.max()))
+        exact += int(np.count_nonzero(distance == 0))
+        err2 += float(np.sum((piece - reference) ** 2))
+        ref2 += float(np.sum(reference**2))
+    assert worst <= 1, f"worst error {worst} bf16 ulp"
+    assert exact / n > 0.999
+    assert (err2 / ref2) ** 0.5 <= 2e-3
+
+
+@pytest.mark.parametrize("dtype,n", [("f32", 1_000_003), ("bf16", 999_999), ("f16", 12_345), ("bf16", 7), ("f32", 1)])
+def test_c_abi_binary_and_mul_add_ragged_sizes(dtype: str, n: int):
+    """Sizes that are not multiples of the vector width or tile, through the C ABI directly."""
+    from baybridge_b200.backend import native
+
+    rng = np.random.default_rng(n)
+    x = oracle.round_to_dtype(rng.uniform(0.5, 2.0, n), dtype)
+    y = oracle.round_to_dtype(rng.uniform(0.5, 2.0, n), dtype)
+    a, b, c = to_device(x, dtype), to_device(y, dtype), device_zeros((n,), dtype)
+    code = native.DTYPE_CODES[dtype]
+    reference = {"add": x + y, "sub": x - y, "mul": x * y, "div": x / y, "max": np.maximum(x, y), "min": np.minimum(x, y)}
+    for op, expected in reference.items():
+        c.zero_()
+        native.call("bb200_elementwise_binary", native.BINARY_OP_CODES[op], code, void_p(a), void_p(b), void_p(c), n, current_stream())
+        expect_rounded(to_host(c), expected, dtype)
+    c.zero_()
+    native.call("bb200_elementwise_mul_add", code, void_p(a), void_p(b), void_p(c), n, current_stream())
+    expect_rounded(to_host(c), x * y + x, dtype, max_ulp=0 if dtype == "f32" else 1)
+
+
+def test_c_abi_unaligned_pointers_take_the_scalar_path():
+    from baybridge_b200.backend import native
+
+    n = 4099
+    rng = np.random.default_rng(5)
+    x = rng.uniform(-1, 1, n + 1).astype(np.float32)
+    y = rng.uniform(-1, 1, n + 1).astype(np.float32)
+    a, b, c = to_device(x, "f32"), to_device(y, "f32"), device_zeros((n + 1,), "f32")
+    # views that start 4 bytes into the allocation: not 16-byte aligned
+    native.call("bb200_elementwise_binary", 0, 0, void_p(a[1:]), void_p(b[1:]), void_p(c[1:]), n, current_stream())
+    out = c.cpu().numpy()
+    assert out[0] == 0.0 and np.array_equal(out[1:], x[1:] + y[1:])
+
+
+def test_c_abi_rejects_bad_arguments():
+    from baybridge_b200 import CudaDriverError
+    from baybridge_b200.backend import native
+
+    a = device_zeros((16,), "f32")
+    with pytest.raises(CudaDriverError) as info:
+        native.call("bb200_elementwise_binary", 99, 0, void_p(a), void_p(a), void_p(a), 16, current_stream())
+    assert info.value.status == -1
+    with pytest.raises(CudaDriverError):
+        native.call("bb200_elementwise_binary", 0, 0, None, void_p(a), void_p(a), 16, current_stream())
+    native.call("bb200_elementwise_binary", 0, 0, void_p(a), void_p(a), void_p(a), 0, current_stream())  # empty is a no-op
+
+
+def test_runtime_tensor_arguments_are_staged_and_copied_back(zoo, tmp_path):
+    import baybridge_b200 as cute
+
+    a = cute.tensor([float(i) for i in range(128)], dtype="f32")
+    b = cute.tensor([float(i * 2) for i in range(128)], dtype="f32")
+    c = cute.zeros((128,), dtype="f32")
+    artifact = cute.compile(zoo.make_indexed_binary("add", 128), a, b, c, backend="b200", cache_dir=tmp_path)
+    with pytest.warns(RuntimeWarning, match="staging"):
+        artifact(a, b, c)
+    assert c.tolist() == [x + y for x, y in zip(a.tolist(), b.tolist())]  # upstream tests/test_backend_ptx_exec.py:2660-2677
