@@ -1,5 +1,330 @@
+// gemm_tcgen05.cu — BF16 GEMM for sm_100a: C[m,n] = sum_k A'[m,k] * B'[k,n], fp32 accumulate.
+//
+// Native form: A is [M,K] and B is [N,K], both row-major (K contiguous) — "A · B^T", the layout
+// tcgen05 consumes directly.  Other transpose combinations are brought to that form by a tiled
+// transpose into a stream-ordered workspace.
+//
+// Kernel structure (one persistent CTA per SM, 192 threads):
+//   warp 0      TMA producer: streams 128x64 A tiles and 256x64 B tiles (128-byte swizzle) into a
+//               4-stage shared-memory ring, signalling `full[stage]` by transaction bytes.
+//   warp 1      MMA issuer: one elected thread issues tcgen05.mma (M128 x N256 x K16, both operands
+//               from shared memory) into one of two 256-column TMEM accumulators; tcgen05.commit
+//               releases ring stages (`empty[stage]`) and publishes finished tiles (`acc_full`).
+//   warps 2..5  epilogue: tcgen05.ld the fp32 accumulator (each warp owns its 32-lane TMEM
+//               quadrant), convert, store C; `acc_empty` hands the accumulator back so the next
+//               tile's main loop overlaps this tile's epilogue.
+// Tensor-core bound: 2*M*N*K flops; per k-block a CTA moves 48 KB of operands for 4.2 MFLOP, so
+// operand traffic is served from L2 (tiles are rasterised in groups of 8 M-blocks) and HBM sees
+// each operand only a few times.
+#include <cuda_bf16.h>
+
 #include "bb200_internal.h"
+#include "bb200_sm100.cuh"
+
+namespace bb200 {
+namespace {
+
+using namespace sm100;
+
+constexpr int BM = 128, BN = 256, BK = 64;
+constexpr int STAGES = 4;
+constexpr int UMMA_K = 16;
+constexpr int A_TILE_BYTES = BM * BK * 2;  // 16 KB
+constexpr int B_TILE_BYTES = BN * BK * 2;  // 32 KB
+constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
+constexpr int ACC_COLUMNS = BN;            // fp32 accumulator: 128 lanes x 256 columns
+constexpr int TMEM_COLUMNS = 2 * ACC_COLUMNS;
+constexpr int THREADS = 192;
+constexpr int GROUP_M = 8;                 // rasterisation: tiles advance down 8 M-blocks before moving in N
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+
+enum WaitCode { kWaitEmpty = 101, kWaitFull = 102, kWaitAccEmpty = 103, kWaitAccFull = 104 };
+
+struct TileCoord { int m_block, n_block; };
+
+__device__ __forceinline__ TileCoord tile_coord(int tile, int m_blocks, int n_blocks) {
+  const int group_size = GROUP_M * n_blocks;
+  const int group = tile / group_size;
+  const int first_m = group * GROUP_M;
+  const int rows = min(GROUP_M, m_blocks - first_m);
+  const int within = tile - group * group_size;
+  return {first_m + within % rows, within / rows};
+}
+
+template <typename OutT> __device__ __forceinline__ void store_chunk(OutT* row_ptr, const uint32_t (&acc)[32], int valid);
+
+template <> __device__ __forceinline__ void store_chunk<__nv_bfloat16>(__nv_bfloat16* row_ptr, const uint32_t (&acc)[32], int valid) {
+  if (valid >= 32 && (reinterpret_cast<uintptr_t>(row_ptr) & 15u) == 0) {
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+      uint32_t packed[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        __nv_bfloat162 pair = __floats2bfloat162_rn(__uint_as_float(acc[v * 8 + 2 * j]), __uint_as_float(acc[v * 8 + 2 * j + 1]));
+        packed[j] = *reinterpret_cast<uint32_t*>(&pair);
+      }
+      *reinterpret_cast<uint4*>(row_ptr + v * 8) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (j < valid) row_ptr[j] = __float2bfloat16_rn(__uint_as_float(acc[j]));
+  }
+}
+
+template <> __device__ __forceinline__ void store_chunk<float>(float* row_ptr, const uint32_t (&acc)[32], int valid) {
+  if (valid >= 32 && (reinterpret_cast<uintptr_t>(row_ptr) & 15u) == 0) {
+#pragma unroll
+    for (int v = 0; v < 8; ++v)
+      *reinterpret_cast<uint4*>(row_ptr + v * 4) = make_uint4(acc[v * 4], acc[v * 4 + 1], acc[v * 4 + 2], acc[v * 4 + 3]);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (j < valid) row_ptr[j] = __uint_as_float(acc[j]);
+  }
+}
+
+template <typename OutT>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_abt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, OutT* __restrict__ c,
+                int m, int n, int k, int* status_word) {
+  extern __shared__ uint8_t smem_raw[];
+  // operand tiles need 1024-byte alignment for the 128-byte swizzle pattern
+  const uint32_t smem_base = (smem_addr(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_aligned = smem_raw + (smem_base - smem_addr(smem_raw));
+  uint64_t* barriers = reinterpret_cast<uint64_t*>(smem_aligned + STAGES * STAGE_BYTES);
+  // barrier layout: full[STAGES], empty[STAGES], acc_full[2], acc_empty[2], then the TMEM slot and abort flag
+  const uint32_t bar_base = smem_base + STAGES * STAGE_BYTES;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto acc_full_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + b); };
+  auto acc_empty_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + 2 + b); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(barriers + 2 * STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int m_blocks = (m + BM - 1) / BM, n_blocks = (n + BN - 1) / BN;
+  const int tiles = m_blocks * n_blocks;
+  const int k_blocks = (k + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(acc_full_bar(b), 1);
+      mbar_init(acc_empty_bar(b), 4);  // one arrival per epilogue warp
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    fence_proxy_async();
+  }
+  if (warp == 1) tmem_alloc(smem_addr(tmem_slot), TMEM_COLUMNS);
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (elect_one()) {
+      prefetch_tensormap(&map_a);
+      prefetch_tensormap(&map_b);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < tiles; tile += gridDim.x) {
+        const TileCoord coord = tile_coord(tile, m_blocks, n_blocks);
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          // a fresh barrier's "previous phase" counts as complete: waiting on parity^1 passes at once
+          if (!(ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, status_word, kWaitEmpty))) break;
+          const uint32_t a_dst = smem_base + stage * STAGE_BYTES;
+          const uint32_t b_dst = a_dst + A_TILE_BYTES;
+          mbar_arrive_expect_tx(full_bar(stage), STAGE_BYTES);
+          tma_load_2d(a_dst, &map_a, full_bar(stage), kb * BK, coord.m_block * BM);
+          tma_load_2d(b_dst, &map_b, full_bar(stage), kb * BK, coord.n_block * BN);
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (elect_one()) {
+      constexpr uint32_t idesc = umma_idesc_bf16_f32(BM, BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int local_tile = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < tiles; tile += gridDim.x, ++local_tile) {
+        const int buffer = local_tile & 1;
+        const uint32_t acc_phase = (uint32_t)(local_tile >> 1) & 1u;
+        if (!(ok = mbar_wait(acc_empty_bar(buffer), acc_phase ^ 1u, abort_flag, status_word, kWaitAccEmpty))) break;
+        tcgen05_fence_after();
+        const uint32_t tmem_acc = tmem_base + (uint32_t)(buffer * ACC_COLUMNS);
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!(ok = mbar_wait(full_bar(stage), phase, abort_flag, status_word, kWaitFull))) break;
+          tcgen05_fence_after();
+          const uint32_t a_src = smem_base + stage * STAGE_BYTES;
+          const uint64_t desc_a = umma_desc_k_major_sw128(a_src);
+          const uint64_t desc_b = umma_desc_k_major_sw128(a_src + A_TILE_BYTES);
+#pragma unroll
+          for (int kk = 0; kk < BK / UMMA_K; ++kk)
+            umma_bf16_ss(tmem_acc, umma_desc_advance_k(desc_a, kk * UMMA_K * 2), umma_desc_advance_k(desc_b, kk * UMMA_K * 2),
+                         idesc, (kb | kk) != 0 ? 1u : 0u);
+          umma_commit(empty_bar(stage));  // the stage may be refilled once these MMAs have read it
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) umma_commit(acc_full_bar(buffer));
+      }
+    }
+  } else {
+    // ---------------- epilogue (warps 2..5) ----------------
+    const int quadrant = warp & 3;  // TMEM lanes [32*quadrant, 32*quadrant+32) are the ones this warp may read
+    int local_tile = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < tiles; tile += gridDim.x, ++local_tile) {
+      const TileCoord coord = tile_coord(tile, m_blocks, n_blocks);
+      const int buffer = local_tile & 1;
+      const uint32_t acc_phase = (uint32_t)(local_tile >> 1) & 1u;
+      ok = mbar_wait(acc_full_bar(buffer), acc_phase, abort_flag, status_word, kWaitAccFull);
+      ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld below is warp-collective: leave together or not at all
+      if (!ok) break;
+      tcgen05_fence_after();
+      const int row = coord.m_block * BM + quadrant * 32 + lane;
+      const int col0 = coord.n_block * BN;
+      const uint32_t taddr = tmem_base + ((uint32_t)(quadrant * 32) << 16) + (uint32_t)(buffer * ACC_COLUMNS);
+#pragma unroll 1
+      for (int chunk = 0; chunk < BN / 32; ++chunk) {
+        uint32_t acc[32];
+        tmem_ld_32x32b_x32(taddr + (uint32_t)(chunk * 32), acc);
+        tmem_ld_wait();
+        const int col = col0 + chunk * 32;
+        if (row < m && col < n) store_chunk<OutT>(c + (size_t)row * n + col, acc, n - col);
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_empty_bar(buffer));
+    }
+  }
+
+  // ---------------- teardown ----------------
+  tcgen05_fence_before();
+  __syncthreads();
+  if (*abort_flag != 0) {
+    // a wait was abandoned: give copies that may still be in flight a bounded time to land before the
+    // shared memory and TMEM are released
+    const unsigned long long started = global_timer_ns();
+    while (global_timer_ns() - started < 2000000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    __syncwarp();
+    tcgen05_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLUMNS);
+  }
+}
+
+// ---- tiled transpose (brings other operand layouts to the native K-contiguous form) ------------------
+__global__ void transpose_bf16_kernel(const __nv_bfloat16* __restrict__ src, __nv_bfloat16* __restrict__ dst, int rows, int cols) {
+  __shared__ __nv_bfloat16 tile[32][33];
+  const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+  for (int j = threadIdx.y; j < 32; j += blockDim.y) {
+    const int r = r0 + j, c = c0 + threadIdx.x;
+    if (r < rows && c < cols) tile[j][threadIdx.x] = src[(size_t)r * cols + c];
+  }
+  __syncthreads();
+  for (int j = threadIdx.y; j < 32; j += blockDim.y) {
+    const int c = c0 + j, r = r0 + threadIdx.x;
+    if (r < rows && c < cols) dst[(size_t)c * rows + r] = tile[threadIdx.x][j];
+  }
+}
+
+int launch_transpose(const void* src, void* dst, int rows, int cols, cudaStream_t stream) {
+  dim3 grid((cols + 31) / 32, (rows + 31) / 32), block(32, 8);
+  transpose_bf16_kernel<<<grid, block, 0, stream>>>(static_cast<const __nv_bfloat16*>(src), static_cast<__nv_bfloat16*>(dst), rows, cols);
+  return check_launch("transpose kernel launch");
+}
+
+constexpr int kMaxDevices = 64;
+
+int current_device() {
+  int device = 0;
+  return cudaGetDevice(&device) == cudaSuccess && device >= 0 && device < kMaxDevices ? device : -1;
+}
+
+int cached_sm_count(int device) {
+  static int counts[kMaxDevices] = {};
+  if (counts[device] == 0 &&
+      cudaDeviceGetAttribute(&counts[device], cudaDevAttrMultiProcessorCount, device) != cudaSuccess)
+    counts[device] = 0;
+  return counts[device];
+}
+
+template <typename OutT>
+int launch_native(const void* a_mk, const void* b_nk, void* c, int m, int n, int k, cudaStream_t stream) {
+  alignas(64) CUtensorMap map_a, map_b;
+  if (int status = encode_tensormap_2d(&map_a, BB200_BF16, a_mk, (uint64_t)m, (uint64_t)k, (uint64_t)k * 2, BM, BK, 3)) return status;
+  if (int status = encode_tensormap_2d(&map_b, BB200_BF16, b_nk, (uint64_t)n, (uint64_t)k, (uint64_t)k * 2, BN, BK, 3)) return status;
+  const int device = current_device();
+  if (device < 0) return fail(BB200_E_NO_DRIVER, "gemm: no CUDA device is current");
+  static bool configured[kMaxDevices] = {};  // per template instantiation and device
+  if (!configured[device]) {
+    if (int status = check_runtime(cudaFuncSetAttribute(gemm_abt_kernel<OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES),
+                                   "cudaFuncSetAttribute(gemm smem)"))
+      return status;
+    configured[device] = true;
+  }
+  const int sms = cached_sm_count(device);
+  if (sms <= 0) return fail(BB200_E_NO_DRIVER, "gemm: could not query the SM count");
+  const int tiles = ((m + BM - 1) / BM) * ((n + BN - 1) / BN);
+  const int grid = tiles < sms ? tiles : sms;
+  gemm_abt_kernel<OutT><<<grid, THREADS, SMEM_BYTES, stream>>>(map_a, map_b, static_cast<OutT*>(c), m, n, k, device_status_word());
+  return check_launch("gemm kernel launch");
+}
+
+}  // namespace
+}  // namespace bb200
+
 using namespace bb200;
-extern "C" int bb200_gemm_bf16(const void*, const void*, void*, int, int, int, int, int, bb200_dtype, void*) {
-  return fail(BB200_E_UNSUPPORTED_SHAPE, "gemm: not built yet");
+
+extern "C" int bb200_gemm_bf16(const void* a, const void* b, void* c, int m, int n, int k, int transpose_a, int transpose_b,
+                               bb200_dtype c_dtype, void* stream) {
+  if (!a || !b || !c) return fail(BB200_E_INVALID_ARGUMENT, "gemm: null tensor pointer");
+  if (m <= 0 || n <= 0 || k <= 0) return fail(BB200_E_INVALID_ARGUMENT, "gemm: m, n, k must be > 0 (got %d, %d, %d)", m, n, k);
+  if (c_dtype != BB200_BF16 && c_dtype != BB200_F32) return fail(BB200_E_INVALID_ARGUMENT, "gemm: C must be bf16 or f32");
+  if (k % 8) return fail(BB200_E_UNSUPPORTED_SHAPE, "gemm: k=%d must be a multiple of 8 (16-byte rows for TMA)", k);
+  if (!aligned16(a) || !aligned16(b)) return fail(BB200_E_MISALIGNED, "gemm: A and B must be 16-byte aligned");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // bring both operands to K-contiguous form: A as [m,k], B as [n,k]
+  const void* a_mk = a;
+  const void* b_nk = b;
+  void* workspace = nullptr;
+  const size_t a_bytes = transpose_a ? (size_t)m * k * 2 : 0;
+  const size_t b_bytes = !transpose_b ? (size_t)n * k * 2 : 0;
+  if (a_bytes + b_bytes) {
+    if (int status = check_runtime(cudaMallocAsync(&workspace, a_bytes + b_bytes, s), "cudaMallocAsync(gemm workspace)")) return status;
+    int status = BB200_OK;
+    if (transpose_a) {  // stored [k, m] → [m, k]
+      status = launch_transpose(a, workspace, k, m, s);
+      a_mk = workspace;
+    }
+    if (!status && !transpose_b) {  // stored [k, n] → [n, k]
+      void* dst = static_cast<uint8_t*>(workspace) + a_bytes;
+      status = launch_transpose(b, dst, k, n, s);
+      b_nk = dst;
+    }
+    if (status) {
+      cudaFreeAsync(workspace, s);
+      return status;
+    }
+  }
+  int status = c_dtype == BB200_BF16 ? launch_native<__nv_bfloat16>(a_mk, b_nk, c, m, n, k, s)
+                                     : launch_native<float>(a_mk, b_nk, c, m, n, k, s);
+  if (workspace) {
+    const int freed = check_runtime(cudaFreeAsync(workspace, s), "cudaFreeAsync(gemm workspace)");
+    if (!status) status = freed;
+  }
+  return status;
 }
