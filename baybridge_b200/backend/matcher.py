@@ -205,8 +205,8 @@ def _match_attention(ir, op) -> AttentionPlan:
         raise _unsupported("attention lse must be f32 of shape [batch, heads, 1, seq] or [batch, heads, seq]")
     if any(spec.dtype != "bf16" for spec in (q_spec, k_spec, v_spec, out_spec)):
         raise _unsupported("attention operands must be bf16")
-    if head_dim not in (64, 128):
-        raise _unsupported(f"attention head_dim must be 64 or 128 (got {head_dim})")
+    if head_dim not in (64, 128) and seq > 8192:
+        raise _unsupported(f"attention with head_dim {head_dim} (not 64/128) is limited to seq <= 8192 (got {seq})")
     return AttentionPlan(q, k, v, out, lse, batch, seq, heads, kv_heads, head_dim, bool(op.attrs.get("causal")), "bf16")
 
 

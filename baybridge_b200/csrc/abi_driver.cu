@@ -225,6 +225,30 @@ int encode_tensormap_2d(void* map_out, bb200_dtype dtype, const void* base, uint
                       "cuTensorMapEncodeTiled");
 }
 
+int encode_tensormap_3d(void* map_out, bb200_dtype dtype, const void* base, uint64_t dim0, uint64_t dim1, uint64_t dim2,
+                        uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t box0, uint32_t box1, uint32_t box2,
+                        int swizzle) {
+  BB200_DRIVER_OR_RETURN(api);
+  if (!map_out || !base || !dim0 || !dim1 || !dim2 || !box0 || !box1 || !box2)
+    return fail(BB200_E_INVALID_ARGUMENT, "tensormap: null pointer or zero extent");
+  if (dtype != BB200_BF16 && dtype != BB200_F16) return fail(BB200_E_INVALID_ARGUMENT, "tensormap(3d): 16-bit dtypes only");
+  if (!aligned16(base) || (stride1_bytes & 15u) || (stride2_bytes & 15u))
+    return fail(BB200_E_MISALIGNED, "tensormap: base and strides must be multiples of 16 bytes");
+  if (swizzle != 3 || box0 * 2 != 128) return fail(BB200_E_UNSUPPORTED_SHAPE, "tensormap(3d): 128-byte rows with 128-byte swizzle only");
+  if (box1 > 256 || box2 > 256) return fail(BB200_E_UNSUPPORTED_SHAPE, "tensormap: box extents are limited to 256");
+  cuuint64_t dims[3] = {dim0, dim1, dim2};
+  cuuint64_t strides[2] = {stride1_bytes, stride2_bytes};
+  cuuint32_t box[3] = {box0, box1, box2};
+  cuuint32_t element_strides[3] = {1, 1, 1};
+  return check_driver(api,
+                      api->cuTensorMapEncodeTiled(reinterpret_cast<CUtensorMap*>(map_out),
+                                                  dtype == BB200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                                                  3, const_cast<void*>(base), dims, strides, box, element_strides,
+                                                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE),
+                      "cuTensorMapEncodeTiled(3d)");
+}
+
 }  // namespace bb200
 
 using namespace bb200;

@@ -36,4 +36,9 @@ int* device_status_word();
 int encode_tensormap_2d(void* map_out, bb200_dtype dtype, const void* base, uint64_t rows, uint64_t cols,
                         uint64_t row_stride_bytes, uint32_t box_rows, uint32_t box_cols, int swizzle);
 
+// 3-D variant: extents (dim0 innermost), byte strides of dim1 and dim2, box extents.
+int encode_tensormap_3d(void* map_out, bb200_dtype dtype, const void* base, uint64_t dim0, uint64_t dim1, uint64_t dim2,
+                        uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t box0, uint32_t box1, uint32_t box2,
+                        int swizzle);
+
 }  // namespace bb200

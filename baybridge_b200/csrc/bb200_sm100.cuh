@@ -90,6 +90,12 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y)
       : "memory");
 }
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2, int c3) {
   asm volatile(
       "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
@@ -135,6 +141,17 @@ __device__ __forceinline__ uint64_t umma_desc_k_major_sw128(uint32_t tile_smem_a
          | (64ull << 32)                              // stride byte offset: 1024 B between 8-row groups
          | (1ull << 46)                               // descriptor version for sm_100
          | (2ull << 61);                              // layout type: 128-byte swizzle
+}
+// MN-major operand (the MN dimension is contiguous in memory): sub-tiles of [k rows, 64 elements]
+// with 128-byte rows and the 128-byte swizzle; 8-row groups are 1024 bytes apart and consecutive
+// 64-element groups along MN are `mn_group_stride_bytes` apart.  A K step of 16 advances the start
+// address by 16 rows (2048 bytes).
+__device__ __forceinline__ uint64_t umma_desc_mn_major_sw128(uint32_t tile_smem_addr, uint32_t mn_group_stride_bytes) {
+  return (uint64_t)((tile_smem_addr >> 4) & 0x3FFFu)
+         | ((uint64_t)((mn_group_stride_bytes >> 4) & 0x3FFFu) << 16)  // leading-dimension byte offset
+         | (64ull << 32)                                               // stride byte offset: 1024 B
+         | (1ull << 46)
+         | (2ull << 61);
 }
 // Advancing along K inside the swizzle atom by `elements` (a multiple of 8 bf16 = 16 B) is a plain
 // start-address advance.

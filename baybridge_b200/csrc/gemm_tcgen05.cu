@@ -1,8 +1,9 @@
 // gemm_tcgen05.cu — BF16 GEMM for sm_100a: C[m,n] = sum_k A'[m,k] * B'[k,n], fp32 accumulate.
 //
-// Native form: A is [M,K] and B is [N,K], both row-major (K contiguous) — "A · B^T", the layout
-// tcgen05 consumes directly.  Other transpose combinations are brought to that form by a tiled
-// transpose into a stream-ordered workspace.
+// Native forms: A is [M,K] row-major (K contiguous); B is either [N,K] (K contiguous, "A · B^T") or
+// [K,N] (N contiguous, "A · B") — tcgen05 consumes both through its K-major / MN-major shared-memory
+// descriptors.  A stored [K,M] is brought to [M,K] by a tiled transpose into a stream-ordered
+// workspace.
 //
 // Kernel structure (one persistent CTA per SM, 192 threads):
 //   warp 0      TMA producer: streams 128x64 A tiles and 256x64 B tiles (128-byte swizzle) into a
@@ -84,7 +85,9 @@ template <> __device__ __forceinline__ void store_chunk<float>(float* row_ptr, c
   }
 }
 
-template <typename OutT>
+// B_MN = false: B tile is [BN n-rows, 64 k] (K-major).  B_MN = true: B is stored [K, N]; a stage holds
+// BN/64 sub-tiles of [64 k-rows, 64 n] (MN-major), each 8 KB, consecutive in shared memory.
+template <typename OutT, bool B_MN>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_abt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, OutT* __restrict__ c,
                 int m, int n, int k, int* status_word) {
@@ -144,7 +147,13 @@ gemm_abt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           const uint32_t b_dst = a_dst + A_TILE_BYTES;
           mbar_arrive_expect_tx(full_bar(stage), STAGE_BYTES);
           tma_load_2d(a_dst, &map_a, full_bar(stage), kb * BK, coord.m_block * BM);
-          tma_load_2d(b_dst, &map_b, full_bar(stage), kb * BK, coord.n_block * BN);
+          if constexpr (B_MN) {
+#pragma unroll
+            for (int t = 0; t < BN / 64; ++t)
+              tma_load_2d(b_dst + t * (BK * 128), &map_b, full_bar(stage), coord.n_block * BN + t * 64, kb * BK);
+          } else {
+            tma_load_2d(b_dst, &map_b, full_bar(stage), kb * BK, coord.n_block * BN);
+          }
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
       }
@@ -152,7 +161,7 @@ gemm_abt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (elect_one()) {
-      constexpr uint32_t idesc = umma_idesc_bf16_f32(BM, BN);
+      constexpr uint32_t idesc = umma_idesc_bf16_f32(BM, BN, false, B_MN);
       int stage = 0;
       uint32_t phase = 0;
       int local_tile = 0;
@@ -168,10 +177,13 @@ gemm_abt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           tcgen05_fence_after();
           const uint32_t a_src = smem_base + stage * STAGE_BYTES;
           const uint64_t desc_a = umma_desc_k_major_sw128(a_src);
-          const uint64_t desc_b = umma_desc_k_major_sw128(a_src + A_TILE_BYTES);
+          const uint64_t desc_b = B_MN ? umma_desc_mn_major_sw128(a_src + A_TILE_BYTES, BK * 128)
+                                       : umma_desc_k_major_sw128(a_src + A_TILE_BYTES);
+          // one K step of 16: 32 bytes along a K-major row, or 16 rows of 128 bytes in an MN-major tile
+          constexpr uint32_t b_step = B_MN ? UMMA_K * 128 : UMMA_K * 2;
 #pragma unroll
           for (int kk = 0; kk < BK / UMMA_K; ++kk)
-            umma_bf16_ss(tmem_acc, umma_desc_advance_k(desc_a, kk * UMMA_K * 2), umma_desc_advance_k(desc_b, kk * UMMA_K * 2),
+            umma_bf16_ss(tmem_acc, umma_desc_advance_k(desc_a, kk * UMMA_K * 2), umma_desc_advance_k(desc_b, kk * b_step),
                          idesc, (kb | kk) != 0 ? 1u : 0u);
           umma_commit(empty_bar(stage));  // the stage may be refilled once these MMAs have read it
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -262,16 +274,19 @@ int cached_sm_count(int device) {
   return counts[device];
 }
 
-template <typename OutT>
-int launch_native(const void* a_mk, const void* b_nk, void* c, int m, int n, int k, cudaStream_t stream) {
+// b_is_kn: B is stored [k, n] (n contiguous) and consumed as an MN-major operand; otherwise [n, k].
+template <typename OutT, bool B_MN>
+int launch_native(const void* a_mk, const void* b, void* c, int m, int n, int k, cudaStream_t stream) {
   alignas(64) CUtensorMap map_a, map_b;
   if (int status = encode_tensormap_2d(&map_a, BB200_BF16, a_mk, (uint64_t)m, (uint64_t)k, (uint64_t)k * 2, BM, BK, 3)) return status;
-  if (int status = encode_tensormap_2d(&map_b, BB200_BF16, b_nk, (uint64_t)n, (uint64_t)k, (uint64_t)k * 2, BN, BK, 3)) return status;
+  if (int status = B_MN ? encode_tensormap_2d(&map_b, BB200_BF16, b, (uint64_t)k, (uint64_t)n, (uint64_t)n * 2, BK, 64, 3)
+                        : encode_tensormap_2d(&map_b, BB200_BF16, b, (uint64_t)n, (uint64_t)k, (uint64_t)k * 2, BN, BK, 3))
+    return status;
   const int device = current_device();
   if (device < 0) return fail(BB200_E_NO_DRIVER, "gemm: no CUDA device is current");
   static bool configured[kMaxDevices] = {};  // per template instantiation and device
   if (!configured[device]) {
-    if (int status = check_runtime(cudaFuncSetAttribute(gemm_abt_kernel<OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES),
+    if (int status = check_runtime(cudaFuncSetAttribute(gemm_abt_kernel<OutT, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES),
                                    "cudaFuncSetAttribute(gemm smem)"))
       return status;
     configured[device] = true;
@@ -280,7 +295,7 @@ int launch_native(const void* a_mk, const void* b_nk, void* c, int m, int n, int
   if (sms <= 0) return fail(BB200_E_NO_DRIVER, "gemm: could not query the SM count");
   const int tiles = ((m + BM - 1) / BM) * ((n + BN - 1) / BN);
   const int grid = tiles < sms ? tiles : sms;
-  gemm_abt_kernel<OutT><<<grid, THREADS, SMEM_BYTES, stream>>>(map_a, map_b, static_cast<OutT*>(c), m, n, k, device_status_word());
+  gemm_abt_kernel<OutT, B_MN><<<grid, THREADS, SMEM_BYTES, stream>>>(map_a, map_b, static_cast<OutT*>(c), m, n, k, device_status_word());
   return check_launch("gemm kernel launch");
 }
 
@@ -297,31 +312,24 @@ extern "C" int bb200_gemm_bf16(const void* a, const void* b, void* c, int m, int
   if (k % 8) return fail(BB200_E_UNSUPPORTED_SHAPE, "gemm: k=%d must be a multiple of 8 (16-byte rows for TMA)", k);
   if (!aligned16(a) || !aligned16(b)) return fail(BB200_E_MISALIGNED, "gemm: A and B must be 16-byte aligned");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  // bring both operands to K-contiguous form: A as [m,k], B as [n,k]
+  // B is consumed in place in either layout; only A stored [k, m] needs a transposed copy
+  const bool b_is_kn = !transpose_b;
+  if (b_is_kn && (n % 8)) return fail(BB200_E_UNSUPPORTED_SHAPE, "gemm: n=%d must be a multiple of 8 when B is stored [k, n]", n);
   const void* a_mk = a;
-  const void* b_nk = b;
   void* workspace = nullptr;
-  const size_t a_bytes = transpose_a ? (size_t)m * k * 2 : 0;
-  const size_t b_bytes = !transpose_b ? (size_t)n * k * 2 : 0;
-  if (a_bytes + b_bytes) {
-    if (int status = check_runtime(cudaMallocAsync(&workspace, a_bytes + b_bytes, s), "cudaMallocAsync(gemm workspace)")) return status;
-    int status = BB200_OK;
-    if (transpose_a) {  // stored [k, m] → [m, k]
-      status = launch_transpose(a, workspace, k, m, s);
-      a_mk = workspace;
-    }
-    if (!status && !transpose_b) {  // stored [k, n] → [n, k]
-      void* dst = static_cast<uint8_t*>(workspace) + a_bytes;
-      status = launch_transpose(b, dst, k, n, s);
-      b_nk = dst;
-    }
-    if (status) {
+  if (transpose_a) {  // stored [k, m] -> [m, k]
+    if (int status = check_runtime(cudaMallocAsync(&workspace, (size_t)m * k * 2, s), "cudaMallocAsync(gemm workspace)")) return status;
+    if (int status = launch_transpose(a, workspace, k, m, s)) {
       cudaFreeAsync(workspace, s);
       return status;
     }
+    a_mk = workspace;
   }
-  int status = c_dtype == BB200_BF16 ? launch_native<__nv_bfloat16>(a_mk, b_nk, c, m, n, k, s)
-                                     : launch_native<float>(a_mk, b_nk, c, m, n, k, s);
+  int status;
+  if (c_dtype == BB200_BF16)
+    status = b_is_kn ? launch_native<__nv_bfloat16, true>(a_mk, b, c, m, n, k, s) : launch_native<__nv_bfloat16, false>(a_mk, b, c, m, n, k, s);
+  else
+    status = b_is_kn ? launch_native<float, true>(a_mk, b, c, m, n, k, s) : launch_native<float, false>(a_mk, b, c, m, n, k, s);
   if (workspace) {
     const int freed = check_runtime(cudaFreeAsync(workspace, s), "cudaFreeAsync(gemm workspace)");
     if (!status) status = freed;

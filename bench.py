@@ -149,10 +149,16 @@ class Workload:
     def config(self) -> dict:
         raise NotImplementedError
 
+    def shrink(self) -> None:
+        raise NotImplementedError
+
 
 class FusedMulAdd(Workload):
     name, unit, bound = "fused_mul_add", "GB/s", "hbm"
     n = 2**28
+
+    def shrink(self):
+        self.n = 2**26  # 400 MB working set
 
     def work_per_step(self) -> float:
         return 6.0 * self.n  # read a, read b, write c at 2 B each
@@ -188,7 +194,7 @@ class FusedMulAdd(Workload):
         torch.cuda.current_stream().synchronize()
 
     def config(self):
-        return {"workload": "fused_mul_add c=a*b+a bf16 2^28 elements per GPU (6 B/element), indexed IR form",
+        return {"workload": f"fused_mul_add c=a*b+a bf16 {self.n} (2^{self.n.bit_length() - 1}) elements per GPU (6 B/element), indexed IR form",
                 "l2": "working set 1.6 GB > 126 MB L2, no flush"}
 
     # CPU port leg -------------------------------------------------------------------------------
@@ -220,6 +226,9 @@ class FusedMulAdd(Workload):
 class RmsNorm(Workload):
     name, unit, bound = "rmsnorm", "GB/s", "hbm"
     rows, hidden = 65536, 8192
+
+    def shrink(self):
+        self.rows = 8192  # 268 MB working set
 
     def work_per_step(self) -> float:
         return 2.0 * self.rows * self.hidden * 2 + self.hidden * 2
@@ -253,7 +262,7 @@ class RmsNorm(Workload):
         torch.cuda.current_stream().synchronize()
 
     def config(self):
-        return {"workload": "rmsnorm bf16 [65536, 8192] per GPU, weight [8192], eps 1e-6",
+        return {"workload": f"rmsnorm bf16 [{self.rows}, {self.hidden}] per GPU, weight [{self.hidden}], eps 1e-6",
                 "l2": "working set 2.1 GB > 126 MB L2, no flush"}
 
     def cpu_sample(self):
@@ -270,6 +279,9 @@ class Gemm(Workload):
     name, unit, bound = "gemm", "TFLOP/s", "tensor"
     m = n = k = 8192
     needs_l2_flush = True
+
+    def shrink(self):
+        self.m = self.n = self.k = 4096
 
     def work_per_step(self) -> float:
         return 2.0 * self.m * self.n * self.k
@@ -305,7 +317,7 @@ class Gemm(Workload):
         torch.cuda.current_stream().synchronize()
 
     def config(self):
-        return {"workload": "gemm C=A·B^T bf16 M=N=K=8192 per GPU, fp32 accumulate, bf16 out",
+        return {"workload": f"gemm C=A·B^T bf16 M=N=K={self.m} per GPU, fp32 accumulate, bf16 out",
                 "l2": "384 MB working set; 256 MB L2 flush write between timed steps (outside the event pairs)"}
 
     def cpu_sample(self):
@@ -321,6 +333,9 @@ class Gemm(Workload):
 class Attention(Workload):
     name, unit, bound = "attention", "TFLOP/s", "tensor"
     batch, heads, seq, dim = 16, 32, 4096, 128
+
+    def shrink(self):
+        self.batch = 2
 
     def work_per_step(self) -> float:
         return 4.0 * self.batch * self.heads * self.dim * self.seq * (self.seq + 1) / 2
@@ -356,7 +371,7 @@ class Attention(Workload):
         torch.cuda.current_stream().synchronize()
 
     def config(self):
-        return {"workload": "causal attention fwd bf16 B16 H32 S4096 D128 per GPU (layout [B,S,H,D]), causal FLOPs",
+        return {"workload": f"causal attention fwd bf16 B{self.batch} H{self.heads} S{self.seq} D{self.dim} per GPU (layout [B,S,H,D]), causal FLOPs",
                 "l2": "working set 2.1 GB > 126 MB L2, no flush"}
 
     def cpu_sample(self):
@@ -434,8 +449,12 @@ def main() -> None:
     parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--e2e-steps", type=int, default=3)
+    parser.add_argument("--small", action="store_true",
+                        help="reduced problem (still larger than L2) for profiler captures; never a bench value")
     args = parser.parse_args()
     workload = WORKLOADS[args.workload]()
+    if args.small:
+        workload.shrink()
     if args.impl == "reference":
         reference_arm(args, workload)
         return

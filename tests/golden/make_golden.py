@@ -307,6 +307,10 @@ def main() -> None:
     run_case("c5_attn_causal_b1s24h2d32", zoo.attention_causal, attn_inputs(1, 24, 2, 2, 32), ["out", "lse"])
     run_case("attn_full_b1s24h2d32", zoo.attention_full, attn_inputs(1, 24, 2, 2, 32), ["out", "lse"])
     run_case("attn_causal_gqa_b2s16h4kv2d16", zoo.attention_causal, attn_inputs(2, 16, 4, 2, 16), ["out", "lse"])
+    # head dims the tensor-core kernel serves (upstream's exec backend requires head_dim 128)
+    run_case("attn_causal_gqa_b1s128h2kv1d64", zoo.attention_causal, attn_inputs(1, 128, 2, 1, 64), ["out", "lse"])
+    run_case("attn_full_b1s64h1d128", zoo.attention_full, attn_inputs(1, 64, 1, 1, 128), ["out", "lse"])
+    run_case("attn_causal_b1s160h1d128", zoo.attention_causal, attn_inputs(1, 160, 1, 1, 128), ["out", "lse"])
     dump_ir(
         "c5_attn_causal_b16s4096h32d128",
         zoo.attention_causal,
