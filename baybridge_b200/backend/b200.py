@@ -32,7 +32,7 @@ from ..portable_ir import row_major_stride
 from ..scalar_types import DEVICE_NUMPY, byte_width, normalize_dtype_name
 from . import native
 from .elementwise import THREADS, UNROLL, compile_cubin, render
-from .matcher import AttentionPlan, ElementwisePlan, GemmPlan, RmsNormPlan, match
+from .matcher import AttentionPlan, ElementwisePlan, GemmPlan, RmsNormPlan, adopt, match
 
 _thread_state = threading.local()
 
@@ -97,6 +97,7 @@ class B200Backend:
         arch = getattr(target, "arch", None)
         if arch not in ("sm_100a", "sm_100"):
             raise BackendNotImplementedError(f"b200 lowers for NvidiaTarget('sm_100a') only (got {arch!r})")
+        ir = adopt(ir)
         plan = match(ir)
         record: dict[str, Any] = {"backend": self.name, "kernel": ir.name, "plan": plan.kind, "target": arch}
         if isinstance(plan, ElementwisePlan):
@@ -115,6 +116,7 @@ class B200Backend:
     # -- contract: launcher ------------------------------------------------------------------------
     def build_launcher(self, ir: Any, target: Any, lowered_module: Any, lowered_path: Path | None = None) -> Callable[..., None]:
         del lowered_path
+        ir = adopt(ir)
         plan = match(ir)
         record = json.loads(lowered_module.text)
         state: dict[str, Any] = {"slots": {}}
@@ -131,7 +133,7 @@ class B200Backend:
             if len(args) != len(arguments):
                 raise TypeError(f"{ir.name} expects {len(arguments)} arguments, got {len(args)}")
             native.require_device()
-            staged: list[tuple[RuntimeTensor, _StagedSlot]] = []
+            staged: list[tuple[RuntimeTensor, _StagedSlot, Any]] = []
             stream_handle = native.stream_handle(stream)
             try:
                 pointers: dict[int, int] = {}
@@ -147,11 +149,13 @@ class B200Backend:
                 LAUNCH_COUNTER["launches"] += 1
                 if staged or self.synchronize:
                     native.call("bb200_stream_synchronize", stream_handle)
-                for tensor, slot in staged:
+                for tensor, slot, foreign in staged:
                     image = np.empty(tensor.numel, dtype=DEVICE_NUMPY[tensor.dtype])
                     native.call("bb200_memcpy_d2h", image.ctypes.data_as(ctypes.c_void_p), slot.pointer, slot.nbytes, stream_handle)
                     native.call("bb200_stream_synchronize", stream_handle)
                     tensor.absorb_device_image(image)
+                    if foreign is not None:
+                        foreign._storage[:] = tensor.as_numpy().reshape(-1).tolist()
             except Exception:
                 for slot in state.pop("slots", {}).values():
                     slot.release()
@@ -163,13 +167,19 @@ class B200Backend:
 
     # -- argument marshalling ------------------------------------------------------------------------
     def _device_of(self, args: tuple[Any, ...]) -> int:
-        devices = {int(value.device_id) for value in args if isinstance(value, TensorHandle)}
+        # duck-typed so handles created by an upstream checkout's runtime module count too
+        devices = {int(value.device_id) for value in args
+                   if getattr(value, "device_type", None) == DLPACK_CUDA and hasattr(value, "device_id")}
         if len(devices) > 1:
             raise BackendNotImplementedError(f"b200: tensor arguments live on different devices {sorted(devices)}")
         return devices.pop() if devices else self.device
 
     def _tensor_pointer(self, position, argument, value, stream, stream_handle, state, staged) -> int:
         spec = argument.spec
+        foreign = None
+        if not isinstance(value, (RuntimeTensor, TensorHandle)) and hasattr(value, "_storage") and hasattr(value, "tolist"):
+            # a host tensor of an upstream checkout (list storage): stage a copy, write results back into its list
+            foreign, value = value, RuntimeTensor.from_data(value.tolist(), dtype=value.dtype)
         if not isinstance(value, (RuntimeTensor, TensorHandle)) and hasattr(value, "__dlpack__") and hasattr(value, "__dlpack_device__"):
             value = from_dlpack(value, stream=stream)
         if isinstance(value, TensorHandle):
@@ -208,7 +218,7 @@ class B200Backend:
                 slot = state["slots"][position] = _StagedSlot(image.nbytes, signature)
             native.call("bb200_memcpy_h2d", slot.pointer, image.ctypes.data_as(ctypes.c_void_p), image.nbytes, stream_handle)
             native.call("bb200_stream_synchronize", stream_handle)  # `image` is pageable and about to go out of scope
-            staged.append((value, slot))
+            staged.append((value, slot, foreign))
             return int(slot.pointer.value)
         raise TypeError(
             "b200 currently expects RuntimeTensor values, CUDA TensorHandle values, or CUDA DLPack-capable tensor objects "

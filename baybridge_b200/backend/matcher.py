@@ -660,11 +660,20 @@ def _match_ssa_elementwise(ir) -> ElementwisePlan:
 # ---------------------------------------------------------------------------------------------
 # entry point
 # ---------------------------------------------------------------------------------------------
+def adopt(ir):
+    """IR objects built by an upstream checkout are rebuilt from their serialised form, which is
+    identical by construction, so the rest of the backend can rely on this package's record types."""
+    from ..portable_ir import PortableKernelIR
+
+    return ir if isinstance(ir, PortableKernelIR) else PortableKernelIR.from_dict(ir.to_dict())
+
+
 EXPLICIT = {"mma": _match_gemm, "rmsnorm": _match_rmsnorm, "attention": _match_attention}
 
 
 def match(ir):
     """Classify ``ir`` (a ``PortableKernelIR`` from this package or from upstream) into a plan."""
+    ir = adopt(ir)
     operations = ir.operations
     if not operations:
         raise _unsupported("the kernel body is empty")

@@ -121,7 +121,9 @@ int bb200_launch(void* function, const unsigned grid[3], const unsigned block[3]
 int bb200_device_synchronize(void);
 int bb200_stream_synchronize(void* stream);
 
-int bb200_stream_create(void** stream_out); /* non-blocking stream */
+/* Create / destroy a non-blocking stream.  No upstream counterpart: upstream only forwards a stream
+ * handle supplied by the caller (src/baybridge/backends/ptx_exec.py:160-171). */
+int bb200_stream_create(void** stream_out);
 int bb200_stream_destroy(void* stream);
 
 /* CUDA-event timing on the launching stream (upstream times with the host clock only,
@@ -197,7 +199,7 @@ int bb200_attention_fwd(const void* q, const void* k, const void* v, void* out, 
 
 /* Kernels with bounded device-side waits record a give-up in a per-device status word.  This
  * reads and clears it: *status_out = 0 if no wait timed out since the last call.  Synchronises
- * `stream` first. */
+ * `stream` first.  No upstream counterpart (its generated kernels never wait on one another). */
 int bb200_take_device_status(void* stream, int* status_out);
 
 #ifdef __cplusplus

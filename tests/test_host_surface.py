@@ -1,0 +1,258 @@
+"""Host-side mirror of the DSL: tracing, IR parity with upstream listings, compile cache, registry, interop.
+
+These mirror upstream's CPU-only test tiers (tests/test_api.py, test_elementwise.py, test_cache.py,
+test_interop.py, test_backend_ptx_exec.py's fake-DLPack launcher tests) for the b200 path.
+"""
+
+import json
+import sys
+from pathlib import Path
+
+import pytest
+from conftest import GOLDEN, golden_ir
+
+import baybridge_b200 as cute
+from baybridge_b200.backend.matcher import match
+from baybridge_b200.driver import cache_key_for
+from baybridge_b200.portable_ir import PortableKernelIR
+
+TARGET = cute.NvidiaTarget("sm_100a", "8.8")
+
+
+class FakeCudaTensor:
+    """DLPack-looking device tensor (upstream tests/test_backend_ptx_exec.py:2557-2576)."""
+
+    def __init__(self, shape, dtype, ptr=4096, device=(2, 0), stride=None):
+        self.shape, self.dtype, self._ptr, self._device, self._stride = tuple(shape), dtype, ptr, device, stride
+        self.dlpack_streams = []
+
+    def __dlpack__(self, stream=None):
+        self.dlpack_streams.append(stream)
+        return "capsule"
+
+    def __dlpack_device__(self):
+        return self._device
+
+    def data_ptr(self):
+        return self._ptr
+
+    def stride(self):
+        return self._stride
+
+
+def _carriers(ir: dict):
+    names = {"f32": "float32", "bf16": "bfloat16", "f16": "float16"}
+    out = []
+    for argument in ir["arguments"]:
+        if argument["kind"] == "scalar":
+            out.append(0.75)
+        else:
+            out.append(FakeCudaTensor(argument["spec"]["shape"], names[argument["spec"]["dtype"]]))
+    return out
+
+
+def _zoo_kernel(case: str, zoo):
+    parts = case.split("_")
+    table = {
+        "c1": lambda: zoo.make_indexed_add_2d(256, 256),
+        "c3": lambda: zoo.gemm_abt,
+        "c4": lambda: zoo.make_rmsnorm(1e-6),
+        "clamp": lambda: zoo.make_indexed_clamp_scale(512),
+        "masked": lambda: zoo.make_indexed_masked_add(1000),
+        "bin": lambda: zoo.make_indexed_binary(parts[1], int(parts[2])),
+        "un": lambda: zoo.make_indexed_unary(parts[1], int(parts[2])),
+        "rmsnorm": lambda: zoo.make_rmsnorm(None),
+    }
+    if case.startswith("c2_fused_indexed"):
+        return zoo.make_fused_mul_add_indexed(2**28 if "2p28" in case else int(parts[3]))
+    if case.startswith("c2_fused_ssa"):
+        return zoo.fused_mul_add_ssa
+    if case.startswith("ssa_"):
+        return getattr(zoo, "_".join(parts[:-2]))
+    if case.startswith(("c5_", "attn_")):
+        return zoo.attention_causal if "causal" in case else zoo.attention_full
+    if case.startswith("gemm_"):
+        return getattr(zoo, "gemm_" + parts[1])
+    return table[parts[0]]()
+
+
+ALL_IR_CASES = sorted(path.stem[3:] for path in GOLDEN.glob("ir_*.json"))
+
+
+@pytest.mark.parametrize("case", ALL_IR_CASES)
+def test_traced_ir_and_cache_key_equal_upstream(case, zoo, tmp_path):
+    """Same kernel body traced here and by upstream → identical IR dict and identical sha256 cache key."""
+    golden = golden_ir(case)
+    artifact = cute.compile(_zoo_kernel(case, zoo), *_carriers(golden["ir"]), backend="portable", cache_dir=tmp_path, target=TARGET)
+    assert json.loads(json.dumps(artifact.ir.to_dict())) == golden["ir"]
+    assert cache_key_for(artifact.ir, TARGET, "b200") == golden["cache_key_b200_sm100a"]
+    assert PortableKernelIR.from_dict(golden["ir"]).to_dict() == golden["ir"]
+
+
+@pytest.mark.parametrize("case", ALL_IR_CASES)
+def test_matcher_classifies_every_listing(case):
+    plan = match(PortableKernelIR.from_dict(golden_ir(case)["ir"]))
+    if case.startswith(("c3_", "gemm_")):
+        assert plan.kind == "gemm"
+    elif case.startswith(("c4_", "rmsnorm_")):
+        assert plan.kind == "rmsnorm"
+    elif case.startswith(("c5_", "attn_")):
+        assert plan.kind == "attention"
+    else:
+        assert plan.kind == "elementwise" and plan.mode == "flat"  # every zoo body is an index bijection
+
+
+def test_config_plans_carry_the_expected_shapes():
+    gemm = match(PortableKernelIR.from_dict(golden_ir("c3_gemm_abt_8192_bf16")["ir"]))
+    assert (gemm.m, gemm.n, gemm.k, gemm.transpose_a, gemm.transpose_b, gemm.c_dtype) == (8192, 8192, 8192, False, True, "bf16")
+    norm = match(PortableKernelIR.from_dict(golden_ir("c4_rmsnorm_65536x8192_bf16")["ir"]))
+    assert (norm.rows, norm.hidden, norm.gamma_is_full, norm.epsilon) == (65536, 8192, False, 1e-6)
+    attn = match(PortableKernelIR.from_dict(golden_ir("c5_attn_causal_b16s4096h32d128")["ir"]))
+    assert (attn.batch, attn.seq, attn.heads, attn.kv_heads, attn.head_dim, attn.causal) == (16, 4096, 32, 32, 128, True)
+    fused = match(PortableKernelIR.from_dict(golden_ir("c2_fused_indexed_2p28_bf16")["ir"]))
+    assert fused.extent == 2**28 and fused.inputs == (0, 1)  # the repeated load of `a` is merged
+    c1 = match(PortableKernelIR.from_dict(golden_ir("c1_indexed_add_256x256_f32")["ir"]))
+    assert c1.extent == 65536  # (i // 256, i % 256) on a row-major 256x256 tensor is proved to be offset i
+
+
+def test_non_bijective_indexing_is_lowered_literally_and_unknown_ops_are_rejected(tmp_path):
+    @cute.kernel(launch=cute.LaunchConfig(grid=(4, 1, 1), block=(64, 1, 1)))
+    def reverse(src: cute.TensorSpec(shape=(256,), dtype="f32"), dst: cute.TensorSpec(shape=(256,), dtype="f32")):
+        i = cute.block_idx("x") * cute.block_dim("x") + cute.thread_idx("x")
+        dst[255 - i] = src[i]
+
+    artifact = cute.compile(reverse, backend="portable", cache_dir=tmp_path)
+    plan = match(artifact.ir)
+    assert plan.mode == "literal"
+
+    @cute.kernel(launch=cute.LaunchConfig(grid=(2, 2, 1), block=(16, 16, 1)))
+    def add_2d_launch(a: cute.TensorSpec(shape=(32, 32), dtype="f32"), c: cute.TensorSpec(shape=(32, 32), dtype="f32")):
+        col = cute.block_idx("x") * cute.block_dim("x") + cute.thread_idx("x")
+        row = cute.block_idx("y") * cute.block_dim("y") + cute.thread_idx("y")
+        c[row, col] = a[row, col] + 1.0
+
+    assert match(cute.compile(add_2d_launch, backend="portable", cache_dir=tmp_path).ir).mode == "literal"
+    lowered = cute.compile(add_2d_launch, backend="b200", cache_dir=tmp_path)  # lowering + nvcc need no GPU
+    assert "blockIdx.y" in json.loads(lowered.lowered_module.text)["source"]
+
+    @cute.kernel
+    def two_ops(a: cute.TensorSpec(shape=(64, 64), dtype="bf16"), b: cute.TensorSpec(shape=(64, 64), dtype="bf16"),
+                c: cute.TensorSpec(shape=(64, 64), dtype="bf16")):
+        cute.gemm(a, b, c, transpose_b=True)
+        cute.rmsnorm(c, c, a)
+
+    with pytest.raises(cute.BackendNotImplementedError, match="only op"):
+        cute.compile(two_ops, backend="b200", cache_dir=tmp_path)
+
+
+def test_compile_hits_cache_and_writes_manifest(zoo, tmp_path):
+    carriers = _carriers(golden_ir("c2_fused_indexed_4096_bf16")["ir"])
+    kernel = zoo.make_fused_mul_add_indexed(4096)
+    first = cute.compile(kernel, *carriers, backend="b200", cache_dir=tmp_path)
+    second = cute.compile(kernel, *carriers, backend="b200", cache_dir=tmp_path)
+    assert first.cache_key == second.cache_key and not first.from_cache and second.from_cache
+    assert first.artifact_path == tmp_path / "b200" / "sm_100a" / f"{first.cache_key}.json"
+    manifest = json.loads(first.artifact_path.read_text())
+    assert manifest["backend_name"] == "b200" and manifest["ir"] == json.loads(json.dumps(first.ir.to_dict()))
+    assert first.lowered_path.exists() and first.lowered_module.dialect == "b200.plan"
+    other = cute.compile(zoo.make_fused_mul_add_indexed(8192), *[FakeCudaTensor((8192,), "bfloat16")] * 3, backend="b200", cache_dir=tmp_path)
+    assert other.cache_key != first.cache_key  # shapes and launch dims are part of the key
+
+
+def test_registry_and_errors(tmp_path, zoo):
+    assert {"b200", "portable"} <= set(cute.registered_backends())
+    with pytest.raises(cute.CompilationError, match="unknown backend 'ptx_exec'"):
+        cute.compile(zoo.ssa_add, *[FakeCudaTensor((8, 8), "float32")] * 3, backend="ptx_exec", cache_dir=tmp_path)
+    portable = cute.compile(zoo.ssa_add, *[FakeCudaTensor((8, 8), "float32")] * 3, backend="portable", cache_dir=tmp_path)
+    with pytest.raises(cute.BackendNotImplementedError):  # IR-only artifact: nothing to launch, and no CPU runtime
+        portable(*[FakeCudaTensor((8, 8), "float32")] * 3)
+    with pytest.raises(cute.BackendNotImplementedError, match="sm_100a"):
+        cute.compile(zoo.ssa_add, *[FakeCudaTensor((8, 8), "float32")] * 3, backend="b200", cache_dir=tmp_path,
+                     target=cute.NvidiaTarget("sm_80", "8.0"))
+    sentinel = object()
+    cute.register_backend("custom_probe", lambda: None)
+    assert "custom_probe" in cute.registered_backends() and sentinel is not None
+    with pytest.raises(cute.CompilationError):
+        @cute.kernel
+        def branchy(a: cute.TensorSpec(shape=(8,), dtype="f32")):
+            if cute.thread_idx("x") > 0:  # data-dependent Python control flow cannot be traced
+                a[0] = a[0]
+
+        cute.compile(branchy, backend="portable", cache_dir=tmp_path)
+
+
+def test_host_tensors_are_containers_not_a_cpu_runtime():
+    a = cute.tensor([[1, 2, 3], [4, 5, 6]], dtype="f32")
+    assert a.shape == (2, 3) and a.tolist() == [[1, 2, 3], [4, 5, 6]] and a[1, 2] == 6
+    assert cute.tensor([1.5, 2]).dtype == "f32" and cute.tensor([1, 2]).dtype == "index" and cute.tensor([True]).dtype == "i1"
+    with pytest.raises(cute.BackendNotImplementedError):
+        a + a
+    with pytest.raises(cute.BackendNotImplementedError):
+        cute.gemm(a, a, a)
+    bf = cute.tensor([1.00390625, 1.01171875], dtype="bf16")  # ties: RNE on the upper half of the f32 pattern
+    assert list(bf.device_image()) == [0x3F80, 0x3F82]
+    assert cute.Float32(3).value == 3.0 and cute.Int32(2**31 + 5).value == -(2**31) + 5
+
+
+def test_launcher_contract_without_a_device(zoo, tmp_path):
+    """Arity/kwarg checks come first; then the launcher refuses loudly because no CUDA device exists here."""
+    from baybridge_b200.backend import native
+
+    carriers = [FakeCudaTensor((1024,), "float32") for _ in range(3)]
+    artifact = cute.compile(zoo.make_indexed_binary("add", 1024), *carriers, backend="b200", cache_dir=tmp_path)
+    launcher = cute.B200Backend().build_launcher(artifact.ir, TARGET, artifact.lowered_module, artifact.lowered_path)
+    with pytest.raises(TypeError, match="expects 3 arguments, got 2"):
+        launcher(*[cute.from_dlpack(c) for c in carriers[:2]])
+    with pytest.raises(TypeError, match="optional stream="):
+        launcher(*[cute.from_dlpack(c) for c in carriers], block=1)
+    if not native.device_available():
+        with pytest.raises(cute.BackendNotImplementedError, match="CUDA device"):
+            artifact(*carriers)
+    # stream= is forwarded into __dlpack__ when arguments are normalised (upstream compiler.py:63-74)
+    try:
+        artifact(*carriers, stream=77)
+    except cute.BaybridgeError:
+        pass
+    assert 77 in carriers[0].dlpack_streams
+
+
+def test_from_dlpack_handle_fields():
+    handle = cute.from_dlpack(FakeCudaTensor((4, 8), "torch.float16", ptr=16384, stride=(8, 1)), assumed_align=32)
+    assert (handle.shape, handle.dtype, handle.device_type, handle.device_id) == ((4, 8), "f16", 2, 0)
+    assert handle.data_ptr() == 16384 and handle.stride == (8, 1) and handle.assumed_align == 32 and handle.is_contiguous
+    with pytest.raises(TypeError):
+        cute.from_dlpack(object())
+
+
+REFERENCE_SRC = Path("/root/reference/src")
+
+
+@pytest.mark.skipif(not REFERENCE_SRC.exists(), reason="upstream checkout not present on this machine")
+def test_backend_object_is_a_drop_in_for_an_unmodified_upstream_checkout(tmp_path):
+    """Run in a subprocess (both packages cannot share one interpreter's idea of `baybridge`): upstream's own
+    compile() accepts B200Backend() and, after install_into_upstream(), the backend name "b200"."""
+    import subprocess
+
+    script = f"""
+import sys
+sys.path.insert(0, {str(REFERENCE_SRC)!r}); sys.path.insert(0, {str(Path(__file__).resolve().parent.parent)!r})
+import baybridge as bb
+import baybridge_b200
+from baybridge_b200 import B200Backend, install_into_upstream
+
+@bb.kernel
+def gemm_kernel(a: bb.TensorSpec(shape=(256, 128), dtype="bf16"), b: bb.TensorSpec(shape=(512, 128), dtype="bf16"),
+                c: bb.TensorSpec(shape=(256, 512), dtype="bf16")):
+    bb.gemm(a, b, c, transpose_b=True)
+
+target = bb.NvidiaTarget(sm="sm_100a", ptx_version="8.8")
+art = bb.compile(gemm_kernel, backend=B200Backend(), target=target, cache_dir={str(tmp_path)!r})
+assert art.backend_name == "b200" and art.lowered_module.entry_point == "bb200_gemm_bf16", art
+assert art.runtime_callable is not None
+install_into_upstream(bb)
+art2 = bb.compile(gemm_kernel, backend="b200", target=target, cache_dir={str(tmp_path)!r})
+assert art2.cache_key == art.cache_key and art2.from_cache
+print("drop-in ok")
+"""
+    done = subprocess.run([sys.executable, "-c", script], capture_output=True, text=True, timeout=300)
+    assert done.returncode == 0 and "drop-in ok" in done.stdout, done.stderr[-2000:]
