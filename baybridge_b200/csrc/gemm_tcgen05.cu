@@ -19,6 +19,8 @@
 // each operand only a few times.
 #include <cuda_bf16.h>
 
+#include <mutex>
+
 #include "bb200_internal.h"
 #include "bb200_sm100.cuh"
 
@@ -335,4 +337,72 @@ extern "C" int bb200_gemm_bf16(const void* a, const void* b, void* c, int m, int
     if (!status) status = freed;
   }
   return status;
+}
+
+// ---- allocation-free variant -------------------------------------------------------------------------
+// bb200_gemm_bf16 above borrows a stream-ordered workspace (cudaMallocAsync) whenever A arrives stored
+// [k, m].  That is a problem for embedders that must not allocate while they run: an inference server
+// that has already sized its own pools to fill the device (so a late driver allocation can fail or
+// evict), a host framework whose caching allocator is meant to be the only owner of device memory, or
+// a latency-critical loop where an allocation call may stall behind other work on the device.  For
+// them the transposed copy of A goes into the fixed buffer below, which is part of the library image.
+//
+// The buffer is one per GPU for the life of the process (every device that loads this library holds
+// these 32 MiB until exit).  It is shared by every call: calls whose GPU work can overlap (different
+// streams, different host threads) would overwrite each other's copy of A — callers serialise them.
+// Nothing in the buffer has to start at zero: each call rewrites the m*k elements it then reads.
+constexpr size_t kGemmStaticScratchBytes = 32u << 20;  // transposed A of up to 16 Mi bf16 elements
+static __device__ __align__(256) unsigned char g_gemm_static_scratch[kGemmStaticScratchBytes];
+
+namespace {
+
+// In host code `g_gemm_static_scratch` is only a handle for the runtime, not a device address; the
+// address a kernel can use is looked up once per device, with that device current.
+int gemm_static_scratch(void** device_ptr_out) {
+  static void* resolved[64] = {};
+  static std::mutex guard;
+  int device = 0;
+  if (int status = check_runtime(cudaGetDevice(&device), "cudaGetDevice")) return status;
+  if (device < 0 || device >= 64) return fail(BB200_E_UNSUPPORTED_SHAPE, "gemm (no-alloc): device ordinal %d is out of range", device);
+  std::lock_guard<std::mutex> lock(guard);
+  if (!resolved[device]) {
+    void* address = nullptr;
+    if (int status = check_runtime(cudaGetSymbolAddress(&address, g_gemm_static_scratch),
+                                   "cudaGetSymbolAddress(gemm static scratch)"))
+      return status;
+    if (!address) return fail(BB200_E_NO_DRIVER, "gemm (no-alloc): the static scratch buffer has no device address");
+    resolved[device] = address;
+  }
+  *device_ptr_out = resolved[device];
+  return BB200_OK;
+}
+
+}  // namespace
+
+extern "C" int bb200_gemm_bf16_noalloc(const void* a, const void* b, void* c, int m, int n, int k, int transpose_a,
+                                       int transpose_b, bb200_dtype c_dtype, void* stream) {
+  if (!a || !b || !c) return fail(BB200_E_INVALID_ARGUMENT, "gemm (no-alloc): null tensor pointer");
+  if (m <= 0 || n <= 0 || k <= 0) return fail(BB200_E_INVALID_ARGUMENT, "gemm (no-alloc): m, n, k must be > 0 (got %d, %d, %d)", m, n, k);
+  if (c_dtype != BB200_BF16 && c_dtype != BB200_F32) return fail(BB200_E_INVALID_ARGUMENT, "gemm (no-alloc): C must be bf16 or f32");
+  if (k % 8) return fail(BB200_E_UNSUPPORTED_SHAPE, "gemm (no-alloc): k=%d must be a multiple of 8 (16-byte rows for TMA)", k);
+  if (!aligned16(a) || !aligned16(b)) return fail(BB200_E_MISALIGNED, "gemm (no-alloc): A and B must be 16-byte aligned");
+  const bool b_is_kn = !transpose_b;
+  if (b_is_kn && (n % 8)) return fail(BB200_E_UNSUPPORTED_SHAPE, "gemm (no-alloc): n=%d must be a multiple of 8 when B is stored [k, n]", n);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const void* a_mk = a;
+  if (transpose_a) {
+    const size_t needed = (size_t)m * (size_t)k * 2;
+    if (needed > kGemmStaticScratchBytes)
+      return fail(BB200_E_TOO_LARGE,
+                  "gemm (no-alloc): A stored [k, m] needs a %zu-byte transposed copy but the built-in buffer holds %zu bytes "
+                  "(m*k <= %zu); pass A as [m, k] or use bb200_gemm_bf16",
+                  needed, kGemmStaticScratchBytes, kGemmStaticScratchBytes / 2);
+    void* scratch = nullptr;
+    if (int status = gemm_static_scratch(&scratch)) return status;
+    if (int status = launch_transpose(a, scratch, k, m, s)) return status;
+    a_mk = scratch;
+  }
+  if (c_dtype == BB200_BF16)
+    return b_is_kn ? launch_native<__nv_bfloat16, true>(a_mk, b, c, m, n, k, s) : launch_native<__nv_bfloat16, false>(a_mk, b, c, m, n, k, s);
+  return b_is_kn ? launch_native<float, true>(a_mk, b, c, m, n, k, s) : launch_native<float, false>(a_mk, b, c, m, n, k, s);
 }

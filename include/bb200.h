@@ -188,6 +188,24 @@ int bb200_rmsnorm(bb200_dtype dtype, const void* x, const void* gamma, void* out
 int bb200_gemm_bf16(const void* a, const void* b, void* c, int m, int n, int k, int transpose_a, int transpose_b,
                     bb200_dtype c_dtype, void* stream);
 
+/* Same contract and same kernels as bb200_gemm_bf16, for callers that must not allocate device memory
+ * while they run — a server whose own pools already fill the GPU, a framework whose allocator has to
+ * stay the sole owner of device memory, a latency-critical loop that cannot afford a driver
+ * allocation stalling or failing late.  bb200_gemm_bf16 takes a stream-ordered workspace from the
+ * driver when A is stored [k, m]; this entry point puts that transposed copy of A into a 32 MiB
+ * buffer built into the library instead, and performs no cudaMalloc / cudaFree / pool operation of
+ * any kind.  Limits and rules:
+ *   - with transpose_a != 0, m*k must not exceed 16,777,216 elements (32 MiB of bf16); larger requests
+ *     return BB200_E_TOO_LARGE.  With transpose_a == 0 the buffer is not used and any size is accepted.
+ *   - the buffer exists once per GPU and every call uses it, so two calls whose GPU work may overlap
+ *     (different streams or threads) must be serialised by the caller; it keeps the previous call's
+ *     contents between calls, which is harmless because each call overwrites what it reads.
+ *   - the first call on each device looks up the buffer's device address (that device must be
+ *     current); make that first call before starting any stream capture.
+ * This entry point has no counterpart in the upstream package. */
+int bb200_gemm_bf16_noalloc(const void* a, const void* b, void* c, int m, int n, int k, int transpose_a,
+                            int transpose_b, bb200_dtype c_dtype, void* stream);
+
 /* Softmax attention forward.  q/out: [batch, seq, heads, head_dim]; k/v: [batch, seq, kv_heads,
  * head_dim] (heads % kv_heads == 0), all bf16 row-major; lse: fp32 [batch, heads, seq]
  * (identical memory layout to [batch, heads, 1, seq]), natural log.  Scale is fixed at
