@@ -182,3 +182,99 @@ def test_runtime_tensor_arguments_are_staged_and_copied_back(zoo, tmp_path):
     with pytest.warns(RuntimeWarning, match="staging"):
         artifact(a, b, c)
     assert c.tolist() == [x + y for x, y in zip(a.tolist(), b.tolist())]  # upstream tests/test_backend_ptx_exec.py:2660-2677
+
+
+# ---- bodies whose indexing is not the identity: lowered literally (one device thread per traced thread) ----
+def _run_against_oracle(kernel, host_arrays: dict, dtypes: dict, tmp_path, scalars=()):
+    """Compile for b200 with device tensors, run, and compare every tensor with the oracle's interpretation of
+    the very IR that was compiled (bit-exact after one rounding to the storage dtype)."""
+    import baybridge_b200 as cute
+
+    device = {name: to_device(value, dtypes[name]) for name, value in host_arrays.items()}
+    args = list(device.values()) + list(scalars)
+    artifact = cute.compile(kernel, *args, backend="b200", cache_dir=tmp_path)
+    artifact(*args)
+    expected = {name: np.array(value, dtype=np.float64) for name, value in host_arrays.items()}
+    names = [argument.name for argument in artifact.ir.arguments]
+    oracle_args = dict(expected)
+    for name, value in zip(names[len(host_arrays):], scalars):
+        oracle_args[name] = value
+    oracle.run_kernel_ir(artifact.ir.to_dict(), oracle_args)
+    for name in host_arrays:
+        expect_rounded(to_host(device[name]), expected[name], dtypes[name])
+    return artifact
+
+
+def test_literal_lowering_reversed_and_strided_indices(tmp_path):
+    import baybridge_b200 as cute
+
+    n = 1000
+
+    @cute.kernel(launch=cute.LaunchConfig(grid=(8, 1, 1), block=(128, 1, 1)))
+    def reverse_scale(src: cute.Tensor, dst: cute.Tensor):
+        i = cute.block_idx("x") * cute.block_dim("x") + cute.thread_idx("x")
+        inside = i < n
+        value = cute.load(src, (n - 1) - i, predicate=inside, else_value=0.0)
+        cute.store(value * 3.0 - 1.0, dst, i, predicate=inside)
+
+    rng = np.random.default_rng(21)
+    artifact = _run_against_oracle(reverse_scale, {"src": rng.uniform(-1, 1, n).astype(np.float32), "dst": np.zeros(n, np.float32)},
+                                   {"src": "f32", "dst": "f32"}, tmp_path)
+    assert artifact.runtime_callable is not None
+    from baybridge_b200.backend.matcher import match
+
+    assert match(artifact.ir).mode == "literal"
+
+    @cute.kernel(launch=cute.LaunchConfig(grid=(4, 1, 1), block=(64, 1, 1)))
+    def gather_even(src: cute.Tensor, dst: cute.Tensor):
+        i = cute.block_idx("x") * cute.block_dim("x") + cute.thread_idx("x")
+        dst[i] = src[i * 2] + src[i * 2 + 1]
+
+    _run_against_oracle(gather_even, {"src": oracle.bf16_round(rng.standard_normal(512).astype(np.float32)), "dst": np.zeros(256, np.float32)},
+                        {"src": "bf16", "dst": "bf16"}, tmp_path)
+
+
+def test_literal_lowering_two_dimensional_launch(tmp_path):
+    import baybridge_b200 as cute
+
+    rows, cols = 48, 80
+
+    @cute.kernel(launch=cute.LaunchConfig(grid=(5, 3, 1), block=(16, 16, 1)))
+    def saxpy_2d(x: cute.Tensor, y: cute.Tensor, out: cute.Tensor, alpha: float):
+        col = cute.block_idx("x") * cute.block_dim("x") + cute.thread_idx("x")
+        row = cute.block_idx("y") * cute.block_dim("y") + cute.thread_idx("y")
+        out[row, col] = x[row, col] * alpha + y[row, col]
+
+    rng = np.random.default_rng(22)
+    _run_against_oracle(
+        saxpy_2d,
+        {"x": rng.uniform(-1, 1, (rows, cols)).astype(np.float32), "y": rng.uniform(-1, 1, (rows, cols)).astype(np.float32),
+         "out": np.zeros((rows, cols), np.float32)},
+        {"x": "f32", "y": "f32", "out": "f32"}, tmp_path, scalars=(0.1,),  # 0.1 is not an f32: the f64 path keeps it exact
+    )
+
+
+def test_flat_lowering_rank3_digits_and_in_place_update(tmp_path):
+    import baybridge_b200 as cute
+
+    shape = (6, 10, 16)
+    total = 6 * 10 * 16
+
+    @cute.kernel(launch=cute.LaunchConfig(grid=((total + 127) // 128, 1, 1), block=(128, 1, 1)))
+    def rank3_inplace(t: cute.Tensor, bias: cute.Tensor):
+        i = cute.block_idx("x") * cute.block_dim("x") + cute.thread_idx("x")
+        inside = i < total
+        a = i // 160
+        b = (i // 16) % 10
+        c = i % 16
+        value = cute.load(t, (a, b, c), predicate=inside, else_value=0.0)
+        other = cute.load(bias, (a, b, c), predicate=inside, else_value=0.0)
+        cute.store(cute.math.sqrt(value * value + other * other), t, (a, b, c), predicate=inside)
+
+    rng = np.random.default_rng(23)
+    artifact = _run_against_oracle(rank3_inplace, {"t": rng.uniform(0.5, 2, shape).astype(np.float32), "bias": rng.uniform(0.5, 2, shape).astype(np.float32)},
+                                   {"t": "f32", "bias": "f32"}, tmp_path)
+    from baybridge_b200.backend.matcher import match
+
+    plan = match(artifact.ir)
+    assert plan.mode == "flat" and plan.extent == total  # (i//160, (i//16)%10, i%16) on [6,10,16] is proved to be offset i
