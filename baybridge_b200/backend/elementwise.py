@@ -317,7 +317,7 @@ def _skeleton_digest() -> str:
 
 def compile_cubin(source: str) -> Path:
     """``nvcc -cubin`` for sm_100a, cached by the hash of (source, skeleton header, flags)."""
-    key = hashlib.sha256("\n".join([source, _skeleton_digest(), " ".join(GENCODE + NVCC_COMMON)]).encode()).hexdigest()[:32]
+    key = hashlib.sha256("\n".join([source, _skeleton_digest(), " ".join(GENCODE + NVCC_COMMON + ("-fmad=false",))]).encode()).hexdigest()[:32]
     directory = kernel_cache_dir()
     cubin = directory / f"{key}.cubin"
     if cubin.exists() and cubin.stat().st_size:
@@ -326,7 +326,8 @@ def compile_cubin(source: str) -> Path:
     unit = directory / f"{key}.cu"
     unit.write_text(source)
     scratch = directory / f"{key}.{os.getpid()}.tmp"
-    command = [nvcc_path(), *GENCODE, *NVCC_COMMON, "-cubin", "-I", str(CSRC_DIR), str(unit), "-o", str(scratch)]
+    # -fmad=false: the CPU runtime rounds after every multiply and add; a fused multiply-add would round once
+    command = [nvcc_path(), *GENCODE, *NVCC_COMMON, "-fmad=false", "-cubin", "-I", str(CSRC_DIR), str(unit), "-o", str(scratch)]
     done = subprocess.run(command, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     if done.returncode:
         scratch.unlink(missing_ok=True)

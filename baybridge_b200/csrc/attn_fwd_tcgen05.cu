@@ -6,16 +6,20 @@
 // rows are `heads*head_dim` elements apart; TMA reads it through a 3-D map (head_dim*heads, seq,
 // batch) and zero-fills rows past `seq`.
 //
-// One CTA handles one 128-query block of one (batch, head) and walks the key/value blocks of 128
-// keys (only those at or below the diagonal when causal).  192 threads:
-//   warp 0      TMA producer: Q once, then K and V blocks into a 2-stage shared-memory ring.
-//   warp 1      MMA issuer (one elected thread):  S = Q·K^T  (tcgen05.mma, both operands K-major in
-//               shared memory, fp32 S in TMEM, double buffered so the next block's S is computed
-//               while this block's softmax runs), then  O_blk = P·V  (P from shared memory, V
-//               consumed in place as an MN-major operand).
-//   warps 2..5  softmax: thread = query row.  Two passes over S in TMEM (row max; then exp2, row sum
-//               and P written as bf16 into 128-byte-swizzled shared memory), then the running
-//               output is updated in registers:  o = o * 2^(m_old - m_new) + O_blk.
+// One CTA handles TWO 128-query tiles of one (batch, head) and walks the key/value blocks of 128
+// keys once for both (only blocks at or below the diagonal when causal).  320 threads:
+//   warp 0       TMA producer: both Q tiles once, then K and V blocks into a 2-stage ring.
+//   warp 1       MMA issuer (one elected thread).  Per tile t and block j:  S_t = Q_t·K_j^T  into TMEM
+//                (both operands K-major in shared memory), later  O_t += P_t·V_j  with P_t read from
+//                TMEM and V_j consumed in place as an MN-major shared-memory operand.  The issue order
+//                QK0, QK1, {PV0, QK0', PV1, QK1'}… keeps the tensor pipe busy with one tile while the
+//                other tile's softmax runs.
+//   warps 2..5   softmax of tile 0, warps 6..9 softmax of tile 1; thread = query row.  The fp32 score
+//                row is read from TMEM once (128 registers), p = 2^(s·c − m·c) is written back over
+//                the same TMEM columns as packed bf16, and the row sum is kept in fp32.  O stays in
+//                TMEM for the whole walk; it is rescaled (tcgen05.ld / st) only when some row of the
+//                warp sees its running maximum grow by more than 2^8, so most blocks skip it.
+// TMEM (512 columns): S0/P0 [0,128), S1/P1 [128,256), O0 [256,256+D), O1 [384,384+D).
 // Tensor-core bound (4·B·H·D·S(S+1)/2 flops causal); HBM traffic is ~4·B·S·H·D·2 bytes.
 // Head dims other than 64/128 use a plain SIMT kernel below.
 #include <cuda_bf16.h>
@@ -30,25 +34,31 @@ namespace {
 using namespace sm100;
 
 constexpr int BLOCK_M = 128, BLOCK_N = 128;
+constexpr int Q_TILES = 2;                 // query tiles per CTA
 constexpr int KV_STAGES = 2;
-constexpr int THREADS = 192;
-constexpr int SUBTILE_BYTES = 128 * 128;  // [128 rows, 64 bf16] with 128-byte rows
+constexpr int THREADS = 32 * (2 + 4 * Q_TILES);
+constexpr int SUBTILE_BYTES = 128 * 128;   // [128 rows, 64 bf16] with 128-byte rows
+constexpr float RESCALE_THRESHOLD = 8.0f;  // in log2 units: p stays below 2^8 between rescales
 
-enum WaitCode { kWaitQ = 201, kWaitKvEmpty = 202, kWaitK = 203, kWaitV = 204, kWaitSFull = 205, kWaitSEmpty = 206,
-                kWaitP = 207, kWaitO = 208 };
+enum WaitCode { kWaitQ = 201, kWaitKvEmpty = 202, kWaitK = 203, kWaitV = 204, kWaitSReady = 205, kWaitPReady = 206,
+                kWaitODone = 207 };
 
 template <int D> struct Smem {
   static constexpr int DCH = D / 64;                       // 64-column sub-tiles per row block
-  static constexpr int Q_BYTES = DCH * SUBTILE_BYTES;
+  static constexpr int Q_BYTES = DCH * SUBTILE_BYTES;      // one query tile
   static constexpr int K_BYTES = DCH * SUBTILE_BYTES;
   static constexpr int V_BYTES = DCH * SUBTILE_BYTES;
-  static constexpr int P_BYTES = 2 * SUBTILE_BYTES;        // [128 queries, 128 keys] bf16
   static constexpr int Q_OFF = 0;
-  static constexpr int KV_OFF = Q_OFF + Q_BYTES;
-  static constexpr int P_OFF = KV_OFF + KV_STAGES * (K_BYTES + V_BYTES);
-  static constexpr int BAR_OFF = P_OFF + P_BYTES;
+  static constexpr int KV_OFF = Q_OFF + Q_TILES * Q_BYTES;
+  static constexpr int BAR_OFF = KV_OFF + KV_STAGES * (K_BYTES + V_BYTES);
   static constexpr int TOTAL = BAR_OFF + 256 + 1024;       // barriers + alignment slack
 };
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 
 template <int D, bool CAUSAL>
 __global__ void __launch_bounds__(THREADS, 1)
@@ -60,26 +70,32 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   const uint32_t base = (smem_addr(smem_raw) + 1023u) & ~1023u;
   uint8_t* aligned = smem_raw + (base - smem_addr(smem_raw));
   const uint32_t bar_base = base + L::BAR_OFF;
-  // barriers: q_full, k_full[2], v_full[2], kv_empty[2], s_full[2], s_empty[2], p_full, o_full
+  // barriers: q_full, k_full[2], v_full[2], kv_empty[2], s_ready[2], p_ready[2], o_done[2]
   const uint32_t q_full = bar_base;
   auto k_full = [&](int s) { return bar_base + 8u * (1 + s); };
   auto v_full = [&](int s) { return bar_base + 8u * (3 + s); };
   auto kv_empty = [&](int s) { return bar_base + 8u * (5 + s); };
-  auto s_full = [&](int b) { return bar_base + 8u * (7 + b); };
-  auto s_empty = [&](int b) { return bar_base + 8u * (9 + b); };
-  const uint32_t p_full = bar_base + 8u * 11;
-  const uint32_t o_full = bar_base + 8u * 12;
+  auto s_ready = [&](int t) { return bar_base + 8u * (7 + t); };
+  auto p_ready = [&](int t) { return bar_base + 8u * (9 + t); };
+  auto o_done = [&](int t) { return bar_base + 8u * (11 + t); };
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(aligned + L::BAR_OFF + 8 * 13);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int q_blocks = (seq + BLOCK_M - 1) / BLOCK_M;
-  const int q_block = q_blocks - 1 - (int)blockIdx.x;  // longest causal rows first
+  const int pairs = (q_blocks + Q_TILES - 1) / Q_TILES;
+  const int pair = pairs - 1 - (int)blockIdx.x;  // longest causal rows first
   const int head = blockIdx.y, batch = blockIdx.z;
   const int kv_head = head / (heads / kv_heads);
-  const int q0 = q_block * BLOCK_M;
   const int kv_blocks_all = (seq + BLOCK_N - 1) / BLOCK_N;
-  const int kv_blocks = CAUSAL ? min(q_block + 1, kv_blocks_all) : kv_blocks_all;
+  // key/value blocks each query tile needs (0 for a tile that starts past the end of the sequence)
+  int blocks_of[Q_TILES];
+#pragma unroll
+  for (int t = 0; t < Q_TILES; ++t) {
+    const int q_block = pair * Q_TILES + t;
+    blocks_of[t] = q_block >= q_blocks ? 0 : (CAUSAL ? min(q_block + 1, kv_blocks_all) : kv_blocks_all);
+  }
+  const int kv_blocks = max(blocks_of[0], blocks_of[1]);
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -88,12 +104,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       mbar_init(v_full(s), 1);
       mbar_init(kv_empty(s), 1);
     }
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(s_full(b), 1);
-      mbar_init(s_empty(b), 128);
+    for (int t = 0; t < Q_TILES; ++t) {
+      mbar_init(s_ready(t), 1);
+      mbar_init(p_ready(t), 128);
+      mbar_init(o_done(t), 1);
     }
-    mbar_init(p_full, 128);
-    mbar_init(o_full, 1);
     *abort_flag = 0;
     fence_barrier_init();
     fence_proxy_async();
@@ -103,8 +118,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_s = tmem_base;          // two S buffers: columns [0,128) and [128,256)
-  const uint32_t tmem_o = tmem_base + 256;    // O block: columns [256, 256+D)
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
@@ -112,10 +125,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       prefetch_tensormap(&map_q);
       prefetch_tensormap(&map_k);
       prefetch_tensormap(&map_v);
-      mbar_arrive_expect_tx(q_full, L::Q_BYTES);
+      mbar_arrive_expect_tx(q_full, Q_TILES * L::Q_BYTES);
 #pragma unroll
-      for (int c = 0; c < L::DCH; ++c)
-        tma_load_3d(base + L::Q_OFF + c * SUBTILE_BYTES, &map_q, q_full, head * D + c * 64, q0, batch);
+      for (int t = 0; t < Q_TILES; ++t)
+#pragma unroll
+        for (int c = 0; c < L::DCH; ++c)
+          tma_load_3d(base + L::Q_OFF + t * L::Q_BYTES + c * SUBTILE_BYTES, &map_q, q_full, head * D + c * 64,
+                      (pair * Q_TILES + t) * BLOCK_M, batch);
       bool ok = true;
       for (int j = 0; ok && j < kv_blocks; ++j) {
         const int stage = j & 1;
@@ -138,162 +154,171 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     if (elect_one()) {
       constexpr uint32_t idesc_qk = umma_idesc_bf16_f32(BLOCK_M, BLOCK_N);
       constexpr uint32_t idesc_pv = umma_idesc_bf16_f32(BLOCK_M, D, false, true);  // V is MN-major
-      auto issue_qk = [&](int j) {
-        const int stage = j & 1;
-        const uint32_t k_src = base + L::KV_OFF + stage * (L::K_BYTES + L::V_BYTES);
-        const uint32_t acc = tmem_s + (uint32_t)((j & 1) * BLOCK_N);
+      auto issue_qk = [&](int t, int j) {  // S_t = Q_t · K_j^T
+        const uint32_t k_src = base + L::KV_OFF + (j & 1) * (L::K_BYTES + L::V_BYTES);
+        const uint32_t acc = tmem_base + (uint32_t)(t * BLOCK_N);
 #pragma unroll
         for (int c = 0; c < L::DCH; ++c) {
-          const uint64_t desc_q = umma_desc_k_major_sw128(base + L::Q_OFF + c * SUBTILE_BYTES);
+          const uint64_t desc_q = umma_desc_k_major_sw128(base + L::Q_OFF + t * L::Q_BYTES + c * SUBTILE_BYTES);
           const uint64_t desc_k = umma_desc_k_major_sw128(k_src + c * SUBTILE_BYTES);
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
             umma_bf16_ss(acc, umma_desc_advance_k(desc_q, kk * 32), umma_desc_advance_k(desc_k, kk * 32), idesc_qk,
                          (c | kk) != 0 ? 1u : 0u);
         }
-        umma_commit(s_full(j & 1));
+        umma_commit(s_ready(t));
+      };
+      auto issue_pv = [&](int t, int j) {  // O_t (+)= P_t · V_j, P_t packed bf16 in the first 64 columns of S_t
+        const uint32_t v_src = base + L::KV_OFF + (j & 1) * (L::K_BYTES + L::V_BYTES) + L::K_BYTES;
+        const uint64_t desc_v = umma_desc_mn_major_sw128(v_src, SUBTILE_BYTES);
+        const uint32_t p_addr = tmem_base + (uint32_t)(t * BLOCK_N);
+        const uint32_t o_addr = tmem_base + 256u + (uint32_t)(t * 128);
+#pragma unroll
+        for (int kk = 0; kk < BLOCK_N / 16; ++kk)
+          umma_bf16_ts(o_addr, p_addr + (uint32_t)(kk * 8), umma_desc_advance_k(desc_v, kk * 2048), idesc_pv,
+                       (j | kk) != 0 ? 1u : 0u);
+        umma_commit(o_done(t));
       };
       bool ok = mbar_wait(q_full, 0, abort_flag, status_word, kWaitQ);
-      if (ok) ok = mbar_wait(k_full(0), 0, abort_flag, status_word, kWaitK);
+      if (ok && kv_blocks > 0) ok = mbar_wait(k_full(0), 0, abort_flag, status_word, kWaitK);
       if (ok) {
         tcgen05_fence_after();
-        issue_qk(0);
+#pragma unroll
+        for (int t = 0; t < Q_TILES; ++t)
+          if (0 < blocks_of[t]) issue_qk(t, 0);
       }
       for (int j = 0; ok && j < kv_blocks; ++j) {
-        const int stage = j & 1;
-        const uint32_t use_parity = (uint32_t)(j >> 1) & 1u;
-        if (j + 1 < kv_blocks) {
-          // S for the next block goes into the other buffer while this block's softmax runs
-          const int next = j + 1;
-          const uint32_t next_parity = (uint32_t)(next >> 1) & 1u;
-          if (!(ok = mbar_wait(k_full(next & 1), next_parity, abort_flag, status_word, kWaitK))) break;
-          if (!(ok = mbar_wait(s_empty(next & 1), next_parity ^ 1u, abort_flag, status_word, kWaitSEmpty))) break;
-          tcgen05_fence_after();
-          issue_qk(next);
-        }
-        if (!(ok = mbar_wait(p_full, (uint32_t)j & 1u, abort_flag, status_word, kWaitP))) break;
-        if (!(ok = mbar_wait(v_full(stage), use_parity, abort_flag, status_word, kWaitV))) break;
-        tcgen05_fence_after();
-        const uint32_t v_src = base + L::KV_OFF + stage * (L::K_BYTES + L::V_BYTES) + L::K_BYTES;
-        const uint64_t desc_v = umma_desc_mn_major_sw128(v_src, SUBTILE_BYTES);
+        const int stage = j & 1, next = j + 1;
+        if (!(ok = mbar_wait(v_full(stage), (uint32_t)(j >> 1) & 1u, abort_flag, status_word, kWaitV))) break;
+        bool next_k_ready = false;
 #pragma unroll
-        for (int kk = 0; kk < BLOCK_N / 16; ++kk) {
-          const uint64_t desc_p = umma_desc_k_major_sw128(base + L::P_OFF + (kk >> 2) * SUBTILE_BYTES);
-          umma_bf16_ss(tmem_o, umma_desc_advance_k(desc_p, (kk & 3) * 32), umma_desc_advance_k(desc_v, kk * 2048), idesc_pv,
-                       kk != 0 ? 1u : 0u);
+        for (int t = 0; t < Q_TILES; ++t) {
+          if (j < blocks_of[t]) {
+            if (!(ok = mbar_wait(p_ready(t), (uint32_t)j & 1u, abort_flag, status_word, kWaitPReady))) break;
+            tcgen05_fence_after();
+            issue_pv(t, j);
+          }
+          if (next < blocks_of[t]) {
+            if (!next_k_ready) {
+              if (!(ok = mbar_wait(k_full(next & 1), (uint32_t)(next >> 1) & 1u, abort_flag, status_word, kWaitK))) break;
+              tcgen05_fence_after();
+              next_k_ready = true;
+            }
+            issue_qk(t, next);  // overwrites S_t/P_t: ordered after PV_t(j) on the tensor pipe
+          }
         }
-        umma_commit(o_full);
-        umma_commit(kv_empty(stage));
+        if (ok) umma_commit(kv_empty(stage));
       }
     }
   } else {
-    // ---------------- softmax and output accumulation (warps 2..5) ----------------
-    const int quadrant = warp & 3;
-    const int row = quadrant * 32 + lane;   // row of the query block == TMEM lane
+    // ---------------- softmax + epilogue: warps 2..5 own tile 0, warps 6..9 own tile 1 ----------------
+    const int tile = (warp - 2) >> 2;
+    const int quadrant = warp & 3;          // TMEM lanes [32*quadrant, +32) are the ones this warp may touch
+    const int row = quadrant * 32 + lane;   // row of the query tile == TMEM lane
+    const int q0 = (pair * Q_TILES + tile) * BLOCK_M;
     const int query = q0 + row;
+    const int my_blocks = tile == 0 ? blocks_of[0] : blocks_of[1];
     const uint32_t lane_base = (uint32_t)(quadrant * 32) << 16;
-    float o[D];
-#pragma unroll
-    for (int i = 0; i < D; ++i) o[i] = 0.0f;
-    float row_max = -INFINITY, row_sum = 0.0f;
+    const uint32_t s_addr = tmem_base + lane_base + (uint32_t)(tile * BLOCK_N);
+    const uint32_t o_addr = tmem_base + lane_base + 256u + (uint32_t)(tile * 128);
+    float used_max = -INFINITY;             // running maximum (scaled, log2 units) the exponentials refer to
+    float row_sum = 0.0f;
     bool ok = true;
-    for (int j = 0; j < kv_blocks; ++j) {
-      const int buffer = j & 1;
-      const uint32_t use_parity = (uint32_t)(j >> 1) & 1u;
-      ok = mbar_wait(s_full(buffer), use_parity, abort_flag, status_word, kWaitSFull);
+    for (int j = 0; j < my_blocks; ++j) {
+      ok = mbar_wait(s_ready(tile), (uint32_t)j & 1u, abort_flag, status_word, kWaitSReady);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tcgen05_fence_after();
-      const uint32_t s_addr = tmem_s + lane_base + (uint32_t)(buffer * BLOCK_N);
+      uint32_t s[BLOCK_N];
+#pragma unroll
+      for (int chunk = 0; chunk < BLOCK_N / 32; ++chunk)
+        tmem_ld_32x32b_x32(s_addr + (uint32_t)(chunk * 32), *reinterpret_cast<uint32_t(*)[32]>(&s[chunk * 32]));
+      tmem_ld_wait();
       const int key0 = j * BLOCK_N;
-      // a block needs masking when it crosses the causal diagonal or the end of the sequence
-      const bool masked_block = (CAUSAL && key0 + BLOCK_N - 1 > q0) || (key0 + BLOCK_N > seq);
-      const int key_limit = CAUSAL ? min(query, seq - 1) : seq - 1;  // largest key index this row may see
-      // pass 1: row maximum of the scaled scores
+      // only blocks that cross the causal diagonal or the end of the sequence need masking
+      if ((CAUSAL && key0 + BLOCK_N - 1 > q0) || (key0 + BLOCK_N > seq)) {
+        const int key_limit = (CAUSAL ? min(query, seq - 1) : seq - 1) - key0;  // largest visible column
+#pragma unroll
+        for (int i = 0; i < BLOCK_N; ++i)
+          if (i > key_limit) s[i] = 0xff800000u;  // -inf
+      }
       float block_max = -INFINITY;
-#pragma unroll 1
-      for (int chunk = 0; chunk < BLOCK_N / 32; ++chunk) {
-        uint32_t raw[32];
-        tmem_ld_32x32b_x32(s_addr + (uint32_t)(chunk * 32), raw);
-        tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float t = __uint_as_float(raw[i]) * scale_log2e;
-          if (masked_block && key0 + chunk * 32 + i > key_limit) t = -INFINITY;
-          block_max = fmaxf(block_max, t);
-        }
-      }
-      const float new_max = fmaxf(row_max, block_max);
-      const float safe_max = new_max == -INFINITY ? 0.0f : new_max;  // fully masked so far: exp2(-inf - 0) = 0
-      const float alpha = exp2f(row_max - safe_max);                 // row_max = -inf gives 0
-      // pass 2: p = 2^(t - max), row sum, P as bf16 into swizzled shared memory
-      float block_sum = 0.0f;
-#pragma unroll 1
-      for (int chunk = 0; chunk < BLOCK_N / 32; ++chunk) {
-        uint32_t raw[32];
-        tmem_ld_32x32b_x32(s_addr + (uint32_t)(chunk * 32), raw);
-        tmem_ld_wait();
-        uint32_t packed[16];
+      for (int i = 0; i < BLOCK_N; ++i) block_max = fmaxf(block_max, __uint_as_float(s[i]));
+      const float candidate = fmaxf(used_max, block_max * scale_log2e);  // scale > 0 commutes with max
+      // O stays in TMEM; it is rescaled only when some row of this warp outgrows the threshold
+      const bool grow = candidate > used_max + RESCALE_THRESHOLD;        // also true on the first finite block
+      if (__any_sync(0xffffffffu, grow)) {
+        const float alpha = candidate == -INFINITY ? 1.0f : fast_exp2(used_max - candidate);  // used_max = -inf gives 0
+        row_sum *= alpha;
+        used_max = candidate;
+        if (j > 0) {
+          // P·V of the previous block must have landed in O before it is rescaled
+          ok = mbar_wait(o_done(tile), (uint32_t)(j - 1) & 1u, abort_flag, status_word, kWaitODone);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          tcgen05_fence_after();
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float t0 = __uint_as_float(raw[i]) * scale_log2e, t1 = __uint_as_float(raw[i + 1]) * scale_log2e;
-          if (masked_block) {
-            if (key0 + chunk * 32 + i > key_limit) t0 = -INFINITY;
-            if (key0 + chunk * 32 + i + 1 > key_limit) t1 = -INFINITY;
+          for (int chunk = 0; chunk < D / 32; ++chunk) {
+            uint32_t acc[32];
+            tmem_ld_32x32b_x32(o_addr + (uint32_t)(chunk * 32), acc);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) acc[i] = __float_as_uint(__uint_as_float(acc[i]) * alpha);
+            tmem_st_32x32b_x32(o_addr + (uint32_t)(chunk * 32), acc);
           }
-          const float p0 = exp2f(t0 - safe_max), p1 = exp2f(t1 - safe_max);
-          // the row sum uses the bf16-rounded probabilities that the P·V product will see
-          const __nv_bfloat162 pair = __floats2bfloat162_rn(p0, p1);
-          block_sum += __low2float(pair) + __high2float(pair);
-          packed[i >> 1] = *reinterpret_cast<const uint32_t*>(&pair);
         }
-        // 32 keys = four 16-byte chunks of this row; chunk index is XOR-swizzled with (row % 8)
-        const int sub = chunk >> 1;                      // which [128, 64] sub-tile of P
-        const int first = (chunk & 1) * 4;               // first 16-byte chunk within the 128-byte row
-        uint8_t* p_row = aligned + L::P_OFF + sub * SUBTILE_BYTES + row * 128;
-#pragma unroll
-        for (int v = 0; v < 4; ++v)
-          *reinterpret_cast<uint4*>(p_row + (((first + v) ^ (row & 7)) << 4)) =
-              make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
       }
-      // S buffer fully read: hand it back; P written: publish it to the tensor core (async proxy)
-      tcgen05_fence_before();
-      mbar_arrive(s_empty(buffer));
-      fence_proxy_async();
-      mbar_arrive(p_full);
-      row_sum = row_sum * alpha + block_sum;
-      row_max = new_max;
-      // O_blk = P·V, then o = o * alpha + O_blk
-      ok = mbar_wait(o_full, (uint32_t)j & 1u, abort_flag, status_word, kWaitO);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      tcgen05_fence_after();
+      const float shift = used_max == -INFINITY ? 0.0f : -used_max;  // fully masked so far: 2^(-inf) = 0
+      float block_sum = 0.0f;
+      // packed in place: word i/2 of `s` is free once scores i and i+1 have been consumed
 #pragma unroll
-      for (int chunk = 0; chunk < D / 32; ++chunk) {
-        uint32_t raw[32];
-        tmem_ld_32x32b_x32(tmem_o + lane_base + (uint32_t)(chunk * 32), raw);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o[chunk * 32 + i] = fmaf(o[chunk * 32 + i], alpha, __uint_as_float(raw[i]));
+      for (int i = 0; i < BLOCK_N; i += 2) {
+        const float p0 = fast_exp2(fmaf(__uint_as_float(s[i]), scale_log2e, shift));
+        const float p1 = fast_exp2(fmaf(__uint_as_float(s[i + 1]), scale_log2e, shift));
+        block_sum += p0 + p1;
+        const __nv_bfloat162 pair2 = __floats2bfloat162_rn(p0, p1);  // low half = even key
+        s[i >> 1] = *reinterpret_cast<const uint32_t*>(&pair2);
       }
+      row_sum += block_sum;
+      // P overwrites the first 64 columns of this tile's S (each thread only touches its own lane)
+      tmem_st_32x32b_x32(s_addr, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
+      tmem_st_32x32b_x32(s_addr + 32u, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
+      tmem_st_wait();
       tcgen05_fence_before();
+      mbar_arrive(p_ready(tile));
     }
-    if (ok && query < seq) {
+    if (ok && my_blocks > 0) {
+      ok = mbar_wait(o_done(tile), (uint32_t)(my_blocks - 1) & 1u, abort_flag, status_word, kWaitODone);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    if (ok && my_blocks > 0) {
+      tcgen05_fence_after();
       const float inv = row_sum > 0.0f ? 1.0f / row_sum : 0.0f;
       __nv_bfloat16* dst = out + (((size_t)batch * seq + query) * heads + head) * D;
 #pragma unroll
-      for (int v = 0; v < D / 8; ++v) {
-        uint32_t packed[4];
+      for (int chunk = 0; chunk < D / 32; ++chunk) {
+        uint32_t acc[32];
+        tmem_ld_32x32b_x32(o_addr + (uint32_t)(chunk * 32), acc);
+        tmem_ld_wait();
+        if (query < seq) {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const __nv_bfloat162 pair = __floats2bfloat162_rn(o[v * 8 + 2 * i] * inv, o[v * 8 + 2 * i + 1] * inv);
-          packed[i] = *reinterpret_cast<const uint32_t*>(&pair);
+          for (int v = 0; v < 4; ++v) {
+            uint32_t word[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const __nv_bfloat162 pair2 = __floats2bfloat162_rn(__uint_as_float(acc[v * 8 + 2 * i]) * inv,
+                                                                 __uint_as_float(acc[v * 8 + 2 * i + 1]) * inv);
+              word[i] = *reinterpret_cast<const uint32_t*>(&pair2);
+            }
+            *reinterpret_cast<uint4*>(dst + chunk * 32 + v * 8) = make_uint4(word[0], word[1], word[2], word[3]);
+          }
         }
-        *reinterpret_cast<uint4*>(dst + v * 8) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
       }
       // natural-log sum of exponentials of the scaled scores
-      lse[((size_t)batch * heads + head) * seq + query] =
-          row_sum > 0.0f ? (row_max + log2f(row_sum)) * 0.6931471805599453f : -INFINITY;
+      if (query < seq)
+        lse[((size_t)batch * heads + head) * seq + query] =
+            row_sum > 0.0f ? (used_max + log2f(row_sum)) * 0.6931471805599453f : -INFINITY;
     }
   }
 
@@ -301,6 +326,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   tcgen05_fence_before();
   __syncthreads();
   if (*abort_flag != 0) {
+    // a wait was abandoned: give copies that may still be in flight a bounded time to land
     const unsigned long long started = global_timer_ns();
     while (global_timer_ns() - started < 2000000ull) __nanosleep(1000);
     __syncthreads();
@@ -311,6 +337,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     tmem_dealloc(tmem_base, 512);
   }
 }
+
 
 // ---- plain SIMT kernel for head dims the tensor-core kernel does not cover -------------------------
 // One CTA per (query, head, batch); scores live in shared memory (seq <= 8192).
@@ -390,7 +417,8 @@ int launch_tensor(const void* q, const void* k, const void* v, void* out, float*
     configured[device] = true;
   }
   const float scale_log2e = (1.0f / sqrtf((float)D)) * 1.4426950408889634f;
-  dim3 grid((seq + BLOCK_M - 1) / BLOCK_M, heads, batch);
+  const int q_blocks = (seq + BLOCK_M - 1) / BLOCK_M;
+  dim3 grid((q_blocks + Q_TILES - 1) / Q_TILES, heads, batch);
   attn_fwd_kernel<D, CAUSAL><<<grid, THREADS, Smem<D>::TOTAL, stream>>>(
       map_q, map_k, map_v, static_cast<__nv_bfloat16*>(out), lse, seq, heads, kv_heads, scale_log2e, device_status_word());
   return check_launch("attention kernel launch");
