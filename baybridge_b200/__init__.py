@@ -53,7 +53,7 @@ from .dsl import (
     KernelDefinition,
     KernelLaunch,
     acos, arch, asin, atan, atan2, attention, block_dim, block_idx, ceil, copy, cos, dim, erf, exp, exp2, floor,
-    gemm, grid_dim, jit, kernel, lane_id, load, log, log10, log2, make_tensor, math, maximum, minimum, mma,
+    gemm, grid_dim, jit, kernel, lane_id, layernorm, load, log, log10, log2, make_tensor, math, maximum, minimum, mma,
     program_id, rmsnorm, round, rsqrt, sin, sqrt, store, thread_idx, trunc, where,
 )
 from .targets import AMDTarget, NvidiaTarget

@@ -32,7 +32,7 @@ from ..portable_ir import row_major_stride
 from ..scalar_types import DEVICE_NUMPY, byte_width, normalize_dtype_name
 from . import native
 from .elementwise import THREADS, UNROLL, compile_cubin, render
-from .matcher import AttentionPlan, ElementwisePlan, GemmPlan, RmsNormPlan, adopt, match
+from .matcher import AttentionPlan, ElementwisePlan, GemmPlan, LayerNormPlan, RmsNormPlan, adopt, match
 
 _thread_state = threading.local()
 
@@ -109,7 +109,8 @@ class B200Backend:
             )
         else:
             record.update(asdict(plan))
-            record["entry"] = {"gemm": "bb200_gemm_bf16", "rmsnorm": "bb200_rmsnorm", "attention": "bb200_attention_fwd"}[plan.kind]
+            record["entry"] = {"gemm": "bb200_gemm_bf16", "rmsnorm": "bb200_rmsnorm", "layernorm": "bb200_layernorm",
+                               "attention": "bb200_attention_fwd"}[plan.kind]
         text = json.dumps(record, indent=1, sort_keys=True) + "\n"
         return _lowered_module_type()(backend_name=self.name, entry_point=record["entry"], dialect="b200.plan", text=text)
 
@@ -122,7 +123,7 @@ class B200Backend:
         state: dict[str, Any] = {"slots": {}}
         runner = {
             "elementwise": self._elementwise_runner, "gemm": self._gemm_runner,
-            "rmsnorm": self._rmsnorm_runner, "attention": self._attention_runner,
+            "rmsnorm": self._rmsnorm_runner, "layernorm": self._layernorm_runner, "attention": self._attention_runner,
         }[plan.kind](ir, plan, record, state)
         arguments = ir.arguments
 
@@ -277,6 +278,16 @@ class B200Backend:
         def run(pointers, scalars, stream_handle) -> None:
             native.call("bb200_rmsnorm", code, pointers[plan.x], pointers[plan.gamma], pointers[plan.out], plan.rows,
                         plan.hidden, 1 if plan.gamma_is_full else 0, plan.epsilon, stream_handle)
+
+        return run
+
+    def _layernorm_runner(self, ir, plan: LayerNormPlan, record, state):
+        code = native.DTYPE_CODES[plan.dtype]
+
+        def run(pointers, scalars, stream_handle) -> None:
+            native.call("bb200_layernorm", code, pointers[plan.x], pointers[plan.residual], pointers[plan.weight],
+                        pointers[plan.bias], pointers[plan.out], pointers[plan.out_resid], plan.rows, plan.hidden,
+                        1 if plan.weight_is_full else 0, 1 if plan.bias_is_full else 0, plan.epsilon, stream_handle)
 
         return run
 

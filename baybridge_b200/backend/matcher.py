@@ -89,6 +89,23 @@ class RmsNormPlan:
 
 
 @dataclass(frozen=True)
+class LayerNormPlan:
+    x: int
+    residual: int
+    out: int
+    out_resid: int
+    weight: int
+    bias: int
+    rows: int
+    hidden: int
+    weight_is_full: bool
+    bias_is_full: bool
+    epsilon: float
+    dtype: str
+    kind: str = "layernorm"
+
+
+@dataclass(frozen=True)
 class AttentionPlan:
     q: int
     k: int
@@ -186,6 +203,27 @@ def _match_rmsnorm(ir, op) -> RmsNormPlan:
         raise _unsupported(f"rmsnorm hidden size {hidden} must be a multiple of {vector} for {x_spec.dtype}")
     full = gamma_spec.shape == x_spec.shape and len(x_spec.shape) > 1
     return RmsNormPlan(x, out, gamma, x_spec.numel // hidden, hidden, full, float(op.attrs.get("epsilon", 1e-5)), x_spec.dtype)
+
+
+def _match_layernorm(ir, op) -> LayerNormPlan:
+    positions = _argument_positions(ir)
+    (x, xs), (res, rs), (out, os_), (out_resid, ors), (weight, ws), (bias, bs) = (
+        _tensor_arg(ir, positions, name, "layernorm") for name in op.inputs
+    )
+    if not (xs.shape == rs.shape == os_.shape == ors.shape) or not xs.shape:
+        raise _unsupported("layernorm requires x, residual, out and out_resid of equal, non-scalar shape")
+    hidden = xs.shape[-1]
+    for label, spec in (("weight", ws), ("bias", bs)):
+        if spec.shape not in ((hidden,), xs.shape):
+            raise _unsupported(f"layernorm {label} shape must be {(hidden,)} or {xs.shape}")
+    if len({spec.dtype for spec in (xs, rs, os_, ors, ws, bs)}) != 1 or xs.dtype not in FLOAT_DTYPES:
+        raise _unsupported("layernorm requires all tensors of one dtype among f32/bf16/f16")
+    vector = 4 if xs.dtype == "f32" else 8
+    if hidden % vector or hidden > 4096 * vector:
+        raise _unsupported(f"layernorm hidden size {hidden} must be a multiple of {vector} and at most {4096 * vector}")
+    full = lambda spec: spec.shape == xs.shape and len(xs.shape) > 1  # noqa: E731
+    return LayerNormPlan(x, res, out, out_resid, weight, bias, xs.numel // hidden, hidden, full(ws), full(bs),
+                         float(op.attrs.get("epsilon", 1e-5)), xs.dtype)
 
 
 def _match_attention(ir, op) -> AttentionPlan:
@@ -668,7 +706,7 @@ def adopt(ir):
     return ir if isinstance(ir, PortableKernelIR) else PortableKernelIR.from_dict(ir.to_dict())
 
 
-EXPLICIT = {"mma": _match_gemm, "rmsnorm": _match_rmsnorm, "attention": _match_attention}
+EXPLICIT = {"mma": _match_gemm, "rmsnorm": _match_rmsnorm, "layernorm": _match_layernorm, "attention": _match_attention}
 
 
 def match(ir):

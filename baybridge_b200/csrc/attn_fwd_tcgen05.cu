@@ -7,14 +7,16 @@
 // batch) and zero-fills rows past `seq`.
 //
 // One CTA handles TWO 128-query tiles of one (batch, head) and walks the key/value blocks of 128
-// keys once for both (only blocks at or below the diagonal when causal).  320 threads:
+// keys once for both (only blocks at or below the diagonal when causal).  384 threads in three
+// warpgroups; warpgroup 0 gives registers back (setmaxnreg) so the softmax warpgroups can hold a
+// full 128-column score row per thread:
 //   warp 0       TMA producer: both Q tiles once, then K and V blocks into a 2-stage ring.
 //   warp 1       MMA issuer (one elected thread).  Per tile t and block j:  S_t = Q_t·K_j^T  into TMEM
 //                (both operands K-major in shared memory), later  O_t += P_t·V_j  with P_t read from
 //                TMEM and V_j consumed in place as an MN-major shared-memory operand.  The issue order
 //                QK0, QK1, {PV0, QK0', PV1, QK1'}… keeps the tensor pipe busy with one tile while the
 //                other tile's softmax runs.
-//   warps 2..5   softmax of tile 0, warps 6..9 softmax of tile 1; thread = query row.  The fp32 score
+//   warps 4..7   softmax of tile 0, warps 8..11 softmax of tile 1; thread = query row.  The fp32 score
 //                row is read from TMEM once (128 registers), p = 2^(s·c − m·c) is written back over
 //                the same TMEM columns as packed bf16, and the row sum is kept in fp32.  O stays in
 //                TMEM for the whole walk; it is rescaled (tcgen05.ld / st) only when some row of the
@@ -36,7 +38,7 @@ using namespace sm100;
 constexpr int BLOCK_M = 128, BLOCK_N = 128;
 constexpr int Q_TILES = 2;                 // query tiles per CTA
 constexpr int KV_STAGES = 2;
-constexpr int THREADS = 32 * (2 + 4 * Q_TILES);
+constexpr int THREADS = 128 * (1 + Q_TILES);  // warpgroup 0: TMA + MMA warps; warpgroups 1..2: softmax of tile 0 / 1
 constexpr int SUBTILE_BYTES = 128 * 128;   // [128 rows, 64 bf16] with 128-byte rows
 constexpr float RESCALE_THRESHOLD = 8.0f;  // in log2 units: p stays below 2^8 between rescales
 
@@ -119,6 +121,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  if (warp < 4) {
+    // warpgroup 0 (TMA, MMA and two idle warps) hands registers to the softmax warpgroups
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
   if (warp == 0) {
     // ---------------- TMA producer ----------------
     if (elect_one()) {
@@ -210,9 +215,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         if (ok) umma_commit(kv_empty(stage));
       }
     }
+  }
   } else {
-    // ---------------- softmax + epilogue: warps 2..5 own tile 0, warps 6..9 own tile 1 ----------------
-    const int tile = (warp - 2) >> 2;
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
+    // ---------------- softmax + epilogue: warps 4..7 own tile 0, warps 8..11 own tile 1 ----------------
+    const int tile = (warp - 4) >> 2;
     const int quadrant = warp & 3;          // TMEM lanes [32*quadrant, +32) are the ones this warp may touch
     const int row = quadrant * 32 + lane;   // row of the query tile == TMEM lane
     const int q0 = (pair * Q_TILES + tile) * BLOCK_M;
@@ -242,9 +249,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         for (int i = 0; i < BLOCK_N; ++i)
           if (i > key_limit) s[i] = 0xff800000u;  // -inf
       }
-      float block_max = -INFINITY;
+      // four independent chains instead of one 128-long dependency chain
+      float max0 = -INFINITY, max1 = -INFINITY, max2 = -INFINITY, max3 = -INFINITY;
 #pragma unroll
-      for (int i = 0; i < BLOCK_N; ++i) block_max = fmaxf(block_max, __uint_as_float(s[i]));
+      for (int i = 0; i < BLOCK_N; i += 4) {
+        max0 = fmaxf(max0, __uint_as_float(s[i]));
+        max1 = fmaxf(max1, __uint_as_float(s[i + 1]));
+        max2 = fmaxf(max2, __uint_as_float(s[i + 2]));
+        max3 = fmaxf(max3, __uint_as_float(s[i + 3]));
+      }
+      const float block_max = fmaxf(fmaxf(max0, max1), fmaxf(max2, max3));
       const float candidate = fmaxf(used_max, block_max * scale_log2e);  // scale > 0 commutes with max
       // O stays in TMEM; it is rescaled only when some row of this warp outgrows the threshold
       const bool grow = candidate > used_max + RESCALE_THRESHOLD;        // also true on the first finite block
@@ -270,17 +284,21 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         }
       }
       const float shift = used_max == -INFINITY ? 0.0f : -used_max;  // fully masked so far: 2^(-inf) = 0
-      float block_sum = 0.0f;
+      float sum0 = 0.0f, sum1 = 0.0f, sum2 = 0.0f, sum3 = 0.0f;
       // packed in place: word i/2 of `s` is free once scores i and i+1 have been consumed
 #pragma unroll
-      for (int i = 0; i < BLOCK_N; i += 2) {
+      for (int i = 0; i < BLOCK_N; i += 4) {
         const float p0 = fast_exp2(fmaf(__uint_as_float(s[i]), scale_log2e, shift));
         const float p1 = fast_exp2(fmaf(__uint_as_float(s[i + 1]), scale_log2e, shift));
-        block_sum += p0 + p1;
-        const __nv_bfloat162 pair2 = __floats2bfloat162_rn(p0, p1);  // low half = even key
-        s[i >> 1] = *reinterpret_cast<const uint32_t*>(&pair2);
+        const float p2 = fast_exp2(fmaf(__uint_as_float(s[i + 2]), scale_log2e, shift));
+        const float p3 = fast_exp2(fmaf(__uint_as_float(s[i + 3]), scale_log2e, shift));
+        sum0 += p0; sum1 += p1; sum2 += p2; sum3 += p3;
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(p0, p1);  // low half = even key
+        const __nv_bfloat162 hi = __floats2bfloat162_rn(p2, p3);
+        s[i >> 1] = *reinterpret_cast<const uint32_t*>(&lo);
+        s[(i >> 1) + 1] = *reinterpret_cast<const uint32_t*>(&hi);
       }
-      row_sum += block_sum;
+      row_sum += (sum0 + sum1) + (sum2 + sum3);
       // P overwrites the first 64 columns of this tile's S (each thread only touches its own lane)
       tmem_st_32x32b_x32(s_addr, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
       tmem_st_32x32b_x32(s_addr + 32u, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));

@@ -444,6 +444,23 @@ def rmsnorm(x: Any, out: Any, gamma: Any, *, epsilon: float = 1e-5) -> Any:
     return out
 
 
+def layernorm(x: Any, residual: Any, out: Any, out_resid: Any, weight: Any, bias: Any, *, epsilon: float = 1e-5) -> Any:
+    """``out_resid = x + residual``; ``out = (out_resid - mean) / sqrt(var + epsilon) * weight + bias`` over the last axis."""
+    _all_traced((x, residual, out, out_resid, weight, bias), "layernorm")
+    if not (x.spec.shape == residual.spec.shape == out.spec.shape == out_resid.spec.shape):
+        raise ValueError("baybridge.layernorm requires x, residual, out, and out_resid to have matching shapes")
+    if x.ndim < 1:
+        raise ValueError("baybridge.layernorm requires rank >= 1 tensors")
+    hidden = x.spec.shape[-1]
+    for name, value in (("weight", weight), ("bias", bias)):
+        if value.spec.shape not in {(hidden,), x.spec.shape}:
+            raise ValueError(f"baybridge.layernorm expects {name} shape {(hidden,)} or {x.spec.shape}, got {value.spec.shape}")
+    if any(value.spec.dtype != x.spec.dtype for value in (residual, out, out_resid, weight, bias)):
+        raise ValueError("baybridge.layernorm requires matching tensor dtypes")
+    require_builder().emit_void("layernorm", x, residual, out, out_resid, weight, bias, attrs={"epsilon": float(epsilon)})
+    return out
+
+
 def attention(q: Any, k: Any, v: Any, out: Any, lse: Any, *, causal: bool = False) -> Any:
     """Softmax attention on ``[batch, seq, heads, head_dim]`` tensors, scale ``1/sqrt(head_dim)``;
     ``lse`` (``[batch, heads, 1, seq]`` or ``[batch, heads, seq]``) receives the natural-log row sums."""

@@ -180,6 +180,16 @@ int bb200_elementwise_mul_add(bb200_dtype dtype, const void* a, const void* b, v
 int bb200_rmsnorm(bb200_dtype dtype, const void* x, const void* gamma, void* out, size_t rows, size_t hidden,
                   int gamma_is_full, float epsilon, void* stream);
 
+/* mixed = x + residual; out_resid = mixed; out = (mixed - mean) / sqrt(var + eps) * weight + bias, with mean and
+ * (biased) variance over the last axis in fp32 and one rounding per output.  x/residual/out/out_resid: [rows, hidden]
+ * row-major; weight and bias: [hidden] (…_is_full = 0) or [rows, hidden] (…_is_full = 1).  dtype bf16 / f16 / f32;
+ * hidden a multiple of 8 (16-bit) or 4 (f32) and at most 32768 (16-bit) / 16384 (f32).  Replaces launch_<kernel> of
+ * the LayerNorm template (src/baybridge/backends/hipkittens_exec.py:1046-1103; semantics
+ * src/baybridge/frontend.py:3754-3793). */
+int bb200_layernorm(bb200_dtype dtype, const void* x, const void* residual, const void* weight, const void* bias, void* out,
+                    void* out_resid, size_t rows, size_t hidden, int weight_is_full, int bias_is_full, float epsilon,
+                    void* stream);
+
 /* C[m, n] = sum_k A'[m, k] * B'[k, n]; A' = A or A^T, B' = B or B^T per the transpose flags;
  * A, B bf16 row-major as stored ([m,k] or [k,m]; [k,n] or [n,k]); C row-major [m, n] of
  * c_dtype bf16 or f32; fp32 accumulation on tcgen05 tensor cores; C is overwritten.

@@ -15,7 +15,7 @@ What it restates (numpy float64, following upstream's CPU reference runtime):
   Values are Python-float (f64) semantics and are NEVER rounded to the tensor
   dtype, exactly like ``RuntimeTensor.__setitem__`` (``runtime.py:459-462``).
 * ``gemm``            — ``frontend.py:3709-3716`` (C is overwritten, f64 accumulate).
-* ``rmsnorm``         — ``frontend.py:3845-3852``.
+* ``rmsnorm``         — ``frontend.py:3845-3852``;  ``layernorm`` — ``frontend.py:3775-3793``.
 * ``attention``       — ``frontend.py:3903-3937`` including masked scores
   contributing weight 0 and ``lse = -inf`` when the row norm is 0.
 
@@ -233,6 +233,16 @@ def rmsnorm(x: np.ndarray, gamma: np.ndarray, epsilon: float = 1e-5) -> np.ndarr
         raise ValueError(f"rmsnorm expects gamma shape {(hidden,)} or {x.shape}, got {gamma.shape}")
     mean_square = np.sum(x * x, axis=-1, keepdims=True) / float(hidden)
     return x * (1.0 / np.sqrt(mean_square + float(epsilon))) * gamma
+
+
+def layernorm(x: np.ndarray, residual: np.ndarray, weight: np.ndarray, bias: np.ndarray,
+              epsilon: float = 1e-5) -> tuple[np.ndarray, np.ndarray]:
+    """Upstream ``frontend.py:3754-3793``: returns (out, out_resid); biased variance, f64 throughout."""
+    mixed = np.asarray(x, dtype=F64) + np.asarray(residual, dtype=F64)
+    mean = mixed.sum(axis=-1, keepdims=True) / float(mixed.shape[-1])
+    variance = ((mixed - mean) ** 2).sum(axis=-1, keepdims=True) / float(mixed.shape[-1])
+    out = ((mixed - mean) / np.sqrt(variance + float(epsilon))) * np.asarray(weight, dtype=F64) + np.asarray(bias, dtype=F64)
+    return out, mixed
 
 
 def attention(q: np.ndarray, k: np.ndarray, v: np.ndarray, *, causal: bool = False) -> tuple[np.ndarray, np.ndarray]:

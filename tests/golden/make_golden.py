@@ -281,6 +281,27 @@ def main() -> None:
         {"x": (bf16_round(x3), "bf16"), "out": (np.zeros((2, 4, 128)), "bf16"), "gamma": (bf16_round(g3), "bf16")},
         ["out"],
     )
+    # tests/test_backend_hipkittens_exec_norm_attention.py:115-133 — LayerNorm with fused residual add
+    xl = np.array([[[((bt * 4 + row) * 128 + col) % 17 / 8.0 for col in range(128)] for row in range(4)] for bt in range(2)], dtype=np.float32)
+    rl = np.array([[[((bt * 4 + row) * 128 + col) % 11 / 16.0 for col in range(128)] for row in range(4)] for bt in range(2)], dtype=np.float32)
+    wl = np.array([1.0 + ((col % 7) / 64.0) for col in range(128)], dtype=np.float32)
+    bl = np.array([((col % 5) - 2) / 32.0 for col in range(128)], dtype=np.float32)
+    run_case(
+        "layernorm_2x4x128_bf16",
+        zoo.layernorm_kernel,
+        {"x": (bf16_round(xl), "bf16"), "residual": (bf16_round(rl), "bf16"), "out": (np.zeros((2, 4, 128)), "bf16"),
+         "out_resid": (np.zeros((2, 4, 128)), "bf16"), "weight": (bf16_round(wl), "bf16"), "bias": (bf16_round(bl), "bf16")},
+        ["out", "out_resid"],
+    )
+    rng_ln = np.random.default_rng(1006)
+    run_case(
+        "layernorm_5x256_f32",
+        zoo.layernorm_kernel,
+        {"x": (rng_ln.standard_normal((5, 256)).astype(np.float32), "f32"), "residual": (rng_ln.standard_normal((5, 256)).astype(np.float32), "f32"),
+         "out": (np.zeros((5, 256)), "f32"), "out_resid": (np.zeros((5, 256)), "f32"),
+         "weight": (rng_ln.uniform(0.5, 1.5, 256).astype(np.float32), "f32"), "bias": (rng_ln.uniform(-1, 1, 256).astype(np.float32), "f32")},
+        ["out", "out_resid"],
+    )
     dump_ir(
         "c4_rmsnorm_65536x8192_bf16",
         zoo.make_rmsnorm(1e-6),

@@ -209,6 +209,13 @@ def build_zoo(cute) -> SimpleNamespace:
     zoo.make_rmsnorm = make_rmsnorm
 
     @cute.kernel
+    def layernorm_kernel(x: cute.Tensor, residual: cute.Tensor, out: cute.Tensor, out_resid: cute.Tensor,
+                         weight: cute.Tensor, bias: cute.Tensor):
+        cute.layernorm(x, residual, out, out_resid, weight, bias)
+
+    zoo.layernorm_kernel = layernorm_kernel
+
+    @cute.kernel
     def attention_full(q: cute.Tensor, k: cute.Tensor, v: cute.Tensor, out: cute.Tensor, lse: cute.Tensor):
         cute.attention(q, k, v, out, lse)
 

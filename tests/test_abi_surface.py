@@ -19,7 +19,7 @@ def declared_symbols() -> list[str]:
 def test_header_declares_the_expected_families():
     names = declared_symbols()
     for required in ("bb200_init", "bb200_module_load", "bb200_launch", "bb200_stream_synchronize", "bb200_event_elapsed_ms",
-                     "bb200_tensormap_encode_2d", "bb200_elementwise_binary", "bb200_elementwise_mul_add", "bb200_rmsnorm",
+                     "bb200_tensormap_encode_2d", "bb200_elementwise_binary", "bb200_elementwise_mul_add", "bb200_rmsnorm", "bb200_layernorm",
                      "bb200_gemm_bf16", "bb200_attention_fwd", "bb200_last_error"):
         assert required in names
 

@@ -62,6 +62,7 @@ def _zoo_kernel(case: str, zoo):
         "bin": lambda: zoo.make_indexed_binary(parts[1], int(parts[2])),
         "un": lambda: zoo.make_indexed_unary(parts[1], int(parts[2])),
         "rmsnorm": lambda: zoo.make_rmsnorm(None),
+        "layernorm": lambda: zoo.layernorm_kernel,
     }
     if case.startswith("c2_fused_indexed"):
         return zoo.make_fused_mul_add_indexed(2**28 if "2p28" in case else int(parts[3]))
@@ -96,6 +97,8 @@ def test_matcher_classifies_every_listing(case):
         assert plan.kind == "gemm"
     elif case.startswith(("c4_", "rmsnorm_")):
         assert plan.kind == "rmsnorm"
+    elif case.startswith("layernorm_"):
+        assert plan.kind == "layernorm"
     elif case.startswith(("c5_", "attn_")):
         assert plan.kind == "attention"
     else:

@@ -13,7 +13,7 @@ TIGHT = 1e-12  # f64 vs f64; only summation order differs
 
 
 def _kernel_cases() -> list[str]:
-    explicit = ("c3_", "c4_", "c5_", "gemm_", "rmsnorm_", "attn_")
+    explicit = ("c3_", "c4_", "c5_", "gemm_", "rmsnorm_", "layernorm_", "attn_")
     return [case for case in golden_cases() if not case.startswith(explicit)]
 
 
@@ -80,6 +80,15 @@ def test_rmsnorm_matches_upstream(case: str):
     epsilon = golden_ir(case)["ir"]["operations"][0]["attrs"]["epsilon"]
     got = oracle.rmsnorm(vec["in_x"], vec["in_gamma"], epsilon)
     np.testing.assert_allclose(got, vec["out_out"], rtol=TIGHT, atol=0)
+
+
+@pytest.mark.parametrize("case", golden_cases("layernorm_"))
+def test_layernorm_matches_upstream(case: str):
+    vec = golden_vec(case)
+    epsilon = golden_ir(case)["ir"]["operations"][0]["attrs"]["epsilon"]
+    out, mixed = oracle.layernorm(vec["in_x"], vec["in_residual"], vec["in_weight"], vec["in_bias"], epsilon)
+    np.testing.assert_allclose(out, vec["out_out"], rtol=1e-11, atol=1e-13)
+    np.testing.assert_allclose(mixed, vec["out_out_resid"], rtol=TIGHT, atol=0)
 
 
 @pytest.mark.parametrize("case", golden_cases("c5_") + golden_cases("attn_"))
