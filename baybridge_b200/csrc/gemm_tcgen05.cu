@@ -19,6 +19,8 @@
 // each operand only a few times.
 #include <cuda_bf16.h>
 
+#include <stdlib.h>
+
 #include <mutex>
 
 #include "bb200_internal.h"
@@ -38,18 +40,18 @@ constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
 constexpr int ACC_COLUMNS = BN;            // fp32 accumulator: 128 lanes x 256 columns
 constexpr int TMEM_COLUMNS = 2 * ACC_COLUMNS;
 constexpr int THREADS = 192;
-constexpr int GROUP_M = 8;                 // rasterisation: tiles advance down 8 M-blocks before moving in N
+constexpr int DEFAULT_GROUP_M = 16;        // rasterisation: tiles advance down this many M-blocks before moving in N
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
 
 enum WaitCode { kWaitEmpty = 101, kWaitFull = 102, kWaitAccEmpty = 103, kWaitAccFull = 104 };
 
 struct TileCoord { int m_block, n_block; };
 
-__device__ __forceinline__ TileCoord tile_coord(int tile, int m_blocks, int n_blocks) {
-  const int group_size = GROUP_M * n_blocks;
+__device__ __forceinline__ TileCoord tile_coord(int tile, int m_blocks, int n_blocks, int group_m) {
+  const int group_size = group_m * n_blocks;
   const int group = tile / group_size;
-  const int first_m = group * GROUP_M;
-  const int rows = min(GROUP_M, m_blocks - first_m);
+  const int first_m = group * group_m;
+  const int rows = min(group_m, m_blocks - first_m);
   const int within = tile - group * group_size;
   return {first_m + within % rows, within / rows};
 }
@@ -92,7 +94,7 @@ template <> __device__ __forceinline__ void store_chunk<float>(float* row_ptr, c
 template <typename OutT, bool B_MN>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_abt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, OutT* __restrict__ c,
-                int m, int n, int k, int* status_word) {
+                int m, int n, int k, int group_m, int* status_word) {
   extern __shared__ uint8_t smem_raw[];
   // operand tiles need 1024-byte alignment for the 128-byte swizzle pattern
   const uint32_t smem_base = (smem_addr(smem_raw) + 1023u) & ~1023u;
@@ -141,7 +143,7 @@ gemm_abt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; ok && tile < tiles; tile += gridDim.x) {
-        const TileCoord coord = tile_coord(tile, m_blocks, n_blocks);
+        const TileCoord coord = tile_coord(tile, m_blocks, n_blocks, group_m);
         for (int kb = 0; kb < k_blocks; ++kb) {
           // a fresh barrier's "previous phase" counts as complete: waiting on parity^1 passes at once
           if (!(ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, status_word, kWaitEmpty))) break;
@@ -199,7 +201,7 @@ gemm_abt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     int local_tile = 0;
     bool ok = true;
     for (int tile = blockIdx.x; ok && tile < tiles; tile += gridDim.x, ++local_tile) {
-      const TileCoord coord = tile_coord(tile, m_blocks, n_blocks);
+      const TileCoord coord = tile_coord(tile, m_blocks, n_blocks, group_m);
       const int buffer = local_tile & 1;
       const uint32_t acc_phase = (uint32_t)(local_tile >> 1) & 1u;
       ok = mbar_wait(acc_full_bar(buffer), acc_phase, abort_flag, status_word, kWaitAccFull);
@@ -276,6 +278,19 @@ int cached_sm_count(int device) {
   return counts[device];
 }
 
+// Tiles that run concurrently (148 consecutive tile ids) cover group_m M-blocks x 148/group_m N-blocks;
+// 16 keeps that footprint (A rows + B rows of one wave) inside the 126 MB L2 for K up to 8192.
+// BB200_GEMM_GROUP_M overrides it for tuning runs.
+int raster_group_m() {
+  static int value = 0;
+  if (value == 0) {
+    const char* text = getenv("BB200_GEMM_GROUP_M");
+    const int parsed = text ? atoi(text) : 0;
+    value = parsed > 0 && parsed <= 1024 ? parsed : DEFAULT_GROUP_M;
+  }
+  return value;
+}
+
 // b_is_kn: B is stored [k, n] (n contiguous) and consumed as an MN-major operand; otherwise [n, k].
 template <typename OutT, bool B_MN>
 int launch_native(const void* a_mk, const void* b, void* c, int m, int n, int k, cudaStream_t stream) {
@@ -297,7 +312,7 @@ int launch_native(const void* a_mk, const void* b, void* c, int m, int n, int k,
   if (sms <= 0) return fail(BB200_E_NO_DRIVER, "gemm: could not query the SM count");
   const int tiles = ((m + BM - 1) / BM) * ((n + BN - 1) / BN);
   const int grid = tiles < sms ? tiles : sms;
-  gemm_abt_kernel<OutT, B_MN><<<grid, THREADS, SMEM_BYTES, stream>>>(map_a, map_b, static_cast<OutT*>(c), m, n, k, device_status_word());
+  gemm_abt_kernel<OutT, B_MN><<<grid, THREADS, SMEM_BYTES, stream>>>(map_a, map_b, static_cast<OutT*>(c), m, n, k, raster_group_m(), device_status_word());
   return check_launch("gemm kernel launch");
 }
 

@@ -42,6 +42,15 @@ for entry in (str(ROOT), str(ROOT / "tests")):
         sys.path.insert(0, entry)
 
 L2_FLUSH_BYTES = 256 << 20
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel at the full-size
+# workload, from one-pass `ncu --metrics dram__bytes_read.sum,dram__bytes_write.sum --clock-control none`
+# captures of this script (commands and figures in profiles/); None for other sizes.
+MEASURED_DRAM_TRAFFIC = {
+    ("fused_mul_add", 2**28): 1.07e9 + 497.2e6,
+    ("rmsnorm", 65536): 1.07e9 + 1.02e9,
+    ("gemm", 8192): 1.39e9 + 127.5e6,
+    ("attention", 16): 1.61e9 + 570.5e6,
+}
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
@@ -152,6 +161,9 @@ class Workload:
     def shrink(self) -> None:
         raise NotImplementedError
 
+    def size_key(self) -> int:
+        raise NotImplementedError
+
 
 class FusedMulAdd(Workload):
     name, unit, bound = "fused_mul_add", "GB/s", "hbm"
@@ -159,6 +171,9 @@ class FusedMulAdd(Workload):
 
     def shrink(self):
         self.n = 2**26  # 400 MB working set
+
+    def size_key(self):
+        return self.n
 
     def work_per_step(self) -> float:
         return 6.0 * self.n  # read a, read b, write c at 2 B each
@@ -230,6 +245,9 @@ class RmsNorm(Workload):
     def shrink(self):
         self.rows = 8192  # 268 MB working set
 
+    def size_key(self):
+        return self.rows
+
     def work_per_step(self) -> float:
         return 2.0 * self.rows * self.hidden * 2 + self.hidden * 2
 
@@ -282,6 +300,9 @@ class Gemm(Workload):
 
     def shrink(self):
         self.m = self.n = self.k = 4096
+
+    def size_key(self):
+        return self.m
 
     def work_per_step(self) -> float:
         return 2.0 * self.m * self.n * self.k
@@ -336,6 +357,9 @@ class Attention(Workload):
 
     def shrink(self):
         self.batch = 2
+
+    def size_key(self):
+        return self.batch
 
     def work_per_step(self) -> float:
         return 4.0 * self.batch * self.heads * self.dim * self.seq * (self.seq + 1) / 2
@@ -578,8 +602,12 @@ def main() -> None:
         roofline = {
             "bound": workload.bound, "achieved": per_rank, "peak": peak, "unit": peak_unit, "frac": per_rank / peak,
             "peak_source": f"{peak_source} ({'hbm_gbs' if workload.bound == 'hbm' else 'bf16_tflops burst'})",
-            "traffic": None, "kernel_ms": ms_per_step,
+            "traffic": MEASURED_DRAM_TRAFFIC.get((workload.name, workload.size_key())), "kernel_ms": ms_per_step,
         }
+        if workload.bound == "tensor":
+            roofline["frac_of_sustained_peak"] = per_rank / float(peaks.get("bf16_tflops_sustained", peak))
+        else:
+            roofline["algorithmic_bytes"] = workload.work_per_step()
         line = {
             "metric": METRIC[workload.name], "value": value, "unit": workload.unit, "n_gpus": world, "steps": steps,
             "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
