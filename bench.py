@@ -42,6 +42,7 @@ for entry in (str(ROOT), str(ROOT / "tests")):
         sys.path.insert(0, entry)
 
 L2_FLUSH_BYTES = 256 << 20
+E2E_CHUNKS = 8  # chunks of the host pipeline (copy-in / kernel / copy-out overlap)
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel at the full-size
 # workload, from one-pass `ncu --metrics dram__bytes_read.sum,dram__bytes_write.sum --clock-control none`
 # captures of this script (commands and figures in profiles/); None for other sizes.
@@ -152,8 +153,12 @@ class Workload:
     def output(self):
         raise NotImplementedError
 
-    def e2e_step(self, torch) -> None:
+    def e2e_setup(self, cute, zoo, cache_dir: str) -> None:
         raise NotImplementedError
+
+    def e2e_step(self, torch) -> None:
+        """Host → device → kernel → host through the public host pipeline (copies overlapped in chunks)."""
+        self.pipeline.run()
 
     def config(self) -> dict:
         raise NotImplementedError
@@ -201,12 +206,11 @@ class FusedMulAdd(Workload):
     def output(self):
         return self.c
 
-    def e2e_step(self, torch):
-        self.a.copy_(self.a_host, non_blocking=True)
-        self.b.copy_(self.b_host, non_blocking=True)
-        self.artifact(*self.args, stream=self.stream)
-        self.c_host.copy_(self.c, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+    def e2e_setup(self, cute, zoo, cache_dir):
+        from baybridge_b200.host_pipeline import HostPipeline
+
+        self.pipeline = HostPipeline(lambda rows: zoo.make_fused_mul_add_indexed(rows), [self.a_host, self.b_host, self.c_host],
+                                     chunks=E2E_CHUNKS, cache_dir=cache_dir)
 
     def config(self):
         return {"workload": f"fused_mul_add c=a*b+a bf16 {self.n} (2^{self.n.bit_length() - 1}) elements per GPU (6 B/element), indexed IR form",
@@ -273,11 +277,12 @@ class RmsNorm(Workload):
     def output(self):
         return self.out
 
-    def e2e_step(self, torch):
-        self.x.copy_(self.x_host, non_blocking=True)
-        self.artifact(*self.args, stream=self.stream)
-        self.out_host.copy_(self.out, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+    def e2e_setup(self, cute, zoo, cache_dir):
+        from baybridge_b200.host_pipeline import HostPipeline
+
+        self.w_host = self.w.cpu().pin_memory()
+        self.pipeline = HostPipeline(lambda rows: zoo.make_rmsnorm(1e-6), [self.x_host, self.out_host, self.w_host],
+                                     chunks=E2E_CHUNKS, cache_dir=cache_dir)
 
     def config(self):
         return {"workload": f"rmsnorm bf16 [{self.rows}, {self.hidden}] per GPU, weight [{self.hidden}], eps 1e-6",
@@ -330,12 +335,11 @@ class Gemm(Workload):
     def output(self):
         return self.c
 
-    def e2e_step(self, torch):
-        self.a.copy_(self.a_host, non_blocking=True)
-        self.b.copy_(self.b_host, non_blocking=True)
-        self.artifact(*self.args, stream=self.stream)
-        self.c_host.copy_(self.c, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+    def e2e_setup(self, cute, zoo, cache_dir):
+        from baybridge_b200.host_pipeline import HostPipeline
+
+        self.pipeline = HostPipeline(lambda rows: zoo.gemm_abt, [self.a_host, self.b_host, self.c_host],
+                                     chunks=E2E_CHUNKS, cache_dir=cache_dir)
 
     def config(self):
         return {"workload": f"gemm C=A·B^T bf16 M=N=K={self.m} per GPU, fp32 accumulate, bf16 out",
@@ -387,12 +391,14 @@ class Attention(Workload):
     def output(self):
         return self.o
 
-    def e2e_step(self, torch):
-        for device, host in zip((self.q, self.k, self.v), self.hosts):
-            device.copy_(host, non_blocking=True)
-        self.artifact(*self.args, stream=self.stream)
-        self.o_host.copy_(self.o, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+    def e2e_setup(self, cute, zoo, cache_dir):
+        import torch
+
+        from baybridge_b200.host_pipeline import HostPipeline
+
+        self.lse_host = torch.empty((self.batch, self.heads, 1, self.seq), dtype=torch.float32).pin_memory()
+        self.pipeline = HostPipeline(lambda rows: zoo.attention_causal, [*self.hosts, self.o_host, self.lse_host],
+                                     chunks=min(E2E_CHUNKS, self.batch), cache_dir=cache_dir)
 
     def config(self):
         return {"workload": f"causal attention fwd bf16 B{self.batch} H{self.heads} S{self.seq} D{self.dim} per GPU (layout [B,S,H,D]), causal FLOPs",
@@ -559,7 +565,9 @@ def main() -> None:
     per_rank = workload.work_per_step() / (ms_per_step * 1e-3) / scale
     value = per_rank * world
 
-    # end to end: pinned host inputs → device, kernel through the public artifact call, result → host
+    # end to end: pinned host inputs → device, kernel through the public host pipeline, result → host
+    workload.e2e_setup(cute, zoo, cache_dir)
+    workload.h2d_bytes, workload.d2h_bytes = workload.pipeline.h2d_bytes, workload.pipeline.d2h_bytes
     for _ in range(2):
         workload.e2e_step(torch)
     barrier()

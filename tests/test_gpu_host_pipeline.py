@@ -1,0 +1,57 @@
+"""Host-to-host pipeline (chunked copies overlapped with the kernel) against the one-shot artifact call."""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+
+from oracle import cpu_runtime as oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def test_pipeline_matches_one_shot_elementwise_and_gemm(zoo, tmp_path):
+    import torch
+
+    from baybridge_b200.host_pipeline import HostPipeline
+
+    n = 1_000_000  # 7 chunks are ragged (142858 / 142857 elements): two artifacts; 8 chunks are even
+    rng = np.random.default_rng(3)
+    a = torch.from_numpy(oracle.bf16_round(rng.standard_normal(n, dtype=np.float32))).to(torch.bfloat16).pin_memory()
+    b = torch.from_numpy(oracle.bf16_round(rng.standard_normal(n, dtype=np.float32))).to(torch.bfloat16).pin_memory()
+    for chunks in (1, 7, 8):
+        c = torch.zeros(n, dtype=torch.bfloat16).pin_memory()
+        pipeline = HostPipeline(lambda rows: zoo.make_fused_mul_add_indexed(rows), [a, b, c], chunks=chunks, cache_dir=tmp_path)
+        pipeline.run()
+        pipeline.run()  # buffers and events are reusable
+        reference = a.double().numpy() * b.double().numpy() + a.double().numpy()
+        assert oracle.rel_l2(c.double().numpy(), reference) <= 2e-3
+        assert pipeline.h2d_bytes == 2 * n * 2 and pipeline.d2h_bytes == n * 2
+
+    m, nn, k = 1000, 512, 256  # M sharded in ragged chunks, B replicated
+    a2 = torch.from_numpy(oracle.bf16_round((rng.standard_normal((m, k)) / 16).astype(np.float32))).to(torch.bfloat16).pin_memory()
+    b2 = torch.from_numpy(oracle.bf16_round((rng.standard_normal((nn, k)) / 16).astype(np.float32))).to(torch.bfloat16).pin_memory()
+    c2 = torch.zeros((m, nn), dtype=torch.float32).pin_memory()
+    HostPipeline(lambda rows: zoo.gemm_abt, [a2, b2, c2], chunks=3, cache_dir=tmp_path).run()
+    assert oracle.rel_l2(c2.double().numpy(), oracle.gemm(a2.double().numpy(), b2.double().numpy(), transpose_b=True)) <= 1e-5
+
+
+def test_pipeline_rmsnorm_and_attention(zoo, tmp_path):
+    import torch
+
+    from baybridge_b200.host_pipeline import HostPipeline
+
+    rng = np.random.default_rng(4)
+    x = torch.from_numpy(oracle.bf16_round(rng.standard_normal((300, 1024), dtype=np.float32))).to(torch.bfloat16).pin_memory()
+    w = torch.from_numpy(oracle.bf16_round((1 + 0.1 * rng.standard_normal(1024)).astype(np.float32))).to(torch.bfloat16).pin_memory()
+    out = torch.zeros_like(x).pin_memory()
+    HostPipeline(lambda rows: zoo.make_rmsnorm(1e-6), [x, out, w], chunks=4, cache_dir=tmp_path).run()
+    assert oracle.rel_l2(out.double().numpy(), oracle.rmsnorm(x.double().numpy(), w.double().numpy(), 1e-6)) <= 2e-3
+
+    shape = (3, 256, 2, 128)
+    q, k, v = (torch.from_numpy(oracle.bf16_round(rng.standard_normal(shape, dtype=np.float32))).to(torch.bfloat16).pin_memory() for _ in range(3))
+    o = torch.zeros(shape, dtype=torch.bfloat16).pin_memory()
+    lse = torch.zeros((3, 2, 1, 256), dtype=torch.float32).pin_memory()
+    HostPipeline(lambda rows: zoo.attention_causal, [q, k, v, o, lse], chunks=3, cache_dir=tmp_path).run()
+    ref_out, ref_lse = oracle.attention(q.double().numpy(), k.double().numpy(), v.double().numpy(), causal=True)
+    assert oracle.rel_l2(o.double().numpy(), ref_out) <= 1e-2
+    assert float(np.abs(lse.double().numpy() - ref_lse).max()) <= 1e-2
