@@ -48,7 +48,7 @@ from .host_values import (
     tensor,
     zeros,
 )
-from .trace import ScalarValue, TensorValue
+from .trace import ReductionOp, ScalarValue, TensorValue
 from .dsl import (
     KernelDefinition,
     KernelLaunch,

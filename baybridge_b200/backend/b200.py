@@ -32,7 +32,8 @@ from ..portable_ir import row_major_stride
 from ..scalar_types import DEVICE_NUMPY, byte_width, normalize_dtype_name
 from . import native
 from .elementwise import THREADS, UNROLL, compile_cubin, render
-from .matcher import AttentionPlan, ElementwisePlan, GemmPlan, LayerNormPlan, RmsNormPlan, adopt, match
+from . import reduction as reduction_lowering
+from .matcher import AttentionPlan, ElementwisePlan, GemmPlan, LayerNormPlan, ReductionPlan, RmsNormPlan, adopt, match
 
 _thread_state = threading.local()
 
@@ -107,6 +108,14 @@ class B200Backend:
                 entry=rendered.entry, tensor_order=list(rendered.tensor_order), scalar_order=list(rendered.scalar_order),
                 scalar_ctypes=list(rendered.scalar_ctypes), source=rendered.source,
             )
+        elif isinstance(plan, ReductionPlan):
+            rendered = reduction_lowering.render(plan, ir)
+            record.update(
+                form=plan.form, op=plan.op, outer=plan.outer, inner=plan.inner, compute=rendered.compute,
+                compute_bytes=rendered.compute_bytes, vector_elements=rendered.vec, entry=f"bb200_reduce_{plan.form}",
+                tensor_order=list(rendered.tensor_order), scalar_order=list(rendered.scalar_order),
+                scalar_ctypes=list(rendered.scalar_ctypes), source=rendered.source,
+            )
         else:
             record.update(asdict(plan))
             record["entry"] = {"gemm": "bb200_gemm_bf16", "rmsnorm": "bb200_rmsnorm", "layernorm": "bb200_layernorm",
@@ -122,7 +131,7 @@ class B200Backend:
         record = json.loads(lowered_module.text)
         state: dict[str, Any] = {"slots": {}}
         runner = {
-            "elementwise": self._elementwise_runner, "gemm": self._gemm_runner,
+            "elementwise": self._elementwise_runner, "reduction": self._reduction_runner, "gemm": self._gemm_runner,
             "rmsnorm": self._rmsnorm_runner, "layernorm": self._layernorm_runner, "attention": self._attention_runner,
         }[plan.kind](ir, plan, record, state)
         arguments = ir.arguments
@@ -269,6 +278,86 @@ class B200Backend:
                 values += [ctypes.c_size_t(extent), ctypes.c_int(1 if aligned else 0)]
             params = (ctypes.c_void_p * len(values))(*[ctypes.cast(ctypes.byref(v), ctypes.c_void_p) for v in values])
             native.call("bb200_launch", function, grid, block, cluster, 0, stream_handle, params)
+
+        return run
+
+    def _reduction_runner(self, ir, plan: ReductionPlan, record: dict[str, Any], state: dict[str, Any]):
+        cubin_path = compile_cubin(record["source"])
+        tensor_order, scalar_order = record["tensor_order"], record["scalar_order"]
+        ctype_of = {"double": ctypes.c_double, "int32_t": ctypes.c_int32, "int64_t": ctypes.c_int64}
+        scalar_ctypes = [ctype_of[name] for name in record["scalar_ctypes"]]
+        compute_ctype = {"double": ctypes.c_double, "float": ctypes.c_float, "long long": ctypes.c_longlong}[record["compute"]]
+        compute_bytes, vec = int(record["compute_bytes"]), int(record["vector_elements"])
+        threads = reduction_lowering.THREADS
+        outer, inner, total = plan.outer, plan.inner, plan.outer * plan.inner
+        one = native.U3(1, 1, 1)
+        # launch geometry is fixed by the plan
+        if plan.form == "all":
+            chunks = max(1, min(148 * 8, -(-total // (threads * vec * 2))))
+            chunk_len = -(-(-(-total // chunks)) // vec) * vec
+            chunks = -(-total // chunk_len)
+            scratch_bytes = chunks * compute_bytes if chunks > 1 else 0
+        elif plan.form == "cols":
+            slabs = max(1, min(outer, 256, (148 * 1024) // max(inner, 1)))
+            scratch_bytes = slabs * inner * compute_bytes if slabs > 1 else 0
+        else:
+            scratch_bytes = 0
+
+        def function(name: str):
+            functions = state.setdefault("functions", {})
+            if name not in functions:
+                if "module" not in state:
+                    image = cubin_path.read_bytes()
+                    module = ctypes.c_void_p()
+                    native.call("bb200_module_load", image, len(image), ctypes.byref(module))
+                    state["module"] = module
+                handle = ctypes.c_void_p()
+                native.call("bb200_get_function", state["module"], name.encode(), ctypes.byref(handle))
+                functions[name] = handle
+            return functions[name]
+
+        def launch(name: str, grid, block, values: list[Any], stream_handle) -> None:
+            params = (ctypes.c_void_p * len(values))(*[ctypes.cast(ctypes.byref(v), ctypes.c_void_p) for v in values])
+            native.call("bb200_launch", function(name), grid, block, one, 0, stream_handle, params)
+
+        def run(pointers: dict[int, int], scalars: dict[int, Any], stream_handle) -> None:
+            inputs: list[Any] = [ctypes.c_void_p(pointers[position]) for position in tensor_order]
+            inputs += [ctype(scalars[position]) for position, ctype in zip(scalar_order, scalar_ctypes)]
+            dst = [ctypes.c_void_p(pointers[plan.dst]), ctypes.c_size_t(plan.dst_offset)]
+            init = compute_ctype(plan.init)
+            aligned = ctypes.c_int(1 if all(pointers[position] % 16 == 0 for position in tensor_order) else 0)
+            scratch = None
+            if scratch_bytes:
+                slot = state.get("scratch")
+                if slot is None or slot.nbytes < scratch_bytes:
+                    if slot is not None:
+                        slot.release()
+                    slot = state["scratch"] = _StagedSlot(scratch_bytes, ("scratch",))
+                scratch = ctypes.c_void_p(slot.pointer.value)
+            block = native.U3(threads, 1, 1)
+            if plan.form == "rows":
+                launch("bb200_reduce_rows", native.U3(outer, 1, 1), block,
+                       inputs + dst + [ctypes.c_size_t(outer), ctypes.c_size_t(inner), ctypes.c_size_t(total), init, aligned], stream_handle)
+            elif plan.form == "all":
+                if chunks == 1:
+                    launch("bb200_reduce_rows", native.U3(1, 1, 1), block,
+                           inputs + dst + [ctypes.c_size_t(1), ctypes.c_size_t(total), ctypes.c_size_t(total), init, aligned], stream_handle)
+                else:
+                    launch("bb200_reduce_rows_partial", native.U3(chunks, 1, 1), block,
+                           inputs + [scratch, ctypes.c_size_t(chunks), ctypes.c_size_t(chunk_len), ctypes.c_size_t(total), aligned],
+                           stream_handle)
+                    launch("bb200_reduce_partials_rows", native.U3(1, 1, 1), block, [scratch] + dst + [ctypes.c_size_t(chunks), init],
+                           stream_handle)
+            else:
+                columns = native.U3(-(-inner // threads), slabs, 1)
+                if slabs == 1:
+                    launch("bb200_reduce_cols", columns, block, inputs + dst + [ctypes.c_size_t(outer), ctypes.c_size_t(inner), init],
+                           stream_handle)
+                else:
+                    launch("bb200_reduce_cols_partial", columns, block, inputs + [scratch, ctypes.c_size_t(outer), ctypes.c_size_t(inner)],
+                           stream_handle)
+                    launch("bb200_reduce_partials_cols", native.U3(-(-inner // threads), 1, 1), block,
+                           [scratch] + dst + [ctypes.c_size_t(slabs), ctypes.c_size_t(inner), init], stream_handle)
 
         return run
 

@@ -152,6 +152,29 @@ class ElementwisePlan:
     kind: str = "elementwise"
 
 
+@dataclass(frozen=True)
+class ReductionPlan:
+    """``dst = fold(op, init, value over the reduced axes)`` where ``value`` is the per-element expression
+    ``nodes`` computes from ``inputs`` (all of ``source_shape``).  ``form``: ``rows`` (trailing axes reduced:
+    ``[outer, inner] -> [outer]``), ``cols`` (leading axes reduced: ``[outer, inner] -> [inner]``) or ``all``
+    (scalar result stored at ``dst_offset`` of ``dst``)."""
+
+    nodes: tuple[Node, ...]
+    inputs: tuple[int, ...]
+    scalars: tuple[int, ...]
+    value: str
+    op: str
+    init: Any
+    form: str
+    outer: int
+    inner: int
+    dst: int
+    dst_offset: int
+    source_shape: tuple[int, ...]
+    dtype: str
+    kind: str = "reduction"
+
+
 # ---------------------------------------------------------------------------------------------
 # explicit single-op kernels
 # ---------------------------------------------------------------------------------------------
@@ -594,6 +617,8 @@ def _match_ssa_elementwise(ir) -> ElementwisePlan:
     inputs: list[int] = []
     stores: dict[int, str] = {}
     shape: tuple[int, ...] | None = None
+    reduction: dict[str, Any] | None = None
+    constants: dict[str, Any] = {}
 
     def element_shape(candidate: tuple[int, ...]) -> None:
         nonlocal shape
@@ -615,7 +640,41 @@ def _match_ssa_elementwise(ir) -> ElementwisePlan:
             dtypes[argument.name] = argument.spec.dtype
 
     for op in ir.operations:
-        if op.op == "make_tensor":
+        if reduction is not None and op.op not in ("constant", "copy", "store"):
+            raise _unsupported(f"op '{op.op}' after a reduction is not lowered (only the store of the result is)")
+        if op.op.startswith("reduce_"):
+            if reduction is not None:
+                raise _unsupported("more than one reduction in a kernel is not lowered")
+            source, init = op.inputs
+            if source not in known or init not in constants:
+                raise _unsupported("a reduction must consume a tensor value and a literal init value")
+            profile = op.attrs.get("reduction_profile", 0)
+            source_shape = tuple(shapes.get(source, shape or ()))
+            rank = len(source_shape)
+            keep = () if profile == 0 else tuple(axis for axis, item in enumerate(profile) if item is None)
+            reduction = {"value": known[source], "op": op.op[len("reduce_"):], "init": constants[init], "keep": keep,
+                         "shape": source_shape, "result": op.outputs[0], "dtype": op.attrs["result"]["dtype"], "rank": rank}
+        elif reduction is not None and op.op == "copy":
+            source, destination = op.inputs
+            if source != reduction["result"] or destination not in positions:
+                raise _unsupported("the result of a reduction must be stored straight into a kernel tensor argument")
+            spec = global_tensor(destination)
+            kept_shape = tuple(reduction["shape"][axis] for axis in reduction["keep"])
+            if tuple(spec.shape) != kept_shape or spec.dtype != reduction["dtype"]:
+                raise _unsupported("reduction result and destination differ in shape or dtype")
+            reduction["dst"], reduction["dst_offset"] = positions[destination], 0
+        elif reduction is not None and op.op == "store":
+            value, destination, *indices = op.inputs
+            if value != reduction["result"] or destination not in positions or any(i not in constants for i in indices):
+                raise _unsupported("a scalar reduction result must be stored at a constant index of a kernel tensor argument")
+            spec = global_tensor(destination)
+            if spec.dtype != reduction["dtype"]:
+                raise _unsupported("reduction result and destination differ in dtype")
+            offset = sum(int(constants[i]) * step for i, step in zip(indices, spec.resolved_layout().stride))
+            if not 0 <= offset < spec.numel:
+                raise _unsupported("scalar reduction result stored out of bounds")
+            reduction["dst"], reduction["dst_offset"] = positions[destination], offset
+        elif op.op == "make_tensor":
             if op.attrs.get("address_space") != "register":
                 raise _unsupported("tensor-SSA bodies may only stage through register tensors")
             register_buffers[op.outputs[0]] = op.attrs
@@ -663,6 +722,7 @@ def _match_ssa_elementwise(ir) -> ElementwisePlan:
             nodes.append(Node(op.outputs[0], "constant", dtype, attrs={"value": op.attrs["value"]}))
             known[op.outputs[0]] = op.outputs[0]
             dtypes[op.outputs[0]] = dtype
+            constants[op.outputs[0]] = op.attrs["value"]
         elif op.op in TENSOR_OP_ALIASES or op.op in UNARY_OPS or op.op in BINARY_OPS or op.op == "select":
             base = TENSOR_OP_ALIASES.get(op.op, op.op)
             result = op.attrs["result"]
@@ -680,6 +740,8 @@ def _match_ssa_elementwise(ir) -> ElementwisePlan:
             dtypes[op.outputs[0]], shapes[op.outputs[0]] = result["dtype"], tuple(result["shape"])
         else:
             raise _unsupported(f"op '{op.op}' is not part of a tensor-SSA elementwise body")
+    if reduction is not None:
+        return _reduction_plan(ir, reduction, nodes, inputs)
     if not stores or shape is None:
         raise _unsupported("the kernel body stores nothing")
     by_name = {node.name: node for node in nodes}
@@ -692,6 +754,40 @@ def _match_ssa_elementwise(ir) -> ElementwisePlan:
         mode="flat", nodes=kept, inputs=tuple(position for position in inputs if f"{ir.arguments[position].name}__elem" in live),
         stores=tuple(stores.items()),
         scalars=tuple(node.attrs["position"] for node in kept if node.op == "scalar_arg"), extent=extent,
+    )
+
+
+def _reduction_plan(ir, reduction: dict[str, Any], nodes: list[Node], inputs: list[int]) -> ReductionPlan:
+    if "dst" not in reduction:
+        raise _unsupported("the result of the reduction is never stored")
+    if reduction["dtype"] not in ("f32", "bf16", "f16", "i32"):
+        raise _unsupported(f"reductions over {reduction['dtype']} tensors are not lowered")
+    if reduction["op"] in ("and", "or", "xor") and reduction["dtype"] != "i32":
+        raise _unsupported("bitwise reductions need i32 tensors")
+    shape, keep, rank = reduction["shape"], reduction["keep"], reduction["rank"]
+    total = 1
+    for extent in shape:
+        total *= extent
+    kept = 1
+    for axis in keep:
+        kept *= shape[axis]
+    if not keep:
+        form, outer, inner = "all", 1, total
+    elif keep == tuple(range(len(keep))):
+        form, outer, inner = "rows", kept, total // kept
+    elif keep == tuple(range(rank - len(keep), rank)):
+        form, outer, inner = "cols", total // kept, kept
+    else:
+        raise _unsupported(f"reduction keeping axes {keep} of a rank-{rank} tensor is neither a row nor a column reduction")
+    by_name = {node.name: node for node in nodes}
+    live = _live_set(by_name, [reduction["value"]], lambda name: name)
+    kept_nodes = tuple(node for node in nodes if node.name in live)
+    return ReductionPlan(
+        nodes=kept_nodes,
+        inputs=tuple(p for p in inputs if f"{ir.arguments[p].name}__elem" in live),
+        scalars=tuple(node.attrs["position"] for node in kept_nodes if node.op == "scalar_arg"),
+        value=reduction["value"], op=reduction["op"], init=reduction["init"], form=form, outer=outer, inner=inner,
+        dst=reduction["dst"], dst_offset=reduction["dst_offset"], source_shape=tuple(shape), dtype=reduction["dtype"],
     )
 
 
@@ -724,6 +820,8 @@ def match(ir):
             )
         return EXPLICIT[explicit[0].op](ir, explicit[0])
     names = {op.op for op in operations}
+    if any(name.startswith("reduce_") for name in names):
+        return _match_ssa_elementwise(ir)
     if names & {"load", "store", "masked_load", "masked_store"}:
         return _match_scalar_elementwise(ir)
     if "copy" in names:

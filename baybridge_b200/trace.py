@@ -29,6 +29,43 @@ from .portable_ir import (
 )
 from .scalar_types import byte_width, element_type, is_float_dtype, promote_scalar_dtype
 
+import enum
+
+
+class ReductionOp(str, enum.Enum):
+    """Reduction operators of ``Tensor.reduce`` (upstream ``runtime.py:325-333``)."""
+
+    ADD = "add"
+    MUL = "mul"
+    MAX = "max"
+    MIN = "min"
+    AND = "and"
+    OR = "or"
+    XOR = "xor"
+
+    @classmethod
+    def coerce(cls, value: "ReductionOp | str") -> "ReductionOp":
+        if isinstance(value, cls):
+            return value
+        try:
+            return cls(str(value).lower())
+        except ValueError:
+            names = ", ".join(member.value for member in cls)
+            raise ValueError(f"unsupported reduction op '{value}', expected one of: {names}") from None
+
+
+def reduction_axes(profile: Any, rank: int) -> tuple[tuple[int, ...], tuple[int, ...]]:
+    """``0`` reduces every axis; otherwise a length-``rank`` sequence where ``None`` marks a kept axis."""
+    if isinstance(profile, int) and not isinstance(profile, bool) and profile == 0:
+        return tuple(range(rank)), ()
+    if not isinstance(profile, (tuple, list)):
+        raise TypeError("reduction_profile must be 0 or a tuple/list describing kept axes with None")
+    if len(profile) != rank:
+        raise ValueError(f"reduction_profile must have length {rank} for tensor rank {rank}")
+    keep = tuple(axis for axis, item in enumerate(profile) if item is None)
+    return tuple(axis for axis in range(rank) if axis not in keep), keep
+
+
 _ACTIVE: ContextVar["IRBuilder | None"] = ContextVar("baybridge_b200_builder", default=None)
 
 ScalarLike = Any  # ScalarValue | RuntimeScalar | bool | int | float
@@ -255,6 +292,21 @@ class TensorValue:
         if scalar.spec.dtype != self.spec.dtype:
             raise ValueError(f"fill expects dtype {self.spec.dtype}, got {scalar.spec.dtype}")
         builder.emit_void("fill", self, scalar)
+
+    def reduce(self, op: "ReductionOp | str", init_value: ScalarLike, *, reduction_profile: Any = 0):
+        """Reduce over the axes ``reduction_profile`` does not keep; returns a scalar when none is kept."""
+        reduction = ReductionOp.coerce(op)
+        _, keep = reduction_axes(reduction_profile, self.ndim)
+        builder = require_builder()
+        init = init_value if isinstance(init_value, ScalarValue) else builder.constant(init_value, dtype=self.spec.dtype)
+        if init.spec.dtype != self.spec.dtype:
+            raise ValueError(f"reduce expects init value dtype {self.spec.dtype}, got {init.spec.dtype}")
+        name = f"reduce_{reduction.value}"
+        attrs = {"reduction_profile": list(reduction_profile) if isinstance(reduction_profile, (tuple, list)) else reduction_profile}
+        if not keep:
+            return builder.emit_scalar(name, self, init, spec=ScalarSpec(self.spec.dtype), attrs=attrs, name_hint=name)
+        kept_shape = tuple(self.spec.shape[axis] for axis in keep)
+        return builder.emit_tensor(name, self, init, spec=_register_spec(kept_shape, self.spec.dtype), attrs=attrs, name_hint=name)
 
     def broadcast_to(self, shape: tuple[int, ...]) -> "TensorValue":
         target = tuple(int(extent) for extent in shape)

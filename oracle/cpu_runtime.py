@@ -198,6 +198,20 @@ def run_kernel_ir(ir: dict[str, Any], arguments: dict[str, Any]) -> None:
             continue
         elif op == "broadcast_to":
             result = np.broadcast_to(env[ins[0]], attrs["target_shape"])
+        elif op.startswith("reduce_"):
+            # upstream runtime.py:484-505: fold of every element of the reduced axes, starting from the init value
+            profile = attrs.get("reduction_profile", 0)
+            source = np.asarray(env[ins[0]])
+            keep = () if profile == 0 else tuple(axis for axis, item in enumerate(profile) if item is None)
+            kept_shape = tuple(source.shape[axis] for axis in keep)
+            folded_view = np.moveaxis(source, keep, range(len(keep))).reshape(kept_shape + (-1,))
+            kind = op[len("reduce_"):]
+            integer = kind in ("and", "or", "xor")
+            ufunc = {"add": np.add, "mul": np.multiply, "max": np.maximum, "min": np.minimum,
+                     "and": np.bitwise_and, "or": np.bitwise_or, "xor": np.bitwise_xor}[kind]
+            data = folded_view.astype(np.int64) if integer else folded_view.astype(F64)
+            init = np.int64(env[ins[1]]) if integer else F64(env[ins[1]])
+            result = ufunc(init, ufunc.reduce(data, axis=-1))
         elif op in _TENSOR_ALIAS:
             base = _TENSOR_ALIAS[op]
             operands = [np.asarray(env[n]) for n in ins]

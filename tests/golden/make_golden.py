@@ -211,6 +211,13 @@ def main() -> None:
         "ssa_exp_max_8x96_f32", zoo.ssa_exp_max, {"a": (p, "f32"), "b": (q, "f32"), "c": (np.zeros((8, 96)), "f32")}, ["c"]
     )
 
+    # reductions
+    rsrc = rng.uniform(-1, 1, (16, 96)).astype(np.float32)
+    run_case("reduce_row_sumsq_16x96_f32", zoo.row_sum_of_squares, {"src": (rsrc, "f32"), "dst": (np.zeros(16), "f32")}, ["dst"])
+    run_case("reduce_col_max_24x64_bf16", zoo.column_max,
+             {"src": (bf16_round(rng.uniform(-4, 4, (24, 64)).astype(np.float32)), "bf16"), "dst": (np.zeros(64), "bf16")}, ["dst"])
+    run_case("reduce_total_sum_8x96_f32", zoo.total_sum, {"src": (rsrc[:8], "f32"), "dst": (np.zeros(1), "f32")}, ["dst"])
+
     # ---------------- config 3 (reduced) + upstream's own known-answer GEMMs ---------------------
     rng = np.random.default_rng(1003)
     m, n_, k = 48, 40, 64

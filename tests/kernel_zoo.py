@@ -166,6 +166,26 @@ def build_zoo(cute) -> SimpleNamespace:
 
     zoo.ssa_exp_max = ssa_exp_max
 
+    # ---- reductions (map, then fold) ----------------------------------------------------------------
+    @cute.kernel
+    def row_sum_of_squares(src: cute.Tensor, dst: cute.Tensor):
+        v = src.load()
+        dst.store((v * v).reduce(cute.ReductionOp.ADD, 0.0, reduction_profile=(None, 1)))
+
+    zoo.row_sum_of_squares = row_sum_of_squares
+
+    @cute.kernel
+    def column_max(src: cute.Tensor, dst: cute.Tensor):
+        dst.store(src.load().reduce(cute.ReductionOp.MAX, -1000.0, reduction_profile=(1, None)))
+
+    zoo.column_max = column_max
+
+    @cute.kernel
+    def total_sum(src: cute.Tensor, dst: cute.Tensor):
+        dst[0] = src.load().reduce(cute.ReductionOp.ADD, 1.0)
+
+    zoo.total_sum = total_sum
+
     # ---- explicit single-op kernels ---------------------------------------------------------------
     @cute.kernel
     def gemm_abt(a: cute.Tensor, b: cute.Tensor, c: cute.Tensor):

@@ -64,6 +64,8 @@ def _zoo_kernel(case: str, zoo):
         "rmsnorm": lambda: zoo.make_rmsnorm(None),
         "layernorm": lambda: zoo.layernorm_kernel,
     }
+    if case.startswith("reduce_"):
+        return {"row": zoo.row_sum_of_squares, "col": zoo.column_max, "total": zoo.total_sum}[parts[1]]
     if case.startswith("c2_fused_indexed"):
         return zoo.make_fused_mul_add_indexed(2**28 if "2p28" in case else int(parts[3]))
     if case.startswith("c2_fused_ssa"):
@@ -99,6 +101,8 @@ def test_matcher_classifies_every_listing(case):
         assert plan.kind == "rmsnorm"
     elif case.startswith("layernorm_"):
         assert plan.kind == "layernorm"
+    elif case.startswith("reduce_"):
+        assert plan.kind == "reduction" and plan.form == {"row": "rows", "col": "cols", "total": "all"}[case.split("_")[1]]
     elif case.startswith(("c5_", "attn_")):
         assert plan.kind == "attention"
     else:
