@@ -70,8 +70,8 @@ def test_full_reductions(n, zoo, tmp_path):
     expect_rounded(got, expected, "f32", max_ulp=1)
 
     @cute.kernel
-    def xor_all(values: cute.Tensor, dst: cute.Tensor):
-        dst[0] = values.load().reduce(cute.ReductionOp.XOR, 0)
+    def xor_all(src: cute.Tensor, dst: cute.Tensor):
+        dst[0] = src.load().reduce(cute.ReductionOp.XOR, 0)
 
     bits = rng.integers(-2**31, 2**31 - 1, size=n, dtype=np.int64)
     got, _ = _run(xor_all, bits, (1,), "i32", tmp_path)
