@@ -242,6 +242,173 @@ gemm_abt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   }
 }
 
+// ---- CTA-pair variant (A · B^T with B stored [n, k]) ---------------------------------------------------
+// Two CTAs of a cluster (neighbouring SMs) own one 256x256 tile of C.  Each CTA streams its own 128
+// rows of A and its own 128 rows (half) of the B tile, so a stage is 32 KB instead of 48 KB and the
+// ring holds 6 stages; CTA 0 issues tcgen05.mma.cta_group::2 (M256 x N256 x K16), which reads A from
+// each CTA's shared memory, B from both halves, and writes each CTA's 128 accumulator lanes in that
+// CTA's TMEM.  Per k-block the pair moves 64 KB for 8.4 MFLOP: a third less shared-memory and L2
+// traffic per flop than the single-CTA kernel.
+//   * TMA loads of both CTAs credit CTA 0's `full[stage]`, which expects the bytes of both.
+//   * tcgen05.commit arrives on `empty[stage]` / `acc_full[buffer]` of BOTH CTAs (each CTA's producer
+//     and epilogue wait on their own copy).
+//   * the epilogue warps of both CTAs arrive on CTA 0's `acc_empty[buffer]` (8 arrivals).
+constexpr int PAIR_STAGES = 6;
+constexpr int PAIR_B_ROWS = BN / 2;                       // rows of the B tile held by each CTA
+constexpr int PAIR_B_BYTES = PAIR_B_ROWS * BK * 2;        // 16 KB
+constexpr int PAIR_STAGE_BYTES = A_TILE_BYTES + PAIR_B_BYTES;
+constexpr int PAIR_SMEM_BYTES = PAIR_STAGES * PAIR_STAGE_BYTES + 1024 + 256;
+constexpr int PAIR_BM = 2 * BM;
+
+template <typename OutT>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
+gemm_abt_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, OutT* __restrict__ c,
+                     int m, int n, int k, int group_m, int* status_word) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_addr(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_aligned = smem_raw + (smem_base - smem_addr(smem_raw));
+  uint64_t* barriers = reinterpret_cast<uint64_t*>(smem_aligned + PAIR_STAGES * PAIR_STAGE_BYTES);
+  const uint32_t bar_base = smem_base + PAIR_STAGES * PAIR_STAGE_BYTES;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (PAIR_STAGES + s); };
+  auto acc_full_bar = [&](int b) { return bar_base + 8u * (2 * PAIR_STAGES + b); };
+  auto acc_empty_bar = [&](int b) { return bar_base + 8u * (2 * PAIR_STAGES + 2 + b); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(barriers + 2 * PAIR_STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t cta_rank = cluster_cta_rank();
+  const bool leader = cta_rank == 0;
+  const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+  const int m_blocks = (m + PAIR_BM - 1) / PAIR_BM, n_blocks = (n + BN - 1) / BN;
+  const int tiles = m_blocks * n_blocks;
+  const int k_blocks = (k + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < PAIR_STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(acc_full_bar(b), 1);
+      mbar_init(acc_empty_bar(b), 8);  // one arrival per epilogue warp of either CTA
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    fence_proxy_async();
+  }
+  // the peer's barriers must exist before anything of this CTA can signal them
+  cluster_arrive();
+  cluster_wait();
+  if (warp == 1) tmem_alloc_pair(smem_addr(tmem_slot), TMEM_COLUMNS);
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer (both CTAs) ----------------
+    if (elect_one()) {
+      prefetch_tensormap(&map_a);
+      prefetch_tensormap(&map_b);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = pair; ok && tile < tiles; tile += pairs) {
+        const TileCoord coord = tile_coord(tile, m_blocks, n_blocks, group_m);
+        const int a_row = coord.m_block * PAIR_BM + (int)cta_rank * BM;
+        const int b_row = coord.n_block * BN + (int)cta_rank * PAIR_B_ROWS;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!(ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, status_word, kWaitEmpty))) break;
+          const uint32_t a_dst = smem_base + stage * PAIR_STAGE_BYTES;
+          const uint32_t signal = leader_cta_address(full_bar(stage));
+          if (leader) mbar_arrive_expect_tx(full_bar(stage), 2 * PAIR_STAGE_BYTES);
+          tma_load_2d_pair(a_dst, &map_a, signal, kb * BK, a_row);
+          tma_load_2d_pair(a_dst + A_TILE_BYTES, &map_b, signal, kb * BK, b_row);
+          if (++stage == PAIR_STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer (CTA 0 only) ----------------
+    if (leader && elect_one()) {
+      constexpr uint32_t idesc = umma_idesc_bf16_f32(PAIR_BM, BN, false, false);
+      int stage = 0;
+      uint32_t phase = 0;
+      int local_tile = 0;
+      bool ok = true;
+      for (int tile = pair; ok && tile < tiles; tile += pairs, ++local_tile) {
+        const int buffer = local_tile & 1;
+        const uint32_t acc_phase = (uint32_t)(local_tile >> 1) & 1u;
+        if (!(ok = mbar_wait(acc_empty_bar(buffer), acc_phase ^ 1u, abort_flag, status_word, kWaitAccEmpty))) break;
+        tcgen05_fence_after();
+        const uint32_t tmem_acc = tmem_base + (uint32_t)(buffer * ACC_COLUMNS);
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!(ok = mbar_wait(full_bar(stage), phase, abort_flag, status_word, kWaitFull))) break;
+          tcgen05_fence_after();
+          const uint32_t a_src = smem_base + stage * PAIR_STAGE_BYTES;
+          const uint64_t desc_a = umma_desc_k_major_sw128(a_src);
+          const uint64_t desc_b = umma_desc_k_major_sw128(a_src + A_TILE_BYTES);
+#pragma unroll
+          for (int kk = 0; kk < BK / UMMA_K; ++kk)
+            umma_bf16_ss_pair(tmem_acc, umma_desc_advance_k(desc_a, kk * UMMA_K * 2), umma_desc_advance_k(desc_b, kk * UMMA_K * 2),
+                              idesc, (kb | kk) != 0 ? 1u : 0u);
+          umma_commit_pair(empty_bar(stage), 0x3);
+          if (++stage == PAIR_STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) umma_commit_pair(acc_full_bar(buffer), 0x3);
+      }
+    }
+  } else {
+    // ---------------- epilogue (warps 2..5 of both CTAs; each CTA stores its own 128 rows) ----------------
+    const int quadrant = warp & 3;
+    int local_tile = 0;
+    bool ok = true;
+    for (int tile = pair; ok && tile < tiles; tile += pairs, ++local_tile) {
+      const TileCoord coord = tile_coord(tile, m_blocks, n_blocks, group_m);
+      const int buffer = local_tile & 1;
+      const uint32_t acc_phase = (uint32_t)(local_tile >> 1) & 1u;
+      ok = mbar_wait(acc_full_bar(buffer), acc_phase, abort_flag, status_word, kWaitAccFull);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tcgen05_fence_after();
+      const int row = coord.m_block * PAIR_BM + (int)cta_rank * BM + quadrant * 32 + lane;
+      const int col0 = coord.n_block * BN;
+      const uint32_t taddr = tmem_base + ((uint32_t)(quadrant * 32) << 16) + (uint32_t)(buffer * ACC_COLUMNS);
+#pragma unroll 1
+      for (int chunk = 0; chunk < BN / 32; ++chunk) {
+        uint32_t acc[32];
+        tmem_ld_32x32b_x32(taddr + (uint32_t)(chunk * 32), acc);
+        tmem_ld_wait();
+        const int col = col0 + chunk * 32;
+        if (row < m && col < n) store_chunk<OutT>(c + (size_t)row * n + col, acc, n - col);
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_remote(acc_empty_bar(buffer), 0);
+    }
+  }
+
+  // ---------------- teardown ----------------
+  tcgen05_fence_before();
+  __syncthreads();
+  if (*abort_flag != 0) {
+    const unsigned long long started = global_timer_ns();
+    while (global_timer_ns() - started < 2000000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  // neither CTA may release its TMEM or shared memory while the other can still signal or read it;
+  // every wait above is bounded, so both CTAs get here
+  cluster_arrive();
+  cluster_wait();
+  if (warp == 1) {
+    __syncwarp();
+    tcgen05_fence_after();
+    tmem_dealloc_pair(tmem_base, TMEM_COLUMNS);
+  }
+}
+
 // ---- tiled transpose (brings other operand layouts to the native K-contiguous form) ------------------
 __global__ void transpose_bf16_kernel(const __nv_bfloat16* __restrict__ src, __nv_bfloat16* __restrict__ dst, int rows, int cols) {
   __shared__ __nv_bfloat16 tile[32][33];
@@ -291,6 +458,38 @@ int raster_group_m() {
   return value;
 }
 
+// The pair kernel pays off once both tile dimensions are large enough to fill the pairs; small and
+// ragged problems stay on the single-CTA kernel.  BB200_GEMM_PAIR=0/1 forces the choice for tuning runs.
+bool use_pair_kernel(int m, int n, int sms) {
+  static int forced = -2;
+  if (forced == -2) {
+    const char* text = getenv("BB200_GEMM_PAIR");
+    forced = text ? (atoi(text) != 0 ? 1 : 0) : -1;
+  }
+  if (forced >= 0) return forced == 1;
+  const long tiles = (long)((m + PAIR_BM - 1) / PAIR_BM) * ((n + BN - 1) / BN);
+  return (sms % 2) == 0 && tiles >= sms / 2;
+}
+
+template <typename OutT>
+int launch_pair(const void* a_mk, const void* b_nk, void* c, int m, int n, int k, int device, int sms, cudaStream_t stream) {
+  alignas(64) CUtensorMap map_a, map_b;
+  if (int status = encode_tensormap_2d(&map_a, BB200_BF16, a_mk, (uint64_t)m, (uint64_t)k, (uint64_t)k * 2, BM, BK, 3)) return status;
+  if (int status = encode_tensormap_2d(&map_b, BB200_BF16, b_nk, (uint64_t)n, (uint64_t)k, (uint64_t)k * 2, PAIR_B_ROWS, BK, 3)) return status;
+  static bool configured[kMaxDevices] = {};
+  if (!configured[device]) {
+    if (int status = check_runtime(cudaFuncSetAttribute(gemm_abt_pair_kernel<OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM_BYTES),
+                                   "cudaFuncSetAttribute(gemm pair smem)"))
+      return status;
+    configured[device] = true;
+  }
+  const int tiles = ((m + PAIR_BM - 1) / PAIR_BM) * ((n + BN - 1) / BN);
+  const int pairs = tiles < sms / 2 ? tiles : sms / 2;
+  gemm_abt_pair_kernel<OutT><<<2 * pairs, THREADS, PAIR_SMEM_BYTES, stream>>>(map_a, map_b, static_cast<OutT*>(c), m, n, k, raster_group_m() / 2 > 0 ? raster_group_m() / 2 : 1,
+                                                                             device_status_word());
+  return check_launch("gemm pair kernel launch");
+}
+
 // b_is_kn: B is stored [k, n] (n contiguous) and consumed as an MN-major operand; otherwise [n, k].
 template <typename OutT, bool B_MN>
 int launch_native(const void* a_mk, const void* b, void* c, int m, int n, int k, cudaStream_t stream) {
@@ -310,6 +509,9 @@ int launch_native(const void* a_mk, const void* b, void* c, int m, int n, int k,
   }
   const int sms = cached_sm_count(device);
   if (sms <= 0) return fail(BB200_E_NO_DRIVER, "gemm: could not query the SM count");
+  if constexpr (!B_MN) {
+    if (use_pair_kernel(m, n, sms)) return launch_pair<OutT>(a_mk, b, c, m, n, k, device, sms, stream);
+  }
   const int tiles = ((m + BM - 1) / BM) * ((n + BN - 1) / BN);
   const int grid = tiles < sms ? tiles : sms;
   gemm_abt_kernel<OutT, B_MN><<<grid, THREADS, SMEM_BYTES, stream>>>(map_a, map_b, static_cast<OutT*>(c), m, n, k, raster_group_m(), device_status_word());
