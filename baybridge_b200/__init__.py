@@ -54,7 +54,7 @@ from .dsl import (
     KernelLaunch,
     acos, arch, asin, atan, atan2, attention, block_dim, block_idx, ceil, copy, cos, dim, erf, exp, exp2, floor,
     gemm, grid_dim, jit, kernel, lane_id, layernorm, load, log, log10, log2, make_tensor, math, maximum, minimum, mma,
-    program_id, rmsnorm, round, rsqrt, sin, sqrt, store, thread_idx, trunc, where,
+    partition, partition_program, partition_thread, barrier, program_id, rmsnorm, round, rsqrt, sin, sqrt, store, thread_idx, trunc, where,
 )
 from .targets import AMDTarget, NvidiaTarget
 from .driver import (

@@ -211,6 +211,96 @@ def _match_gemm(ir, op) -> GemmPlan:
     return GemmPlan(a, b, c, m, n, k, transpose_a, transpose_b, "bf16", c_spec.dtype)
 
 
+_PROGRAM_AXIS = {"x": 0, "y": 1, "z": 2}
+TOPOLOGY_OPS = frozenset({"program_id", "block_idx", "thread_idx", "block_dim", "grid_dim", "lane_id"})
+
+
+def _match_tiled_gemm(ir, mma_op) -> GemmPlan:
+    """A GEMM written per program: each program takes ``partition`` views of A, B and C at offsets
+    ``program_id(axis) * tile`` and issues one ``mma`` on them.  When the launch grid tiles C exactly and
+    every program reads the whole K extent, the grid of programs computes one whole GEMM (programs or
+    threads that repeat a tile rewrite the same values), so the kernel lowers to the GEMM on the full
+    tensors.  Anything else about the body (other ops, nested views, partial K) is refused."""
+    grid = tuple(ir.launch.grid)
+    positions = _argument_positions(ir)
+    scalars: dict[str, tuple[int | None, int]] = {}  # name -> (program axis or None, multiplier / constant)
+    views: dict[str, tuple[str, list[tuple[str, int]]]] = {}  # view name -> (argument, per-dim ("all"|axis, tile))
+    for op in ir.operations:
+        if op is mma_op or op.op == "barrier":
+            continue
+        if op.op in ("program_id", "block_idx"):
+            scalars[op.outputs[0]] = (_PROGRAM_AXIS[op.attrs["axis"]], 1)
+        elif op.op == "constant" and isinstance(op.attrs.get("value"), int) and not isinstance(op.attrs.get("value"), bool):
+            scalars[op.outputs[0]] = (None, int(op.attrs["value"]))
+        elif op.op == "mul" and all(name in scalars for name in op.inputs):
+            (axis_l, value_l), (axis_r, value_r) = (scalars[name] for name in op.inputs)
+            if axis_l is not None and axis_r is not None:
+                raise _unsupported("a product of two program ids is not a tile offset")
+            scalars[op.outputs[0]] = (axis_l if axis_l is not None else axis_r, value_l * value_r)
+        elif op.op == "partition":
+            source, offsets = op.inputs[0], op.inputs[1:]
+            spec = _tensor_arg(ir, positions, source, "tiled gemm")[1]
+            tile = tuple(op.attrs["tile"])
+            dims: list[tuple[str, int]] = []
+            for axis_index, (extent, step) in enumerate(zip(spec.shape, tile)):
+                program_axis, factor = scalars.get(offsets[axis_index], (None, None)) if offsets else (None, 0)
+                if factor is None:
+                    raise _unsupported(f"partition offset '{offsets[axis_index]}' is not a constant or a program id times a constant")
+                if program_axis is None or grid[program_axis] == 1:
+                    # a fixed offset (a program id along an axis of extent 1 is always 0)
+                    if (factor if program_axis is None else 0) != 0 or step != extent:
+                        raise _unsupported("a partition at a fixed offset must cover the whole axis to be part of a whole GEMM")
+                    dims.append(("all", step))
+                else:
+                    if factor != step or grid[program_axis] * step != extent:
+                        raise _unsupported(
+                            f"programs along {'xyz'[program_axis]} must tile axis {axis_index} of '{source}' exactly "
+                            f"(extent {extent}, tile {step}, offset step {factor}, grid {grid[program_axis]})")
+                    dims.append(("xyz"[program_axis], step))
+            views[op.outputs[0]] = (source, dims)
+        else:
+            raise _unsupported(f"'{op.op}' next to an mma on partitioned tiles is not lowered")
+    operands = []
+    for name in mma_op.inputs:
+        if name in views:
+            operands.append(views[name])
+        elif name in positions:
+            spec = _tensor_arg(ir, positions, name, "tiled gemm")[1]
+            operands.append((name, [("all", extent) for extent in spec.shape]))
+        else:
+            raise _unsupported(f"mma operand '{name}' is neither a kernel argument nor a partition of one")
+    if any(len(dims) != 2 for _, dims in operands):
+        raise _unsupported("gemm requires rank-2 operands")
+    (a_name, a_dims), (b_name, b_dims), (c_name, c_dims) = operands
+    transpose_a, transpose_b = bool(mma_op.attrs.get("transpose_a")), bool(mma_op.attrs.get("transpose_b"))
+    a_k, a_m = a_dims if transpose_a else a_dims[::-1]
+    b_n, b_k = b_dims if transpose_b else b_dims[::-1]
+    c_m, c_n = c_dims
+    if a_k[0] != "all" or b_k[0] != "all":
+        raise _unsupported("every program must read the whole K extent (split-K over programs is not lowered)")
+    if a_m != c_m or b_n != c_n:
+        raise _unsupported("the A / B tiles of a program do not line up with its C tile")
+    if c_m[0] != "all" and c_m[0] == c_n[0]:
+        raise _unsupported("rows and columns of C are tiled along the same program axis")
+    tile = mma_op.attrs.get("tile")
+    if tile is not None and tuple(tile) != (c_m[1], c_n[1], a_k[1]):
+        raise _unsupported("the mma tile does not match the partitioned operands")
+    full = PortableKernelIRView(ir, a_name, b_name, c_name)
+    return _match_gemm(full, full.operation(transpose_a, transpose_b))
+
+
+class PortableKernelIRView:
+    """The whole-tensor GEMM a tiled kernel amounts to, in the shape ``_match_gemm`` reads."""
+
+    def __init__(self, ir, a: str, b: str, c: str):
+        self.arguments, self._names = ir.arguments, (a, b, c)
+
+    def operation(self, transpose_a: bool, transpose_b: bool):
+        from ..portable_ir import Operation
+
+        return Operation("mma", self._names, (), {"tile": None, "transpose_a": transpose_a, "transpose_b": transpose_b})
+
+
 def _match_rmsnorm(ir, op) -> RmsNormPlan:
     positions = _argument_positions(ir)
     (x, x_spec), (out, out_spec), (gamma, gamma_spec) = (_tensor_arg(ir, positions, name, "rmsnorm") for name in op.inputs)
@@ -639,7 +729,10 @@ def _match_ssa_elementwise(ir) -> ElementwisePlan:
             known[argument.name] = argument.name
             dtypes[argument.name] = argument.spec.dtype
 
+    consumed = {name for op in ir.operations for name in op.inputs}
     for op in ir.operations:
+        if op.op in TOPOLOGY_OPS and not (set(op.outputs) & consumed):
+            continue  # a topology query whose value is never used has no effect
         if reduction is not None and op.op not in ("constant", "copy", "store"):
             raise _unsupported(f"op '{op.op}' after a reduction is not lowered (only the store of the result is)")
         if op.op.startswith("reduce_"):
@@ -813,6 +906,8 @@ def match(ir):
         raise _unsupported("the kernel body is empty")
     explicit = [op for op in operations if op.op in EXPLICIT]
     if explicit:
+        if len(explicit) == 1 and explicit[0].op == "mma" and any(op.op == "partition" for op in operations):
+            return _match_tiled_gemm(ir, explicit[0])
         if len(operations) != 1:
             raise _unsupported(
                 f"'{explicit[0].op}' must be the only op of the kernel (found {len(operations)} ops); "

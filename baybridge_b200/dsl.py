@@ -245,6 +245,81 @@ def make_tensor(name: str, shape: tuple[int, ...] | None = None, dtype: str | No
 
 
 # ---------------------------------------------------------------------------------------------
+# tile views and barriers
+# ---------------------------------------------------------------------------------------------
+_DEFAULT_AXES = {1: ("x",), 2: ("y", "x"), 3: ("z", "y", "x")}
+
+
+def partition(tensor: TensorValue, tile: tuple[int, ...], *, offset: tuple[Any, ...] | None = None,
+              policy: str = "blocked") -> TensorValue:
+    """A ``tile``-shaped view of ``tensor`` starting at ``offset`` (default: the origin); the view keeps
+    the source's strides.  Recorded as a ``partition`` op (``frontend.py:3553-3607`` upstream)."""
+    if not isinstance(tensor, TensorValue):
+        raise BackendNotImplementedError("partition on a host tensor would execute on the host; baybridge_b200 has no CPU runtime")
+    shape = tensor.spec.shape
+    if len(tile) != len(shape):
+        raise ValueError(f"partition expects a tile rank of {len(shape)}")
+    if any(step <= 0 for step in tile):
+        raise ValueError("partition tile dimensions must be > 0")
+    if any(step > extent for step, extent in zip(tile, shape)):
+        raise ValueError("partition tile dimensions cannot exceed the source tensor shape")
+    builder = require_builder()
+    operands: list[ScalarValue] = []
+    if offset is not None:
+        if len(offset) != len(shape):
+            raise ValueError(f"offset expects {len(shape)} values for tensor rank {len(shape)}")
+        for axis, item in enumerate(offset):
+            if isinstance(item, ScalarValue):
+                operands.append(item)
+                continue
+            if not isinstance(item, int) or isinstance(item, bool):
+                raise TypeError("partition offsets must be ScalarValue or int")
+            if item < 0:
+                raise ValueError("partition offsets must be >= 0")
+            if item + tile[axis] > shape[axis]:
+                raise ValueError("static partition offsets plus tile dimensions must stay within the source tensor shape")
+            operands.append(builder.constant(item))
+    source_layout = tensor.spec.resolved_layout()
+    view_layout = type(source_layout)(shape=tuple(tile), stride=source_layout.stride, swizzle=source_layout.swizzle)
+    view_spec = TensorSpec(tuple(tile), tensor.spec.dtype, view_layout, tensor.spec.address_space)
+    return builder.emit_tensor("partition", tensor, *operands, spec=view_spec,
+                               attrs={"tile": list(tile), "policy": policy}, name_hint=f"{tensor.name}_part")
+
+
+def _axes_for(rank: int, axes: tuple[str, ...] | None) -> tuple[str, ...]:
+    if axes is None:
+        if rank not in _DEFAULT_AXES:
+            raise ValueError("default execution axes are only defined for ranks 1, 2, and 3")
+        axes = _DEFAULT_AXES[rank]
+    if len(axes) != rank:
+        raise ValueError(f"axes must have length {rank} for tensor rank {rank}")
+    for axis in axes:
+        if axis not in ("x", "y", "z"):
+            raise ValueError("axis must be one of: x, y, z")
+    return tuple(axes)
+
+
+def partition_program(tensor: TensorValue, tile: tuple[int, ...], *, axes: tuple[str, ...] | None = None,
+                      policy: str = "blocked") -> TensorValue:
+    """The tile owned by this program: ``offset[d] = program_id(axes[d]) * tile[d]``."""
+    offsets = tuple(program_id(axis) * step for axis, step in zip(_axes_for(len(tile), axes), tile))
+    return partition(tensor, tile, offset=offsets, policy=policy)
+
+
+def partition_thread(tensor: TensorValue, tile: tuple[int, ...], *, axes: tuple[str, ...] | None = None,
+                     policy: str = "blocked") -> TensorValue:
+    """The tile owned by this thread: ``offset[d] = thread_idx(axes[d]) * tile[d]``."""
+    offsets = tuple(thread_idx(axis) * step for axis, step in zip(_axes_for(len(tile), axes), tile))
+    return partition(tensor, tile, offset=offsets, policy=policy)
+
+
+def barrier(*, kind: str = "block", **attrs: Any) -> None:
+    if kind not in {"block", "grid", "warp"}:
+        raise ValueError("barrier kind must be 'block', 'grid', or 'warp'")
+    require_builder().emit_void("barrier", attrs={"kind": kind, **attrs})
+
+
+# ---------------------------------------------------------------------------------------------
 # select and math
 # ---------------------------------------------------------------------------------------------
 def where(predicate: Any, true_value: Any, false_value: Any, *, loc: Any = None, ip: Any = None) -> Any:

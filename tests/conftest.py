@@ -32,6 +32,24 @@ def golden_cases(prefix: str = "") -> list[str]:
     return sorted(path.stem[len("vec_"):] for path in GOLDEN.glob(f"vec_{prefix}*.npz"))
 
 
+def mma_attrs(ir: dict) -> dict:
+    """Attributes of the (single) mma op of a GEMM listing, whole-tensor or written per program."""
+    (op,) = [op for op in ir["operations"] if op["op"] == "mma"]
+    return op["attrs"]
+
+
+def gemm_zoo_kernel(case: str, ir: dict, zoo):
+    """The zoo kernel a ``gemm_*`` / ``c3_*`` fixture was generated from."""
+    attrs = mma_attrs(ir)
+    if case.startswith("gemm_tiled_programs"):
+        (m, k), (_, n) = ir["arguments"][0]["spec"]["shape"], ir["arguments"][2]["spec"]["shape"]
+        tile_m, tile_n, _ = attrs["tile"]
+        return zoo.make_tiled_gemm(m, n, k, tile_m, tile_n, transpose_b=attrs["transpose_b"], block=ir["launch"]["block"][0])
+    return {(False, False): zoo.gemm_ab, (False, True): zoo.gemm_abt, (True, False): zoo.gemm_atb, (True, True): zoo.gemm_atbt}[
+        (attrs["transpose_a"], attrs["transpose_b"])
+    ]
+
+
 @pytest.fixture(scope="session")
 def zoo():
     import baybridge_b200 as cute

@@ -257,6 +257,36 @@ def main() -> None:
         {"a": (ramp, "bf16"), "b": (eye, "bf16"), "c": (np.zeros((32, 32)), "f32")},
         ["c"],
     )
+    # the same product written as a grid of programs, each owning one tile (mma inside a larger kernel)
+    run_case(
+        "gemm_tiled_programs_abt_48x40x64_t16x8",
+        zoo.make_tiled_gemm(m, n_, k, 16, 8),
+        {"a": (a, "bf16"), "b": (b, "bf16"), "c": (np.zeros((m, n_)), "bf16")},
+        ["c"],
+    )
+    run_case(
+        "gemm_tiled_programs_ab_48x40x64_t24x40",
+        zoo.make_tiled_gemm(m, n_, k, 24, 40, transpose_b=False, block=2),
+        {"a": (a, "bf16"), "b": (np.ascontiguousarray(b.T), "bf16"), "c": (np.zeros((m, n_)), "f32")},
+        ["c"],
+    )
+    # tests/test_backend_hipkittens_exec.py:60-74 — 64x64x32 ramp A, B with two unit diagonals per half
+    ramp2 = np.array([[row * 32 + col + 1 for col in range(32)] for row in range(64)], dtype=np.float32)
+    twin = np.zeros((32, 64), dtype=np.float32)
+    for row in range(32):
+        if row < 16:
+            twin[row, row] = twin[row, row + 16] = 1.0
+        else:
+            twin[row, row - 16 + 32] = twin[row, row - 16 + 48] = 1.0
+    run_case(
+        "gemm_ab_ramp_twin_diagonals_64x64x32",
+        zoo.gemm_ab,
+        {"a": (ramp2, "bf16"), "b": (twin, "bf16"), "c": (np.zeros((64, 64)), "f32")},
+        ["c"],
+    )
+    dump_ir("api_vector_copy_128_f16", zoo.api_vector_copy, ShapeOnly((128,), "float16"), ShapeOnly((128,), "float16"))
+    dump_ir("api_tile_mma_64x64_f16", zoo.api_tile_mma, ShapeOnly((64, 64), "float16"), ShapeOnly((64, 64), "float16"))
+    dump_ir("api_topology_128_f16", zoo.api_topology, ShapeOnly((128,), "float16"), ShapeOnly((128,), "float16"))
     dump_ir(
         "c3_gemm_abt_8192_bf16",
         zoo.gemm_abt,

@@ -211,6 +211,51 @@ def build_zoo(cute) -> SimpleNamespace:
 
     zoo.gemm_atbt = gemm_atbt
 
+    # a GEMM written per program: every program multiplies its own tiles of A and B into its tile of C
+    def make_tiled_gemm(m: int, n: int, k: int, tile_m: int, tile_n: int, *, transpose_b: bool = True, block: int = 1):
+        @cute.kernel(launch=cute.LaunchConfig(grid=(m // tile_m, n // tile_n, 1), block=(block, 1, 1)))
+        def tiled_gemm_kernel(a: cute.Tensor, b: cute.Tensor, c: cute.Tensor):
+            a_tile = cute.partition_program(a, (tile_m, k), axes=("x", "z"))
+            if transpose_b:
+                b_tile = cute.partition_program(b, (tile_n, k), axes=("y", "z"))
+            else:
+                b_tile = cute.partition_program(b, (k, tile_n), axes=("z", "y"))
+            c_tile = cute.partition_program(c, (tile_m, tile_n), axes=("x", "y"))
+            cute.gemm(a_tile, b_tile, c_tile, transpose_b=transpose_b)
+            cute.barrier()
+
+        return tiled_gemm_kernel
+
+    zoo.make_tiled_gemm = make_tiled_gemm
+
+    # tracing-only shapes of upstream's tests/test_api.py:6-36 (views, register accumulator, barrier, topology)
+    @cute.kernel
+    def api_vector_copy(src: cute.Tensor, dst: cute.Tensor):
+        cute.copy(src, dst, vector_bytes=16)
+
+    zoo.api_vector_copy = api_vector_copy
+
+    @cute.jit(launch=cute.LaunchConfig(grid=(80, 1, 1), block=(256, 1, 1), shared_mem_bytes=4096))
+    def api_tile_mma(a: cute.Tensor, b: cute.Tensor):
+        a_tile = cute.partition(a, (16, 16))
+        b_tile = cute.partition(b, (16, 16))
+        cute.mma(a_tile, b_tile, tile=(16, 16, 16))
+        cute.barrier()
+
+    zoo.api_tile_mma = api_tile_mma
+
+    @cute.kernel(launch=cute.LaunchConfig(grid=(120, 3, 1), block=(256, 1, 1)))
+    def api_topology(src: cute.Tensor, dst: cute.Tensor):
+        cute.program_id("x")
+        cute.block_idx("y")
+        cute.thread_idx("x")
+        cute.block_dim("x")
+        cute.grid_dim("y")
+        cute.lane_id()
+        cute.copy(src, dst)
+
+    zoo.api_topology = api_topology
+
     def make_rmsnorm(epsilon: float | None = None):
         if epsilon is None:
 

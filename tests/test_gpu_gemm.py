@@ -6,7 +6,7 @@ from __future__ import annotations
 
 import numpy as np
 import pytest
-from conftest import golden_cases, golden_ir, golden_vec
+from conftest import gemm_zoo_kernel, golden_cases, golden_ir, golden_vec
 from gpu_util import current_stream, device_zeros, to_device, to_host, void_p
 
 from oracle import cpu_runtime as oracle
@@ -22,10 +22,7 @@ def test_compiled_gemm_matches_upstream_vectors(case, zoo, tmp_path):
 
     ir = golden_ir(case)["ir"]
     vec = golden_vec(case)
-    attrs = ir["operations"][0]["attrs"]
-    kernel = {(False, False): zoo.gemm_ab, (False, True): zoo.gemm_abt, (True, False): zoo.gemm_atb, (True, True): zoo.gemm_atbt}[
-        (attrs["transpose_a"], attrs["transpose_b"])
-    ]
+    kernel = gemm_zoo_kernel(case, ir, zoo)
     c_dtype = ir["arguments"][2]["spec"]["dtype"]
     a, b = to_device(vec["in_a"], "bf16"), to_device(vec["in_b"], "bf16")
     c = device_zeros(vec["out_c"].shape, c_dtype)
@@ -33,9 +30,9 @@ def test_compiled_gemm_matches_upstream_vectors(case, zoo, tmp_path):
     assert artifact.ir.to_dict()["operations"] == ir["operations"]
     artifact(a, b, c)
     got = to_host(c)
-    if case == "gemm_ab_ramp_identity_32x32x16":
-        # upstream tests/test_backend_hipkittens_exec.py:380-407: C[:, :16] equals the ramp A exactly as the
-        # device sees it.  The ramp reaches 512, beyond bf16's 8 significant bits, so the device operand is
+    if case.startswith("gemm_ab_ramp_"):
+        # upstream tests/test_backend_hipkittens_exec.py:380-440: every column of C picks one column of the ramp A,
+        # exactly as the device sees it.  The ramps reach 512 and 2048, beyond bf16's 8 significant bits, so the device operand is
         # RNE(A) (the CPU runtime keeps the unrounded Python floats, which is what the fixture holds).
         expected = oracle.gemm(oracle.bf16_round(vec["in_a"]), vec["in_b"])
         assert np.array_equal(got, expected)

@@ -9,7 +9,7 @@ import sys
 from pathlib import Path
 
 import pytest
-from conftest import GOLDEN, golden_ir
+from conftest import GOLDEN, gemm_zoo_kernel, golden_ir
 
 import baybridge_b200 as cute
 from baybridge_b200.backend.matcher import match
@@ -74,8 +74,10 @@ def _zoo_kernel(case: str, zoo):
         return getattr(zoo, "_".join(parts[:-2]))
     if case.startswith(("c5_", "attn_")):
         return zoo.attention_causal if "causal" in case else zoo.attention_full
+    if case.startswith("api_"):
+        return next(getattr(zoo, name) for name in ("api_vector_copy", "api_tile_mma", "api_topology") if case.startswith(name))
     if case.startswith("gemm_"):
-        return getattr(zoo, "gemm_" + parts[1])
+        return gemm_zoo_kernel(case, golden_ir(case)["ir"], zoo)
     return table[parts[0]]()
 
 
@@ -94,6 +96,11 @@ def test_traced_ir_and_cache_key_equal_upstream(case, zoo, tmp_path):
 
 @pytest.mark.parametrize("case", ALL_IR_CASES)
 def test_matcher_classifies_every_listing(case):
+    if case.startswith("api_tile_mma"):
+        # an mma on a corner tile into a discarded register accumulator has no whole-GEMM meaning: refused, not guessed
+        with pytest.raises(cute.BackendNotImplementedError, match="partition at a fixed offset"):
+            match(PortableKernelIR.from_dict(golden_ir(case)["ir"]))
+        return
     plan = match(PortableKernelIR.from_dict(golden_ir(case)["ir"]))
     if case.startswith(("c3_", "gemm_")):
         assert plan.kind == "gemm"
@@ -150,6 +157,43 @@ def test_non_bijective_indexing_is_lowered_literally_and_unknown_ops_are_rejecte
 
     with pytest.raises(cute.BackendNotImplementedError, match="only op"):
         cute.compile(two_ops, backend="b200", cache_dir=tmp_path)
+
+
+def test_program_tiled_gemm_lowers_to_the_whole_gemm_or_is_refused(zoo, tmp_path):
+    spec = lambda rows, cols, dtype="bf16": cute.TensorSpec(shape=(rows, cols), dtype=dtype)  # noqa: E731
+
+    carriers = [FakeCudaTensor(shape, "bfloat16") for shape in ((256, 128), (512, 128), (256, 512))]
+    plan = match(cute.compile(zoo.make_tiled_gemm(256, 512, 128, 64, 128), *carriers, backend="portable", cache_dir=tmp_path).ir)
+    assert (plan.kind, plan.m, plan.n, plan.k, plan.transpose_b) == ("gemm", 256, 512, 128, True)
+    lowered = cute.compile(zoo.make_tiled_gemm(256, 512, 128, 64, 128), *carriers, backend="b200", cache_dir=tmp_path)
+    assert lowered.lowered_module.entry_point == "bb200_gemm_bf16"
+
+    # the grid leaves rows of C uncovered: not a whole GEMM
+    @cute.kernel(launch=cute.LaunchConfig(grid=(3, 4, 1), block=(1, 1, 1)))
+    def short_grid(a: spec(256, 128), b: spec(512, 128), c: spec(256, 512)):
+        cute.gemm(cute.partition_program(a, (64, 128), axes=("x", "z")), cute.partition_program(b, (128, 128), axes=("y", "z")),
+                  cute.partition_program(c, (64, 128), axes=("x", "y")), transpose_b=True)
+
+    with pytest.raises(cute.BackendNotImplementedError, match="must tile axis 0"):
+        cute.compile(short_grid, backend="b200", cache_dir=tmp_path)
+
+    # programs along z each take a slice of K and overwrite C: split-K is not a GEMM
+    @cute.kernel(launch=cute.LaunchConfig(grid=(4, 4, 2), block=(1, 1, 1)))
+    def split_k(a: spec(256, 128), b: spec(512, 128), c: spec(256, 512)):
+        cute.gemm(cute.partition_program(a, (64, 64), axes=("x", "z")), cute.partition_program(b, (128, 64), axes=("y", "z")),
+                  cute.partition_program(c, (64, 128), axes=("x", "y")), transpose_b=True)
+
+    with pytest.raises(cute.BackendNotImplementedError, match="whole K extent"):
+        cute.compile(split_k, backend="b200", cache_dir=tmp_path)
+
+    # A rows follow program x but C rows follow program y
+    @cute.kernel(launch=cute.LaunchConfig(grid=(4, 4, 1), block=(1, 1, 1)))
+    def crossed(a: spec(256, 128), b: spec(256, 128), c: spec(256, 256)):
+        cute.gemm(cute.partition_program(a, (64, 128), axes=("x", "z")), cute.partition_program(b, (64, 128), axes=("y", "z")),
+                  cute.partition_program(c, (64, 64), axes=("y", "x")), transpose_b=True)
+
+    with pytest.raises(cute.BackendNotImplementedError, match="do not line up"):
+        cute.compile(crossed, backend="b200", cache_dir=tmp_path)
 
 
 def test_compile_hits_cache_and_writes_manifest(zoo, tmp_path):

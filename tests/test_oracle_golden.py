@@ -5,7 +5,7 @@ import hashlib
 
 import numpy as np
 import pytest
-from conftest import golden_cases, golden_ir, golden_vec
+from conftest import golden_cases, golden_ir, golden_vec, mma_attrs
 
 from oracle import cpu_runtime as oracle
 
@@ -61,7 +61,7 @@ def test_traced_kernel_interpreter_matches_upstream(case: str):
 @pytest.mark.parametrize("case", golden_cases("c3_") + golden_cases("gemm_"))
 def test_gemm_matches_upstream(case: str):
     vec = golden_vec(case)
-    attrs = golden_ir(case)["ir"]["operations"][0]["attrs"]
+    attrs = mma_attrs(golden_ir(case)["ir"])
     got = oracle.gemm(vec["in_a"], vec["in_b"], transpose_a=attrs["transpose_a"], transpose_b=attrs["transpose_b"])
     np.testing.assert_allclose(got, vec["out_c"], rtol=TIGHT, atol=1e-15)
 
