@@ -242,9 +242,9 @@ gemm_abt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   }
 }
 
-// ---- CTA-pair variant (A · B^T with B stored [n, k]) ---------------------------------------------------
+// ---- CTA-pair variant ----------------------------------------------------------------------------------
 // Two CTAs of a cluster (neighbouring SMs) own one 256x256 tile of C.  Each CTA streams its own 128
-// rows of A and its own 128 rows (half) of the B tile, so a stage is 32 KB instead of 48 KB and the
+// rows of A and its own half (128 of the 256 n) of the B tile, so a stage is 32 KB instead of 48 KB and the
 // ring holds 6 stages; CTA 0 issues tcgen05.mma.cta_group::2 (M256 x N256 x K16), which reads A from
 // each CTA's shared memory, B from both halves, and writes each CTA's 128 accumulator lanes in that
 // CTA's TMEM.  Per k-block the pair moves 64 KB for 8.4 MFLOP: a third less shared-memory and L2
@@ -260,7 +260,7 @@ constexpr int PAIR_STAGE_BYTES = A_TILE_BYTES + PAIR_B_BYTES;
 constexpr int PAIR_SMEM_BYTES = PAIR_STAGES * PAIR_STAGE_BYTES + 1024 + 256;
 constexpr int PAIR_BM = 2 * BM;
 
-template <typename OutT>
+template <typename OutT, bool B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 gemm_abt_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, OutT* __restrict__ c,
                      int m, int n, int k, int group_m, int* status_word) {
@@ -325,7 +325,13 @@ gemm_abt_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
           const uint32_t signal = leader_cta_address(full_bar(stage));
           if (leader) mbar_arrive_expect_tx(full_bar(stage), 2 * PAIR_STAGE_BYTES);
           tma_load_2d_pair(a_dst, &map_a, signal, kb * BK, a_row);
-          tma_load_2d_pair(a_dst + A_TILE_BYTES, &map_b, signal, kb * BK, b_row);
+          if constexpr (B_MN) {
+#pragma unroll
+            for (int t = 0; t < PAIR_B_ROWS / 64; ++t)
+              tma_load_2d_pair(a_dst + A_TILE_BYTES + t * (BK * 128), &map_b, signal, b_row + t * 64, kb * BK);
+          } else {
+            tma_load_2d_pair(a_dst + A_TILE_BYTES, &map_b, signal, kb * BK, b_row);
+          }
           if (++stage == PAIR_STAGES) { stage = 0; phase ^= 1u; }
         }
       }
@@ -333,7 +339,8 @@ gemm_abt_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   } else if (warp == 1) {
     // ---------------- MMA issuer (CTA 0 only) ----------------
     if (leader && elect_one()) {
-      constexpr uint32_t idesc = umma_idesc_bf16_f32(PAIR_BM, BN, false, false);
+      constexpr uint32_t idesc = umma_idesc_bf16_f32(PAIR_BM, BN, false, B_MN);
+      constexpr uint32_t b_step = B_MN ? UMMA_K * 128 : UMMA_K * 2;
       int stage = 0;
       uint32_t phase = 0;
       int local_tile = 0;
@@ -349,10 +356,11 @@ gemm_abt_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
           tcgen05_fence_after();
           const uint32_t a_src = smem_base + stage * PAIR_STAGE_BYTES;
           const uint64_t desc_a = umma_desc_k_major_sw128(a_src);
-          const uint64_t desc_b = umma_desc_k_major_sw128(a_src + A_TILE_BYTES);
+          const uint64_t desc_b = B_MN ? umma_desc_mn_major_sw128(a_src + A_TILE_BYTES, BK * 128)
+                                       : umma_desc_k_major_sw128(a_src + A_TILE_BYTES);
 #pragma unroll
           for (int kk = 0; kk < BK / UMMA_K; ++kk)
-            umma_bf16_ss_pair(tmem_acc, umma_desc_advance_k(desc_a, kk * UMMA_K * 2), umma_desc_advance_k(desc_b, kk * UMMA_K * 2),
+            umma_bf16_ss_pair(tmem_acc, umma_desc_advance_k(desc_a, kk * UMMA_K * 2), umma_desc_advance_k(desc_b, kk * b_step),
                               idesc, (kb | kk) != 0 ? 1u : 0u);
           umma_commit_pair(empty_bar(stage), 0x3);
           if (++stage == PAIR_STAGES) { stage = 0; phase ^= 1u; }
@@ -471,21 +479,23 @@ bool use_pair_kernel(int m, int n, int sms) {
   return (sms % 2) == 0 && tiles >= sms / 2;
 }
 
-template <typename OutT>
-int launch_pair(const void* a_mk, const void* b_nk, void* c, int m, int n, int k, int device, int sms, cudaStream_t stream) {
+template <typename OutT, bool B_MN>
+int launch_pair(const void* a_mk, const void* b, void* c, int m, int n, int k, int device, int sms, cudaStream_t stream) {
   alignas(64) CUtensorMap map_a, map_b;
   if (int status = encode_tensormap_2d(&map_a, BB200_BF16, a_mk, (uint64_t)m, (uint64_t)k, (uint64_t)k * 2, BM, BK, 3)) return status;
-  if (int status = encode_tensormap_2d(&map_b, BB200_BF16, b_nk, (uint64_t)n, (uint64_t)k, (uint64_t)k * 2, PAIR_B_ROWS, BK, 3)) return status;
+  if (int status = B_MN ? encode_tensormap_2d(&map_b, BB200_BF16, b, (uint64_t)k, (uint64_t)n, (uint64_t)n * 2, BK, 64, 3)
+                        : encode_tensormap_2d(&map_b, BB200_BF16, b, (uint64_t)n, (uint64_t)k, (uint64_t)k * 2, PAIR_B_ROWS, BK, 3))
+    return status;
   static bool configured[kMaxDevices] = {};
   if (!configured[device]) {
-    if (int status = check_runtime(cudaFuncSetAttribute(gemm_abt_pair_kernel<OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM_BYTES),
+    if (int status = check_runtime(cudaFuncSetAttribute(gemm_abt_pair_kernel<OutT, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM_BYTES),
                                    "cudaFuncSetAttribute(gemm pair smem)"))
       return status;
     configured[device] = true;
   }
   const int tiles = ((m + PAIR_BM - 1) / PAIR_BM) * ((n + BN - 1) / BN);
   const int pairs = tiles < sms / 2 ? tiles : sms / 2;
-  gemm_abt_pair_kernel<OutT><<<2 * pairs, THREADS, PAIR_SMEM_BYTES, stream>>>(map_a, map_b, static_cast<OutT*>(c), m, n, k, raster_group_m() / 2 > 0 ? raster_group_m() / 2 : 1,
+  gemm_abt_pair_kernel<OutT, B_MN><<<2 * pairs, THREADS, PAIR_SMEM_BYTES, stream>>>(map_a, map_b, static_cast<OutT*>(c), m, n, k, raster_group_m() / 2 > 0 ? raster_group_m() / 2 : 1,
                                                                              device_status_word());
   return check_launch("gemm pair kernel launch");
 }
@@ -509,9 +519,7 @@ int launch_native(const void* a_mk, const void* b, void* c, int m, int n, int k,
   }
   const int sms = cached_sm_count(device);
   if (sms <= 0) return fail(BB200_E_NO_DRIVER, "gemm: could not query the SM count");
-  if constexpr (!B_MN) {
-    if (use_pair_kernel(m, n, sms)) return launch_pair<OutT>(a_mk, b, c, m, n, k, device, sms, stream);
-  }
+  if (use_pair_kernel(m, n, sms)) return launch_pair<OutT, B_MN>(a_mk, b, c, m, n, k, device, sms, stream);
   const int tiles = ((m + BM - 1) / BM) * ((n + BN - 1) / BN);
   const int grid = tiles < sms ? tiles : sms;
   gemm_abt_kernel<OutT, B_MN><<<grid, THREADS, SMEM_BYTES, stream>>>(map_a, map_b, static_cast<OutT*>(c), m, n, k, raster_group_m(), device_status_word());
