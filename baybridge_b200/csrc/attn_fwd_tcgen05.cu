@@ -62,6 +62,13 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+// max(a, b, c) in one instruction
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 template <int D, bool CAUSAL>
 __global__ void __launch_bounds__(THREADS, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -72,15 +79,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   const uint32_t base = (smem_addr(smem_raw) + 1023u) & ~1023u;
   uint8_t* aligned = smem_raw + (base - smem_addr(smem_raw));
   const uint32_t bar_base = base + L::BAR_OFF;
-  // barriers: q_full, k_full[2], v_full[2], kv_empty[2], s_ready[2], p_ready[2], o_done[2]
+  // barriers: q_full, k_full[2], v_full[2], kv_empty[2], s_ready[2], p_ready[2 tiles][2 halves], o_done[2]
   const uint32_t q_full = bar_base;
   auto k_full = [&](int s) { return bar_base + 8u * (1 + s); };
   auto v_full = [&](int s) { return bar_base + 8u * (3 + s); };
   auto kv_empty = [&](int s) { return bar_base + 8u * (5 + s); };
   auto s_ready = [&](int t) { return bar_base + 8u * (7 + t); };
-  auto p_ready = [&](int t) { return bar_base + 8u * (9 + t); };
-  auto o_done = [&](int t) { return bar_base + 8u * (11 + t); };
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(aligned + L::BAR_OFF + 8 * 13);
+  auto p_ready = [&](int t, int half) { return bar_base + 8u * (9 + 2 * t + half); };
+  auto o_done = [&](int t) { return bar_base + 8u * (13 + t); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(aligned + L::BAR_OFF + 8 * 15);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -108,7 +115,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     }
     for (int t = 0; t < Q_TILES; ++t) {
       mbar_init(s_ready(t), 1);
-      mbar_init(p_ready(t), 128);
+      mbar_init(p_ready(t, 0), 4);  // one arrival per softmax warp
+      mbar_init(p_ready(t, 1), 4);
       mbar_init(o_done(t), 1);
     }
     *abort_flag = 0;
@@ -173,16 +181,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         }
         umma_commit(s_ready(t));
       };
-      auto issue_pv = [&](int t, int j) {  // O_t (+)= P_t · V_j, P_t packed bf16 in the first 64 columns of S_t
+      // O_t (+)= P_t · V_j over keys [64*half, 64*half+64); P_t is packed bf16 in the first 64 columns of S_t
+      auto issue_pv = [&](int t, int j, int half) {
         const uint32_t v_src = base + L::KV_OFF + (j & 1) * (L::K_BYTES + L::V_BYTES) + L::K_BYTES;
         const uint64_t desc_v = umma_desc_mn_major_sw128(v_src, SUBTILE_BYTES);
         const uint32_t p_addr = tmem_base + (uint32_t)(t * BLOCK_N);
         const uint32_t o_addr = tmem_base + 256u + (uint32_t)(t * 128);
 #pragma unroll
-        for (int kk = 0; kk < BLOCK_N / 16; ++kk)
+        for (int kk = half * 4; kk < half * 4 + 4; ++kk)
           umma_bf16_ts(o_addr, p_addr + (uint32_t)(kk * 8), umma_desc_advance_k(desc_v, kk * 2048), idesc_pv,
                        (j | kk) != 0 ? 1u : 0u);
-        umma_commit(o_done(t));
+        if (half == 1) umma_commit(o_done(t));
       };
       bool ok = mbar_wait(q_full, 0, abort_flag, status_word, kWaitQ);
       if (ok && kv_blocks > 0) ok = mbar_wait(k_full(0), 0, abort_flag, status_word, kWaitK);
@@ -199,9 +208,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 #pragma unroll
         for (int t = 0; t < Q_TILES; ++t) {
           if (j < blocks_of[t]) {
-            if (!(ok = mbar_wait(p_ready(t), (uint32_t)j & 1u, abort_flag, status_word, kWaitPReady))) break;
+            // the first 64 keys of P arrive while the softmax warps still work on the last 64
+            if (!(ok = mbar_wait(p_ready(t, 0), (uint32_t)j & 1u, abort_flag, status_word, kWaitPReady))) break;
             tcgen05_fence_after();
-            issue_pv(t, j);
+            issue_pv(t, j, 0);
+            if (!(ok = mbar_wait(p_ready(t, 1), (uint32_t)j & 1u, abort_flag, status_word, kWaitPReady))) break;
+            tcgen05_fence_after();
+            issue_pv(t, j, 1);
           }
           if (next < blocks_of[t]) {
             if (!next_k_ready) {
@@ -252,11 +265,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       // four independent chains instead of one 128-long dependency chain
       float max0 = -INFINITY, max1 = -INFINITY, max2 = -INFINITY, max3 = -INFINITY;
 #pragma unroll
-      for (int i = 0; i < BLOCK_N; i += 4) {
-        max0 = fmaxf(max0, __uint_as_float(s[i]));
-        max1 = fmaxf(max1, __uint_as_float(s[i + 1]));
-        max2 = fmaxf(max2, __uint_as_float(s[i + 2]));
-        max3 = fmaxf(max3, __uint_as_float(s[i + 3]));
+      for (int i = 0; i < BLOCK_N; i += 8) {
+        max0 = fmax3(max0, __uint_as_float(s[i]), __uint_as_float(s[i + 1]));
+        max1 = fmax3(max1, __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
+        max2 = fmax3(max2, __uint_as_float(s[i + 4]), __uint_as_float(s[i + 5]));
+        max3 = fmax3(max3, __uint_as_float(s[i + 6]), __uint_as_float(s[i + 7]));
       }
       const float block_max = fmaxf(fmaxf(max0, max1), fmaxf(max2, max3));
       const float candidate = fmaxf(used_max, block_max * scale_log2e);  // scale > 0 commutes with max
@@ -285,26 +298,31 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       }
       const float shift = used_max == -INFINITY ? 0.0f : -used_max;  // fully masked so far: 2^(-inf) = 0
       float sum0 = 0.0f, sum1 = 0.0f, sum2 = 0.0f, sum3 = 0.0f;
-      // packed in place: word i/2 of `s` is free once scores i and i+1 have been consumed
+      // Two halves of 64 keys; each is published as soon as it is in TMEM so P·V starts on the first
+      // half while the second is still being exponentiated.  Packed in place: word i/2 of `s` is free
+      // once scores i and i+1 have been consumed.  P overwrites the first 64 columns of this tile's S
+      // (each thread only touches its own lane).
 #pragma unroll
-      for (int i = 0; i < BLOCK_N; i += 4) {
-        const float p0 = fast_exp2(fmaf(__uint_as_float(s[i]), scale_log2e, shift));
-        const float p1 = fast_exp2(fmaf(__uint_as_float(s[i + 1]), scale_log2e, shift));
-        const float p2 = fast_exp2(fmaf(__uint_as_float(s[i + 2]), scale_log2e, shift));
-        const float p3 = fast_exp2(fmaf(__uint_as_float(s[i + 3]), scale_log2e, shift));
-        sum0 += p0; sum1 += p1; sum2 += p2; sum3 += p3;
-        const __nv_bfloat162 lo = __floats2bfloat162_rn(p0, p1);  // low half = even key
-        const __nv_bfloat162 hi = __floats2bfloat162_rn(p2, p3);
-        s[i >> 1] = *reinterpret_cast<const uint32_t*>(&lo);
-        s[(i >> 1) + 1] = *reinterpret_cast<const uint32_t*>(&hi);
+      for (int half = 0; half < 2; ++half) {
+#pragma unroll
+        for (int i = half * 64; i < half * 64 + 64; i += 4) {
+          const float p0 = fast_exp2(fmaf(__uint_as_float(s[i]), scale_log2e, shift));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(s[i + 1]), scale_log2e, shift));
+          const float p2 = fast_exp2(fmaf(__uint_as_float(s[i + 2]), scale_log2e, shift));
+          const float p3 = fast_exp2(fmaf(__uint_as_float(s[i + 3]), scale_log2e, shift));
+          sum0 += p0; sum1 += p1; sum2 += p2; sum3 += p3;
+          const __nv_bfloat162 lo = __floats2bfloat162_rn(p0, p1);  // low half = even key
+          const __nv_bfloat162 hi = __floats2bfloat162_rn(p2, p3);
+          s[i >> 1] = *reinterpret_cast<const uint32_t*>(&lo);
+          s[(i >> 1) + 1] = *reinterpret_cast<const uint32_t*>(&hi);
+        }
+        tmem_st_32x32b_x32(s_addr + (uint32_t)(half * 32), *reinterpret_cast<uint32_t(*)[32]>(&s[half * 32]));
+        tmem_st_wait();
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(p_ready(tile, half));
       }
       row_sum += (sum0 + sum1) + (sum2 + sum3);
-      // P overwrites the first 64 columns of this tile's S (each thread only touches its own lane)
-      tmem_st_32x32b_x32(s_addr, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
-      tmem_st_32x32b_x32(s_addr + 32u, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
-      tmem_st_wait();
-      tcgen05_fence_before();
-      mbar_arrive(p_ready(tile));
     }
     if (ok && my_blocks > 0) {
       ok = mbar_wait(o_done(tile), (uint32_t)(my_blocks - 1) & 1u, abort_flag, status_word, kWaitODone);
