@@ -6,31 +6,26 @@
 // rows are `heads*head_dim` elements apart; TMA reads it through a 3-D map (head_dim*heads, seq,
 // batch) and zero-fills rows past `seq`.
 //
-// One CTA handles TWO 128-query tiles of one (batch, head) and walks the keys once for both, in blocks
-// of 64 keys (only blocks at or below the diagonal when causal).  Each tile has TWO score buffers in
-// TMEM, so S(j+1) = Q·K(j+1)^T is computed while the softmax warps still work on S(j): the softmax
-// warps never wait for the tensor pipe in steady state, and the tensor pipe always has the other
-// tile's and the next block's MMAs queued.  384 threads in three warpgroups; warpgroup 0 gives
-// registers back (setmaxnreg):
-//   warp 0       TMA producer: both Q tiles once, then K and V in tiles of 128 keys (two blocks) into
-//                two 2-stage rings; K and V stages are released separately because a K tile is last
-//                read (by Q·K^T) about three blocks before the V tile of the same keys (by P·V).
-//   warps 1, 2   MMA issuers, one elected thread per query tile t.  Per block j:  S_t[j&1] = Q_t·K_j^T  into
-//                TMEM (both operands K-major in shared memory), later  O_t += P_t·V_j  with P_t read from
-//                TMEM and V_j consumed in place as an MN-major shared-memory operand.  Issue order per
-//                tile: QK(0), QK(1), then per block j: PV(j), QK(j+2).  tcgen05.mma blocks the issuing
-//                thread while the pipe is busy, so one thread per tile keeps both streams flowing.
+// One CTA handles TWO 128-query tiles of one (batch, head) and walks the key/value blocks of 128
+// keys once for both (only blocks at or below the diagonal when causal).  384 threads in three
+// warpgroups; warpgroup 0 gives registers back (setmaxnreg) so the softmax warpgroups can hold a
+// full 128-column score row per thread:
+//   warp 0       TMA producer: both Q tiles once, then K and V blocks into a 2-stage ring.
+//   warp 1       MMA issuer (one elected thread).  Per tile t and block j:  S_t = Q_t·K_j^T  into TMEM
+//                (both operands K-major in shared memory), later  O_t += P_t·V_j  with P_t read from
+//                TMEM and V_j consumed in place as an MN-major shared-memory operand.  The issue order
+//                QK0, QK1, {PV0, QK0', PV1, QK1'}… keeps the tensor pipe busy with one tile while the
+//                other tile's softmax runs.
 //   warps 4..7   softmax of tile 0, warps 8..11 softmax of tile 1; thread = query row.  The fp32 score
-//                row of a block (64 registers) is read from TMEM once, p = 2^(s·c − m·c) is written back
-//                over the first half of the same buffer as packed bf16, and the row sum is kept in fp32.
-//                O stays in TMEM for the whole walk; it is rescaled (tcgen05.ld / st) only when some row
-//                of the warp sees its running maximum grow by more than 2^8, so most blocks skip it.
-// TMEM (512 columns): S_t[b] at 64·(2t+b) for t, b in {0,1}; O0 [256,256+D), O1 [384,384+D).
+//                row is read from TMEM once (128 registers), p = 2^(s·c − m·c) is written back over
+//                the same TMEM columns as packed bf16, and the row sum is kept in fp32.  O stays in
+//                TMEM for the whole walk; it is rescaled (tcgen05.ld / st) only when some row of the
+//                warp sees its running maximum grow by more than 2^8, so most blocks skip it.
+// TMEM (512 columns): S0/P0 [0,128), S1/P1 [128,256), O0 [256,256+D), O1 [384,384+D).
 // Tensor-core bound (4·B·H·D·S(S+1)/2 flops causal); HBM traffic is ~4·B·S·H·D·2 bytes.
 // Head dims other than 64/128 use a plain SIMT kernel below.
 #include <cuda_bf16.h>
 #include <math.h>
-#include <stdlib.h>
 
 #include "bb200_internal.h"
 #include "bb200_sm100.cuh"
@@ -40,23 +35,20 @@ namespace {
 
 using namespace sm100;
 
-constexpr int BLOCK_M = 128;               // queries per tile
-constexpr int BLOCK_N = 64;                // keys per score block
-constexpr int KV_TILE = 128;               // keys per shared-memory tile (two score blocks)
+constexpr int BLOCK_M = 128, BLOCK_N = 128;
 constexpr int Q_TILES = 2;                 // query tiles per CTA
 constexpr int KV_STAGES = 2;
 constexpr int THREADS = 128 * (1 + Q_TILES);  // warpgroup 0: TMA + MMA warps; warpgroups 1..2: softmax of tile 0 / 1
 constexpr int SUBTILE_BYTES = 128 * 128;   // [128 rows, 64 bf16] with 128-byte rows
-constexpr int BLOCK_ROW_BYTES = BLOCK_N * 128;  // offset of the second block's rows inside a sub-tile
 constexpr float RESCALE_THRESHOLD = 8.0f;  // in log2 units: p stays below 2^8 between rescales
 
-enum WaitCode { kWaitQ = 201, kWaitKEmpty = 202, kWaitK = 203, kWaitV = 204, kWaitSReady = 205, kWaitPReady = 206,
-                kWaitODone = 207, kWaitVEmpty = 208 };
+enum WaitCode { kWaitQ = 201, kWaitKvEmpty = 202, kWaitK = 203, kWaitV = 204, kWaitSReady = 205, kWaitPReady = 206,
+                kWaitODone = 207 };
 
 template <int D> struct Smem {
   static constexpr int DCH = D / 64;                       // 64-column sub-tiles per row block
   static constexpr int Q_BYTES = DCH * SUBTILE_BYTES;      // one query tile
-  static constexpr int K_BYTES = DCH * SUBTILE_BYTES;      // one tile of 128 keys
+  static constexpr int K_BYTES = DCH * SUBTILE_BYTES;
   static constexpr int V_BYTES = DCH * SUBTILE_BYTES;
   static constexpr int Q_OFF = 0;
   static constexpr int KV_OFF = Q_OFF + Q_TILES * Q_BYTES;
@@ -77,64 +69,7 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
   return d;
 }
 
-// ---- packed fp32 pairs: one instruction does two lanes' worth of fp32 add / fma -----------------------
-using f32x2 = unsigned long long;
-__device__ __forceinline__ f32x2 pack2(float lo, float hi) {
-  f32x2 r;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
-  return r;
-}
-__device__ __forceinline__ void unpack2(f32x2 v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
-__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
-  f32x2 d;
-  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
-  return d;
-}
-__device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) {
-  f32x2 d;
-  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-  return d;
-}
-__device__ __forceinline__ f32x2 sub2(f32x2 a, f32x2 b) {
-  f32x2 d;
-  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-  return d;
-}
-
-// 2^x for a pair.  POLY = false: two special-function-unit exponentials.  POLY = true: on the FMA and
-// integer pipes — round x to the nearest integer n with the 1.5*2^23 trick, evaluate a cubic for
-// 2^(x-n) on [-0.5, 0.5] (relative error < 7.6e-5, far below the 2^-9 of the bf16 that P is rounded
-// to) and add n to the exponent field; inputs below -125 (masked scores are -inf) give ~2^-125 instead
-// of 0, which vanishes in the row sum and in P (bf16 flushes it when multiplied into O).
-// The special-function unit delivers 16 exponentials per clock per SM; with both query tiles in their
-// softmax at once it is the busiest unit of the kernel, so a share of the pairs goes the other way.
-template <bool POLY> __device__ __forceinline__ f32x2 exp2_pair(f32x2 x) {
-  float lo, hi;
-  unpack2(x, lo, hi);
-  if constexpr (!POLY) {
-    return pack2(fast_exp2(lo), fast_exp2(hi));
-  } else {
-    const f32x2 magic = pack2(12582912.0f, 12582912.0f);
-    x = pack2(fmaxf(lo, -125.0f), fmaxf(hi, -125.0f));
-    const f32x2 shifted = add2(x, magic);               // low mantissa bits now hold n (two's complement)
-    const f32x2 frac = sub2(x, sub2(shifted, magic));
-    f32x2 poly = fma2(pack2(0.05520550534129143f, 0.05520550534129143f), frac, pack2(0.24261397123336792f, 0.24261397123336792f));
-    poly = fma2(poly, frac, pack2(0.6932547688484192f, 0.6932547688484192f));
-    poly = fma2(poly, frac, pack2(0.9999276995658875f, 0.9999276995658875f));
-    float poly_lo, poly_hi, shifted_lo, shifted_hi;
-    unpack2(poly, poly_lo, poly_hi);
-    unpack2(shifted, shifted_lo, shifted_hi);
-    return pack2(__uint_as_float(__float_as_uint(poly_lo) + (__float_as_uint(shifted_lo) << 23)),
-                 __uint_as_float(__float_as_uint(poly_hi) + (__float_as_uint(shifted_hi) << 23)));
-  }
-}
-
-// EMU of every 8 pairs take the polynomial path, spread evenly.
-template <int EMU> __device__ __forceinline__ constexpr bool pair_is_emulated(int pair_index) {
-  return (((pair_index & 7) * EMU) & 7) < EMU && EMU > 0;
-}
-
-template <int D, bool CAUSAL, int EMU>
+template <int D, bool CAUSAL>
 __global__ void __launch_bounds__(THREADS, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                 const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out, float* __restrict__ lse,
@@ -144,20 +79,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   const uint32_t base = (smem_addr(smem_raw) + 1023u) & ~1023u;
   uint8_t* aligned = smem_raw + (base - smem_addr(smem_raw));
   const uint32_t bar_base = base + L::BAR_OFF;
-  // barriers: q_full, k_full[2], v_full[2], k_empty[stage][tile], v_empty[stage][tile], s_ready[tile][buffer],
-  // p_ready[tile][buffer], o_done[tile][block parity].  The "empty" barriers are per issuer: a shared one
-  // with two arrivals could be completed by one issuer arriving twice while the other still reads the tile.
+  // barriers: q_full, k_full[2], v_full[2], kv_empty[2], s_ready[2], p_ready[2 tiles][2 halves], o_done[2]
   const uint32_t q_full = bar_base;
   auto k_full = [&](int s) { return bar_base + 8u * (1 + s); };
   auto v_full = [&](int s) { return bar_base + 8u * (3 + s); };
-  auto k_empty = [&](int s, int t) { return bar_base + 8u * (21 + 2 * s + t); };
-  auto v_empty = [&](int s, int t) { return bar_base + 8u * (25 + 2 * s + t); };
-  auto s_ready = [&](int t, int b) { return bar_base + 8u * (9 + 2 * t + b); };
-  auto p_ready = [&](int t, int b) { return bar_base + 8u * (13 + 2 * t + b); };
-  // P·V(j) completes o_done[t][j&1].  The softmax warps run up to two blocks ahead of the P·V they wait
-  // for, which one barrier's single phase bit could not tell apart; per block parity it is unambiguous.
-  auto o_done = [&](int t, int b) { return bar_base + 8u * (17 + 2 * t + b); };
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(aligned + L::BAR_OFF + 8 * 29);
+  auto kv_empty = [&](int s) { return bar_base + 8u * (5 + s); };
+  auto s_ready = [&](int t) { return bar_base + 8u * (7 + t); };
+  auto p_ready = [&](int t, int half) { return bar_base + 8u * (9 + 2 * t + half); };
+  auto o_done = [&](int t) { return bar_base + 8u * (13 + t); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(aligned + L::BAR_OFF + 8 * 15);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -166,33 +96,28 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   const int pair = pairs - 1 - (int)blockIdx.x;  // longest causal rows first
   const int head = blockIdx.y, batch = blockIdx.z;
   const int kv_head = head / (heads / kv_heads);
-  const int blocks_all = (seq + BLOCK_N - 1) / BLOCK_N;
-  // 64-key blocks each query tile needs (0 for a tile that starts past the end of the sequence)
+  const int kv_blocks_all = (seq + BLOCK_N - 1) / BLOCK_N;
+  // key/value blocks each query tile needs (0 for a tile that starts past the end of the sequence)
   int blocks_of[Q_TILES];
 #pragma unroll
   for (int t = 0; t < Q_TILES; ++t) {
     const int q_block = pair * Q_TILES + t;
-    blocks_of[t] = q_block >= q_blocks ? 0 : (CAUSAL ? min((q_block + 1) * (BLOCK_M / BLOCK_N), blocks_all) : blocks_all);
+    blocks_of[t] = q_block >= q_blocks ? 0 : (CAUSAL ? min(q_block + 1, kv_blocks_all) : kv_blocks_all);
   }
-  const int blocks = max(blocks_of[0], blocks_of[1]);
-  const int kv_tiles = (blocks + 1) / 2;
+  const int kv_blocks = max(blocks_of[0], blocks_of[1]);
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int s = 0; s < KV_STAGES; ++s) {
       mbar_init(k_full(s), 1);
       mbar_init(v_full(s), 1);
-      for (int t = 0; t < Q_TILES; ++t) {
-        mbar_init(k_empty(s, t), 1);
-        mbar_init(v_empty(s, t), 1);
-      }
+      mbar_init(kv_empty(s), 1);
     }
     for (int t = 0; t < Q_TILES; ++t) {
-      for (int b = 0; b < 2; ++b) {
-        mbar_init(s_ready(t, b), 1);
-        mbar_init(p_ready(t, b), 4);  // one arrival per softmax warp
-        mbar_init(o_done(t, b), 1);
-      }
+      mbar_init(s_ready(t), 1);
+      mbar_init(p_ready(t, 0), 4);  // one arrival per softmax warp
+      mbar_init(p_ready(t, 1), 4);
+      mbar_init(o_done(t), 1);
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -221,54 +146,30 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           tma_load_3d(base + L::Q_OFF + t * L::Q_BYTES + c * SUBTILE_BYTES, &map_q, q_full, head * D + c * 64,
                       (pair * Q_TILES + t) * BLOCK_M, batch);
       bool ok = true;
-      for (int tile = 0; ok && tile < kv_tiles; ++tile) {
-        const int stage = tile & 1;
-        const uint32_t free_parity = ((uint32_t)(tile >> 1) & 1u) ^ 1u;  // a fresh barrier passes at once
+      for (int j = 0; ok && j < kv_blocks; ++j) {
+        const int stage = j & 1;
+        const uint32_t use_parity = (uint32_t)(j >> 1) & 1u;
+        if (!(ok = mbar_wait(kv_empty(stage), use_parity ^ 1u, abort_flag, status_word, kWaitKvEmpty))) break;
         const uint32_t k_dst = base + L::KV_OFF + stage * (L::K_BYTES + L::V_BYTES);
         const uint32_t v_dst = k_dst + L::K_BYTES;
-        if (!(ok = mbar_wait(k_empty(stage, 0), free_parity, abort_flag, status_word, kWaitKEmpty))) break;
-        if (!(ok = mbar_wait(k_empty(stage, 1), free_parity, abort_flag, status_word, kWaitKEmpty))) break;
         mbar_arrive_expect_tx(k_full(stage), L::K_BYTES);
 #pragma unroll
         for (int c = 0; c < L::DCH; ++c)
-          tma_load_3d(k_dst + c * SUBTILE_BYTES, &map_k, k_full(stage), kv_head * D + c * 64, tile * KV_TILE, batch);
-        if (!(ok = mbar_wait(v_empty(stage, 0), free_parity, abort_flag, status_word, kWaitVEmpty))) break;
-        if (!(ok = mbar_wait(v_empty(stage, 1), free_parity, abort_flag, status_word, kWaitVEmpty))) break;
+          tma_load_3d(k_dst + c * SUBTILE_BYTES, &map_k, k_full(stage), kv_head * D + c * 64, j * BLOCK_N, batch);
         mbar_arrive_expect_tx(v_full(stage), L::V_BYTES);
 #pragma unroll
         for (int c = 0; c < L::DCH; ++c)
-          tma_load_3d(v_dst + c * SUBTILE_BYTES, &map_v, v_full(stage), kv_head * D + c * 64, tile * KV_TILE, batch);
+          tma_load_3d(v_dst + c * SUBTILE_BYTES, &map_v, v_full(stage), kv_head * D + c * 64, j * BLOCK_N, batch);
       }
     }
-  } else if (warp <= Q_TILES) {
-    // ---------------- MMA issuers: warp 1 drives query tile 0, warp 2 drives query tile 1 ----------------
-    // tcgen05.mma blocks its issuing thread while the pipe is busy (the queue is only a few instructions
-    // deep), so a single issuer that also has to wait for P of the other tile leaves the pipe idle.  With
-    // one issuer per tile the two instruction streams interleave on the pipe by themselves.
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
     if (elect_one()) {
-      const int t = warp - 1;
-      const int my_blocks = t == 0 ? blocks_of[0] : blocks_of[1];
       constexpr uint32_t idesc_qk = umma_idesc_bf16_f32(BLOCK_M, BLOCK_N);
       constexpr uint32_t idesc_pv = umma_idesc_bf16_f32(BLOCK_M, D, false, true);  // V is MN-major
-      bool ok = true;
-      int k_tiles_seen = 0, v_tiles_seen = 0;  // shared-memory tiles whose arrival has been observed
-      auto need_k = [&](int tile) {
-        while (ok && k_tiles_seen <= tile) {
-          ok = mbar_wait(k_full(k_tiles_seen & 1), (uint32_t)(k_tiles_seen >> 1) & 1u, abort_flag, status_word, kWaitK);
-          tcgen05_fence_after();
-          ++k_tiles_seen;
-        }
-      };
-      auto need_v = [&](int tile) {
-        while (ok && v_tiles_seen <= tile) {
-          ok = mbar_wait(v_full(v_tiles_seen & 1), (uint32_t)(v_tiles_seen >> 1) & 1u, abort_flag, status_word, kWaitV);
-          tcgen05_fence_after();
-          ++v_tiles_seen;
-        }
-      };
-      auto issue_qk = [&](int j) {  // S_t[j&1] = Q_t · K_j^T
-        const uint32_t k_src = base + L::KV_OFF + ((j >> 1) & 1) * (L::K_BYTES + L::V_BYTES) + (j & 1) * BLOCK_ROW_BYTES;
-        const uint32_t acc = tmem_base + (uint32_t)((2 * t + (j & 1)) * BLOCK_N);
+      auto issue_qk = [&](int t, int j) {  // S_t = Q_t · K_j^T
+        const uint32_t k_src = base + L::KV_OFF + (j & 1) * (L::K_BYTES + L::V_BYTES);
+        const uint32_t acc = tmem_base + (uint32_t)(t * BLOCK_N);
 #pragma unroll
         for (int c = 0; c < L::DCH; ++c) {
           const uint64_t desc_q = umma_desc_k_major_sw128(base + L::Q_OFF + t * L::Q_BYTES + c * SUBTILE_BYTES);
@@ -278,57 +179,53 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
             umma_bf16_ss(acc, umma_desc_advance_k(desc_q, kk * 32), umma_desc_advance_k(desc_k, kk * 32), idesc_qk,
                          (c | kk) != 0 ? 1u : 0u);
         }
-        umma_commit(s_ready(t, j & 1));
+        umma_commit(s_ready(t));
       };
-      auto issue_pv = [&](int j) {  // O_t (+)= P_t[j&1] · V_j; P is packed bf16 in the first 32 columns of its S buffer
-        const uint32_t v_src = base + L::KV_OFF + ((j >> 1) & 1) * (L::K_BYTES + L::V_BYTES) + L::K_BYTES;
+      // O_t (+)= P_t · V_j over keys [64*half, 64*half+64); P_t is packed bf16 in the first 64 columns of S_t
+      auto issue_pv = [&](int t, int j, int half) {
+        const uint32_t v_src = base + L::KV_OFF + (j & 1) * (L::K_BYTES + L::V_BYTES) + L::K_BYTES;
         const uint64_t desc_v = umma_desc_mn_major_sw128(v_src, SUBTILE_BYTES);
-        const uint32_t p_addr = tmem_base + (uint32_t)((2 * t + (j & 1)) * BLOCK_N);
+        const uint32_t p_addr = tmem_base + (uint32_t)(t * BLOCK_N);
         const uint32_t o_addr = tmem_base + 256u + (uint32_t)(t * 128);
 #pragma unroll
-        for (int kk = 0; kk < BLOCK_N / 16; ++kk)
-          umma_bf16_ts(o_addr, p_addr + (uint32_t)(kk * 8), umma_desc_advance_k(desc_v, ((j & 1) * 4 + kk) * 2048), idesc_pv,
+        for (int kk = half * 4; kk < half * 4 + 4; ++kk)
+          umma_bf16_ts(o_addr, p_addr + (uint32_t)(kk * 8), umma_desc_advance_k(desc_v, kk * 2048), idesc_pv,
                        (j | kk) != 0 ? 1u : 0u);
-        umma_commit(o_done(t, j & 1));
+        if (half == 1) umma_commit(o_done(t));
       };
-      // Both issuers release every K / V tile the producer loads (`blocks` counts the longer tile), whether
-      // or not their own tile still has work in it: a commit with nothing pending arrives at once.  An
-      // issuer without work still observes the tile's arrival before it releases it; otherwise it could
-      // run two releases ahead of the producer, whose parity wait cannot tell phases two apart.
-      auto release_k_after = [&](int j) {  // block j was the last one of its K tile to be multiplied
-        if ((j & 1) == 1 || j == blocks - 1) {
-          need_k(j >> 1);
-          if (ok) umma_commit(k_empty((j >> 1) & 1, t));
-        }
-      };
-      ok = mbar_wait(q_full, 0, abort_flag, status_word, kWaitQ);
-      for (int j = 0; ok && j < 2 && j < blocks; ++j) {
-        if (j < my_blocks) {
-          need_k(0);
-          if (!ok) break;
-          issue_qk(j);
-        }
-        release_k_after(j);
+      bool ok = mbar_wait(q_full, 0, abort_flag, status_word, kWaitQ);
+      if (ok && kv_blocks > 0) ok = mbar_wait(k_full(0), 0, abort_flag, status_word, kWaitK);
+      if (ok) {
+        tcgen05_fence_after();
+#pragma unroll
+        for (int t = 0; t < Q_TILES; ++t)
+          if (0 < blocks_of[t]) issue_qk(t, 0);
       }
-      for (int j = 0; ok && j < blocks; ++j) {
-        const int ahead = j + 2;
-        if (j < my_blocks) {
-          need_v(j >> 1);
-          if (!ok) break;
-          if (!(ok = mbar_wait(p_ready(t, j & 1), (uint32_t)(j >> 1) & 1u, abort_flag, status_word, kWaitPReady))) break;
-          tcgen05_fence_after();
-          issue_pv(j);
+      for (int j = 0; ok && j < kv_blocks; ++j) {
+        const int stage = j & 1, next = j + 1;
+        if (!(ok = mbar_wait(v_full(stage), (uint32_t)(j >> 1) & 1u, abort_flag, status_word, kWaitV))) break;
+        bool next_k_ready = false;
+#pragma unroll
+        for (int t = 0; t < Q_TILES; ++t) {
+          if (j < blocks_of[t]) {
+            // the first 64 keys of P arrive while the softmax warps still work on the last 64
+            if (!(ok = mbar_wait(p_ready(t, 0), (uint32_t)j & 1u, abort_flag, status_word, kWaitPReady))) break;
+            tcgen05_fence_after();
+            issue_pv(t, j, 0);
+            if (!(ok = mbar_wait(p_ready(t, 1), (uint32_t)j & 1u, abort_flag, status_word, kWaitPReady))) break;
+            tcgen05_fence_after();
+            issue_pv(t, j, 1);
+          }
+          if (next < blocks_of[t]) {
+            if (!next_k_ready) {
+              if (!(ok = mbar_wait(k_full(next & 1), (uint32_t)(next >> 1) & 1u, abort_flag, status_word, kWaitK))) break;
+              tcgen05_fence_after();
+              next_k_ready = true;
+            }
+            issue_qk(t, next);  // overwrites S_t/P_t: ordered after PV_t(j) on the tensor pipe
+          }
         }
-        if (ahead < my_blocks) {
-          need_k(ahead >> 1);
-          if (!ok) break;
-          issue_qk(ahead);  // overwrites S_t[j&1] / P_t(j): ordered after PV_t(j), issued by this same thread
-        }
-        if (ahead < blocks) release_k_after(ahead);
-        if ((j & 1) == 1 || j == blocks - 1) {  // this tile's P·V of the V tile are issued
-          need_v(j >> 1);
-          if (ok) umma_commit(v_empty((j >> 1) & 1, t));
-        }
+        if (ok) umma_commit(kv_empty(stage));
       }
     }
   }
@@ -342,14 +239,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     const int query = q0 + row;
     const int my_blocks = tile == 0 ? blocks_of[0] : blocks_of[1];
     const uint32_t lane_base = (uint32_t)(quadrant * 32) << 16;
-    const uint32_t s_base = tmem_base + lane_base + (uint32_t)(2 * tile * BLOCK_N);
+    const uint32_t s_addr = tmem_base + lane_base + (uint32_t)(tile * BLOCK_N);
     const uint32_t o_addr = tmem_base + lane_base + 256u + (uint32_t)(tile * 128);
     float used_max = -INFINITY;             // running maximum (scaled, log2 units) the exponentials refer to
     float row_sum = 0.0f;
     bool ok = true;
     for (int j = 0; j < my_blocks; ++j) {
-      const uint32_t s_addr = s_base + (uint32_t)((j & 1) * BLOCK_N);
-      ok = mbar_wait(s_ready(tile, j & 1), (uint32_t)(j >> 1) & 1u, abort_flag, status_word, kWaitSReady);
+      ok = mbar_wait(s_ready(tile), (uint32_t)j & 1u, abort_flag, status_word, kWaitSReady);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tcgen05_fence_after();
@@ -366,15 +262,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         for (int i = 0; i < BLOCK_N; ++i)
           if (i > key_limit) s[i] = 0xff800000u;  // -inf
       }
-      // eight independent chains instead of one long dependency chain
-      float chain[8];
+      // four independent chains instead of one 128-long dependency chain
+      float max0 = -INFINITY, max1 = -INFINITY, max2 = -INFINITY, max3 = -INFINITY;
 #pragma unroll
-      for (int c = 0; c < 8; ++c) chain[c] = fmaxf(__uint_as_float(s[2 * c]), __uint_as_float(s[2 * c + 1]));
-#pragma unroll
-      for (int i = 16; i < BLOCK_N; i += 16)
-#pragma unroll
-        for (int c = 0; c < 8; ++c) chain[c] = fmax3(chain[c], __uint_as_float(s[i + 2 * c]), __uint_as_float(s[i + 2 * c + 1]));
-      const float block_max = fmaxf(fmax3(chain[0], chain[1], chain[2]), fmax3(chain[3], chain[4], fmax3(chain[5], chain[6], chain[7])));
+      for (int i = 0; i < BLOCK_N; i += 8) {
+        max0 = fmax3(max0, __uint_as_float(s[i]), __uint_as_float(s[i + 1]));
+        max1 = fmax3(max1, __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
+        max2 = fmax3(max2, __uint_as_float(s[i + 4]), __uint_as_float(s[i + 5]));
+        max3 = fmax3(max3, __uint_as_float(s[i + 6]), __uint_as_float(s[i + 7]));
+      }
+      const float block_max = fmaxf(fmaxf(max0, max1), fmaxf(max2, max3));
       const float candidate = fmaxf(used_max, block_max * scale_log2e);  // scale > 0 commutes with max
       // O stays in TMEM; it is rescaled only when some row of this warp outgrows the threshold
       const bool grow = candidate > used_max + RESCALE_THRESHOLD;        // also true on the first finite block
@@ -384,7 +281,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         used_max = candidate;
         if (j > 0) {
           // P·V of the previous block must have landed in O before it is rescaled
-          ok = mbar_wait(o_done(tile, (j - 1) & 1), (uint32_t)((j - 1) >> 1) & 1u, abort_flag, status_word, kWaitODone);
+          ok = mbar_wait(o_done(tile), (uint32_t)(j - 1) & 1u, abort_flag, status_word, kWaitODone);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           tcgen05_fence_after();
@@ -400,33 +297,35 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         }
       }
       const float shift = used_max == -INFINITY ? 0.0f : -used_max;  // fully masked so far: 2^(-inf) = 0
-      const f32x2 scale2 = pack2(scale_log2e, scale_log2e), shift2 = pack2(shift, shift);
-      f32x2 sums[4] = {0ull, 0ull, 0ull, 0ull};  // four chains of (even key, odd key) partial sums
-      // packed in place: word i of `s` is free once scores 2i and 2i+1 have been consumed
+      float sum0 = 0.0f, sum1 = 0.0f, sum2 = 0.0f, sum3 = 0.0f;
+      // Two halves of 64 keys; each is published as soon as it is in TMEM so P·V starts on the first
+      // half while the second is still being exponentiated.  Packed in place: word i/2 of `s` is free
+      // once scores i and i+1 have been consumed.  P overwrites the first 64 columns of this tile's S
+      // (each thread only touches its own lane).
 #pragma unroll
-      for (int i = 0; i < BLOCK_N / 2; ++i) {
-        const f32x2 x = fma2(pack2(__uint_as_float(s[2 * i]), __uint_as_float(s[2 * i + 1])), scale2, shift2);
-        const f32x2 p = pair_is_emulated<EMU>(i) ? exp2_pair<true>(x) : exp2_pair<false>(x);
-        sums[i & 3] = add2(sums[i & 3], p);
-        float p_even, p_odd;
-        unpack2(p, p_even, p_odd);
-        const __nv_bfloat162 packed = __floats2bfloat162_rn(p_even, p_odd);  // low half = even key
-        s[i] = *reinterpret_cast<const uint32_t*>(&packed);
+      for (int half = 0; half < 2; ++half) {
+#pragma unroll
+        for (int i = half * 64; i < half * 64 + 64; i += 4) {
+          const float p0 = fast_exp2(fmaf(__uint_as_float(s[i]), scale_log2e, shift));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(s[i + 1]), scale_log2e, shift));
+          const float p2 = fast_exp2(fmaf(__uint_as_float(s[i + 2]), scale_log2e, shift));
+          const float p3 = fast_exp2(fmaf(__uint_as_float(s[i + 3]), scale_log2e, shift));
+          sum0 += p0; sum1 += p1; sum2 += p2; sum3 += p3;
+          const __nv_bfloat162 lo = __floats2bfloat162_rn(p0, p1);  // low half = even key
+          const __nv_bfloat162 hi = __floats2bfloat162_rn(p2, p3);
+          s[i >> 1] = *reinterpret_cast<const uint32_t*>(&lo);
+          s[(i >> 1) + 1] = *reinterpret_cast<const uint32_t*>(&hi);
+        }
+        tmem_st_32x32b_x32(s_addr + (uint32_t)(half * 32), *reinterpret_cast<uint32_t(*)[32]>(&s[half * 32]));
+        tmem_st_wait();
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(p_ready(tile, half));
       }
-      {
-        float even, odd;
-        unpack2(add2(add2(sums[0], sums[1]), add2(sums[2], sums[3])), even, odd);
-        row_sum += even + odd;
-      }
-      // P overwrites the first 32 columns of this score buffer (each thread only touches its own lane)
-      tmem_st_32x32b_x32(s_addr, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
-      tmem_st_wait();
-      tcgen05_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(p_ready(tile, j & 1));
+      row_sum += (sum0 + sum1) + (sum2 + sum3);
     }
     if (ok && my_blocks > 0) {
-      ok = mbar_wait(o_done(tile, (my_blocks - 1) & 1), (uint32_t)((my_blocks - 1) >> 1) & 1u, abort_flag, status_word, kWaitODone);
+      ok = mbar_wait(o_done(tile), (uint32_t)(my_blocks - 1) & 1u, abort_flag, status_word, kWaitODone);
       ok = __all_sync(0xffffffffu, ok);
     }
     if (ok && my_blocks > 0) {
@@ -529,25 +428,25 @@ __global__ void attn_fwd_generic_kernel(const __nv_bfloat16* __restrict__ q, con
 
 constexpr int kMaxDevices = 64;
 
-template <int D, bool CAUSAL, int EMU>
-int launch_tensor_emu(const void* q, const void* k, const void* v, void* out, float* lse, int batch, int seq, int heads,
+template <int D, bool CAUSAL>
+int launch_tensor(const void* q, const void* k, const void* v, void* out, float* lse, int batch, int seq, int heads,
                   int kv_heads, cudaStream_t stream) {
   alignas(64) CUtensorMap map_q, map_k, map_v;
   if (int status = encode_tensormap_3d(&map_q, BB200_BF16, q, (uint64_t)heads * D, (uint64_t)seq, (uint64_t)batch,
                                        (uint64_t)heads * D * 2, (uint64_t)seq * heads * D * 2, 64, BLOCK_M, 1, 3))
     return status;
   if (int status = encode_tensormap_3d(&map_k, BB200_BF16, k, (uint64_t)kv_heads * D, (uint64_t)seq, (uint64_t)batch,
-                                       (uint64_t)kv_heads * D * 2, (uint64_t)seq * kv_heads * D * 2, 64, KV_TILE, 1, 3))
+                                       (uint64_t)kv_heads * D * 2, (uint64_t)seq * kv_heads * D * 2, 64, BLOCK_N, 1, 3))
     return status;
   if (int status = encode_tensormap_3d(&map_v, BB200_BF16, v, (uint64_t)kv_heads * D, (uint64_t)seq, (uint64_t)batch,
-                                       (uint64_t)kv_heads * D * 2, (uint64_t)seq * kv_heads * D * 2, 64, KV_TILE, 1, 3))
+                                       (uint64_t)kv_heads * D * 2, (uint64_t)seq * kv_heads * D * 2, 64, BLOCK_N, 1, 3))
     return status;
   int device = 0;
   if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices)
     return fail(BB200_E_NO_DRIVER, "attention: no CUDA device is current");
   static bool configured[kMaxDevices] = {};
   if (!configured[device]) {
-    if (int status = check_runtime(cudaFuncSetAttribute(attn_fwd_kernel<D, CAUSAL, EMU>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (int status = check_runtime(cudaFuncSetAttribute(attn_fwd_kernel<D, CAUSAL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                         Smem<D>::TOTAL),
                                    "cudaFuncSetAttribute(attention smem)"))
       return status;
@@ -556,34 +455,9 @@ int launch_tensor_emu(const void* q, const void* k, const void* v, void* out, fl
   const float scale_log2e = (1.0f / sqrtf((float)D)) * 1.4426950408889634f;
   const int q_blocks = (seq + BLOCK_M - 1) / BLOCK_M;
   dim3 grid((q_blocks + Q_TILES - 1) / Q_TILES, heads, batch);
-  attn_fwd_kernel<D, CAUSAL, EMU><<<grid, THREADS, Smem<D>::TOTAL, stream>>>(
+  attn_fwd_kernel<D, CAUSAL><<<grid, THREADS, Smem<D>::TOTAL, stream>>>(
       map_q, map_k, map_v, static_cast<__nv_bfloat16*>(out), lse, seq, heads, kv_heads, scale_log2e, device_status_word());
   return check_launch("attention kernel launch");
-}
-
-// How many of every 8 pairs of exponentials are evaluated on the FMA pipe.  BB200_ATTN_EMU (0, 2, 3 or 4)
-// overrides the default for tuning runs.
-constexpr int DEFAULT_EMU = 2;
-
-int emulated_exponentials() {
-  static int value = -1;
-  if (value < 0) {
-    const char* text = getenv("BB200_ATTN_EMU");
-    const int parsed = text ? atoi(text) : DEFAULT_EMU;
-    value = (parsed == 0 || parsed == 2 || parsed == 3 || parsed == 4) ? parsed : DEFAULT_EMU;  // the instantiated set
-  }
-  return value;
-}
-
-template <int D, bool CAUSAL>
-int launch_tensor(const void* q, const void* k, const void* v, void* out, float* lse, int batch, int seq, int heads,
-                  int kv_heads, cudaStream_t stream) {
-  switch (emulated_exponentials()) {
-    case 2: return launch_tensor_emu<D, CAUSAL, 2>(q, k, v, out, lse, batch, seq, heads, kv_heads, stream);
-    case 3: return launch_tensor_emu<D, CAUSAL, 3>(q, k, v, out, lse, batch, seq, heads, kv_heads, stream);
-    case 4: return launch_tensor_emu<D, CAUSAL, 4>(q, k, v, out, lse, batch, seq, heads, kv_heads, stream);
-    default: return launch_tensor_emu<D, CAUSAL, 0>(q, k, v, out, lse, batch, seq, heads, kv_heads, stream);
-  }
 }
 
 }  // namespace
