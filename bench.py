@@ -49,8 +49,8 @@ E2E_CHUNKS = 8  # chunks of the host pipeline (copy-in / kernel / copy-out overl
 MEASURED_DRAM_TRAFFIC = {
     ("fused_mul_add", 2**28): 1.07e9 + 497.2e6,
     ("rmsnorm", 65536): 1.07e9 + 1.02e9,
-    ("gemm", 8192): 1.39e9 + 127.5e6,
-    ("attention", 16): 1.61e9 + 570.5e6,
+    ("gemm", 8192): 1.43e9 + 126.8e6,
+    ("attention", 16): 1.61e9 + 523.8e6,
 }
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
