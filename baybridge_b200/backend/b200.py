@@ -299,7 +299,13 @@ class B200Backend:
             scratch_bytes = chunks * compute_bytes if chunks > 1 else 0
         elif plan.form == "cols":
             slabs = max(1, min(outer, 256, (148 * 1024) // max(inner, 1)))
-            scratch_bytes = slabs * inner * compute_bytes if slabs > 1 else 0
+            # vectorised form (16-byte column groups): enough row slabs for ~8 CTAs per SM, at least 8 rows each
+            partial_vec = 16 // compute_bytes
+            vector_shape = inner % vec == 0 and inner % partial_vec == 0
+            vec_threads = reduction_lowering.COLS_VEC_THREADS
+            vec_blocks = -(-(inner // max(vec, 1)) // vec_threads) if vector_shape else 1
+            vec_slabs = max(1, min(-(-(148 * 8) // vec_blocks), outer // 8, 1024))
+            scratch_bytes = max(slabs, vec_slabs if vector_shape else 0) * inner * compute_bytes if max(slabs, vec_slabs) > 1 else 0
         else:
             scratch_bytes = 0
 
@@ -348,6 +354,16 @@ class B200Backend:
                            stream_handle)
                     launch("bb200_reduce_partials_rows", native.U3(1, 1, 1), block, [scratch] + dst + [ctypes.c_size_t(chunks), init],
                            stream_handle)
+            elif vector_shape and aligned.value:
+                vec_block = native.U3(vec_threads, 1, 1)
+                if vec_slabs == 1:
+                    launch("bb200_reduce_cols_vec", native.U3(vec_blocks, 1, 1), vec_block,
+                           inputs + dst + [ctypes.c_size_t(outer), ctypes.c_size_t(inner), init], stream_handle)
+                else:
+                    launch("bb200_reduce_cols_vec_partial", native.U3(vec_blocks, vec_slabs, 1), vec_block,
+                           inputs + [scratch, ctypes.c_size_t(outer), ctypes.c_size_t(inner)], stream_handle)
+                    launch("bb200_reduce_partials_cols_vec", native.U3(-(-(inner // partial_vec) // vec_threads), 1, 1), vec_block,
+                           [scratch] + dst + [ctypes.c_size_t(vec_slabs), ctypes.c_size_t(inner), init], stream_handle)
             else:
                 columns = native.U3(-(-inner // threads), slabs, 1)
                 if slabs == 1:

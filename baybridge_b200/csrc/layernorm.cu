@@ -41,20 +41,30 @@ layernorm_rows(const T* __restrict__ x, const T* __restrict__ residual, const T*
   const int nvec = hidden / VEC;
   float mixed[VPT][VEC];
   float sum = 0.0f;
+  {
+    // every load of the row is issued before the first store: the stores cannot move above them
+    Pack<T, VEC> a[VPT], b[VPT];
 #pragma unroll
-  for (int j = 0; j < VPT; ++j) {
-    const int v = threadIdx.x + j * THREADS;
-    if (v < nvec) {
-      const Pack<T, VEC> a = load_stream<T, VEC>(x + offset + (size_t)v * VEC);
-      const Pack<T, VEC> b = load_stream<T, VEC>(residual + offset + (size_t)v * VEC);
-      Pack<T, VEC> r;
-#pragma unroll
-      for (int e = 0; e < VEC; ++e) {
-        mixed[j][e] = Conv<float, T>::widen(a.v[e]) + Conv<float, T>::widen(b.v[e]);
-        sum += mixed[j][e];
-        r.v[e] = Conv<float, T>::narrow(mixed[j][e]);
+    for (int j = 0; j < VPT; ++j) {
+      const int v = threadIdx.x + j * THREADS;
+      if (v < nvec) {
+        a[j] = load_stream<T, VEC>(x + offset + (size_t)v * VEC);
+        b[j] = load_stream<T, VEC>(residual + offset + (size_t)v * VEC);
       }
-      store_stream<T, VEC>(out_resid + offset + (size_t)v * VEC, r);
+    }
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+      const int v = threadIdx.x + j * THREADS;
+      if (v < nvec) {
+        Pack<T, VEC> r;
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+          mixed[j][e] = Conv<float, T>::widen(a[j].v[e]) + Conv<float, T>::widen(b[j].v[e]);
+          sum += mixed[j][e];
+          r.v[e] = Conv<float, T>::narrow(mixed[j][e]);
+        }
+        store_stream<T, VEC>(out_resid + offset + (size_t)v * VEC, r);
+      }
     }
   }
   const float mean = block_sum<THREADS>(sum, scratch) / (float)hidden;

@@ -37,7 +37,8 @@ class ShardSpec:
 
 def shard_spec(plan: Any, ir: Any) -> ShardSpec:
     """Sharding of a matched plan (see ``backend.matcher``): elementwise → flat chunks of axis 0, RMSNorm →
-    rows, GEMM → M (A and C by rows, B replicated), attention → batch."""
+    rows, GEMM → M (A and C by rows, B replicated), attention → batch, LayerNorm → rows, reductions that keep
+    the leading axis → rows (others do not shard)."""
     kind = plan.kind
     if kind == "elementwise":
         tensors = tuple(dict.fromkeys(tuple(plan.inputs) + tuple(store[0] for store in plan.stores)))
@@ -59,6 +60,20 @@ def shard_spec(plan: Any, ir: Any) -> ShardSpec:
     if kind == "attention":
         return ShardSpec(kind, plan.batch, tuple((p, 0) for p in (plan.q, plan.k, plan.v, plan.out, plan.lse)), (),
                          (plan.out, plan.lse))
+    if kind == "layernorm":
+        shape = ir.arguments[plan.x].spec.shape
+        if len(shape) < 2:
+            raise ValueError("a rank-1 layernorm has a single row and does not shard")
+        per_row = (plan.x, plan.residual, plan.out, plan.out_resid)
+        full = tuple(p for p, is_full in ((plan.weight, plan.weight_is_full), (plan.bias, plan.bias_is_full)) if is_full)
+        shared = tuple(p for p, is_full in ((plan.weight, plan.weight_is_full), (plan.bias, plan.bias_is_full)) if not is_full)
+        return ShardSpec(kind, shape[0], tuple((p, 0) for p in per_row + full), shared, (plan.out, plan.out_resid))
+    if kind == "reduction":
+        # only a fold that keeps the leading axis splits without an exchange step (each rank folds its own rows);
+        # folds over the leading axis run whole on one GPU
+        if plan.form == "rows" and len(plan.source_shape) >= 2 and ir.arguments[plan.dst].spec.shape[:1] == plan.source_shape[:1]:
+            return ShardSpec(kind, plan.source_shape[0], tuple((p, 0) for p in tuple(plan.inputs) + (plan.dst,)), (), (plan.dst,))
+        return ShardSpec(kind, 1, (), tuple(plan.inputs) + (plan.dst,), (plan.dst,))
     raise ValueError(f"unknown plan kind '{kind}'")
 
 

@@ -414,10 +414,140 @@ class Attention(Workload):
         return (lambda: oracle.attention(q, k, v, causal=True)), flops, f"B{bsz} H{heads} S{seq} D{self.dim}, numpy f64 port"
 
 
-WORKLOADS = {cls.name: cls for cls in (FusedMulAdd, RmsNorm, Gemm, Attention)}
+class LayerNorm(Workload):
+    """LayerNorm with fused residual add: reads x, residual, weight, bias; writes out and x + residual."""
+    name, unit, bound = "layernorm", "GB/s", "hbm"
+    rows, hidden = 32768, 8192
+
+    def shrink(self):
+        self.rows = 4096  # 268 MB working set
+
+    def size_key(self):
+        return self.rows
+
+    def work_per_step(self) -> float:
+        return 4.0 * self.rows * self.hidden * 2 + 2 * self.hidden * 2
+
+    def setup(self, torch, cute, zoo, rank, cache_dir):
+        generator = torch.Generator(device="cuda").manual_seed(1006 + rank)
+        make = lambda: torch.randn((self.rows, self.hidden), device="cuda", dtype=torch.float32, generator=generator).to(torch.bfloat16)  # noqa: E731
+        self.x, self.residual = make(), make()
+        self.w = (1 + 0.1 * torch.randn((self.hidden,), device="cuda", dtype=torch.float32, generator=generator)).to(torch.bfloat16)
+        self.b = (0.1 * torch.randn((self.hidden,), device="cuda", dtype=torch.float32, generator=generator)).to(torch.bfloat16)
+        self.out, self.out_resid = torch.empty_like(self.x), torch.empty_like(self.x)
+        from baybridge_b200 import B200Backend
+
+        tensors = (self.x, self.residual, self.out, self.out_resid, self.w, self.b)
+        self.artifact = cute.compile(zoo.layernorm_kernel, *tensors, backend=B200Backend(synchronize=False), cache_dir=cache_dir)
+        self.args = tuple(cute.from_dlpack(t) for t in tensors)
+        self.stream = torch.cuda.current_stream().cuda_stream
+        self.host = [t.cpu().pin_memory() for t in tensors]
+        self.h2d_bytes = 2 * self.rows * self.hidden * 2
+        self.d2h_bytes = 2 * self.rows * self.hidden * 2
+
+    def step(self):
+        self.artifact(*self.args, stream=self.stream)
+
+    def output(self):
+        return self.out
+
+    def e2e_setup(self, cute, zoo, cache_dir):
+        from baybridge_b200.host_pipeline import HostPipeline
+
+        self.pipeline = HostPipeline(lambda rows: zoo.layernorm_kernel, self.host, chunks=E2E_CHUNKS, cache_dir=cache_dir)
+
+    def config(self):
+        return {"workload": f"layernorm with residual add, bf16 [{self.rows}, {self.hidden}] per GPU, weight/bias [{self.hidden}], eps 1e-5",
+                "l2": "working set 2.1 GB > 126 MB L2, no flush"}
+
+    def cpu_sample(self):
+        from oracle import cpu_runtime as oracle
+
+        rng = np.random.default_rng(1006)
+        rows = 256
+        x = oracle.bf16_round(rng.standard_normal((rows, self.hidden), dtype=np.float32)).astype(np.float64)
+        r = oracle.bf16_round(rng.standard_normal((rows, self.hidden), dtype=np.float32)).astype(np.float64)
+        w = oracle.bf16_round((1 + 0.1 * rng.standard_normal(self.hidden)).astype(np.float32)).astype(np.float64)
+        b = oracle.bf16_round((0.1 * rng.standard_normal(self.hidden)).astype(np.float32)).astype(np.float64)
+        return (lambda: oracle.layernorm(x, r, w, b, 1e-5)), 4.0 * rows * self.hidden * 2, f"{rows} of {self.rows} rows, numpy f64 port"
+
+
+class _Reduction(Workload):
+    """A traced `Tensor.reduce` over one axis of a bf16 matrix: every element is read once."""
+    unit, bound = "GB/s", "hbm"
+    rows, cols = 65536, 8192
+    kernel_name = ""
+    kept_axis = 0
+
+    def shrink(self):
+        self.rows = 8192
+
+    def size_key(self):
+        return self.rows
+
+    def work_per_step(self) -> float:
+        kept = self.rows if self.kept_axis == 0 else self.cols
+        return self.rows * self.cols * 2.0 + kept * 2.0
+
+    def setup(self, torch, cute, zoo, rank, cache_dir):
+        generator = torch.Generator(device="cuda").manual_seed(1007 + rank)
+        self.src = torch.rand((self.rows, self.cols), device="cuda", dtype=torch.float32, generator=generator).mul_(2).sub_(1).to(torch.bfloat16)
+        kept = self.rows if self.kept_axis == 0 else self.cols
+        self.dst = torch.empty((kept,), device="cuda", dtype=torch.bfloat16)
+        from baybridge_b200 import B200Backend
+
+        self.artifact = cute.compile(getattr(zoo, self.kernel_name), self.src, self.dst, backend=B200Backend(synchronize=False),
+                                     cache_dir=cache_dir)
+        self.args = tuple(cute.from_dlpack(t) for t in (self.src, self.dst))
+        self.stream = torch.cuda.current_stream().cuda_stream
+        self.host = [self.src.cpu().pin_memory(), self.dst.cpu().pin_memory()]
+        self.h2d_bytes = self.rows * self.cols * 2
+        self.d2h_bytes = kept * 2
+
+    def step(self):
+        self.artifact(*self.args, stream=self.stream)
+
+    def output(self):
+        return self.dst
+
+    def e2e_setup(self, cute, zoo, cache_dir):
+        from baybridge_b200.host_pipeline import HostPipeline
+
+        self.pipeline = HostPipeline(lambda rows: getattr(zoo, self.kernel_name), self.host, chunks=E2E_CHUNKS if self.kept_axis == 0 else 1,
+                                     cache_dir=cache_dir)
+
+    def cpu_sample(self):
+        from oracle import cpu_runtime as oracle
+
+        rng = np.random.default_rng(1007)
+        rows = 2048
+        src = oracle.bf16_round(rng.uniform(-1, 1, (rows, self.cols)).astype(np.float32)).astype(np.float64)
+        run = (lambda: (src * src).sum(axis=1)) if self.kept_axis == 0 else (lambda: np.maximum(src.max(axis=0), -1000.0))
+        return run, rows * self.cols * 2.0, f"{rows} of {self.rows} rows, numpy f64 restatement of the traced fold"
+
+
+class RowReduce(_Reduction):
+    name, kernel_name, kept_axis = "reduce_rows", "row_sum_of_squares", 0
+
+    def config(self):
+        return {"workload": f"row reduction dst[r] = sum_c src[r,c]^2, bf16 [{self.rows}, {self.cols}] per GPU (traced Tensor.reduce)",
+                "l2": "working set 1.07 GB > 126 MB L2, no flush"}
+
+
+class ColumnReduce(_Reduction):
+    name, kernel_name, kept_axis = "reduce_cols", "column_max", 1
+
+    def config(self):
+        return {"workload": f"column reduction dst[c] = max_r src[r,c], bf16 [{self.rows}, {self.cols}] per GPU (traced Tensor.reduce)",
+                "l2": "working set 1.07 GB > 126 MB L2, no flush"}
+
+
+WORKLOADS = {cls.name: cls for cls in (FusedMulAdd, RmsNorm, Gemm, Attention, LayerNorm, RowReduce, ColumnReduce)}
 METRIC = {
     "fused_mul_add": "elementwise HBM GB/s (fused c=a*b+a, bf16)", "rmsnorm": "RMSNorm HBM GB/s (bf16)",
     "gemm": "BF16 GEMM TFLOP/s", "attention": "causal attention forward TFLOP/s (bf16)",
+    "layernorm": "LayerNorm + residual HBM GB/s (bf16)", "reduce_rows": "row reduction HBM GB/s (bf16)",
+    "reduce_cols": "column reduction HBM GB/s (bf16)",
 }
 
 

@@ -45,6 +45,13 @@ def test_shard_specs_of_the_five_configs():
     c5 = spec_of("c5_attn_causal_b16s4096h32d128")
     assert c5.extent == 16 and c5.outputs == (3, 4)
     assert local_slices(c5, 8, 3)[0] == (0, slice(6, 8))
+    norm = spec_of("layernorm_2x4x128_bf16")   # rank-3 input: the leading axis splits, weight and bias are replicated
+    assert norm.extent == 2 and norm.sharded == ((0, 0), (1, 0), (2, 0), (3, 0)) and norm.replicated == (4, 5) and norm.outputs == (2, 3)
+    rows = spec_of("reduce_row_sumsq_16x96_f32")
+    assert rows.extent == 16 and rows.sharded == ((0, 0), (1, 0)) and rows.outputs == (1,)
+    for case in ("reduce_col_max_24x64_bf16", "reduce_total_sum_8x96_f32"):  # folds over the leading axis run whole on one GPU
+        whole = spec_of(case)
+        assert whole.extent == 1 and not whole.sharded and whole.replicated == (0, 1) and whole.outputs == (1,)
 
 
 def _free_port() -> int:
