@@ -362,7 +362,8 @@ class B200Backend:
                 else:
                     launch("bb200_reduce_cols_vec_partial", native.U3(vec_blocks, vec_slabs, 1), vec_block,
                            inputs + [scratch, ctypes.c_size_t(outer), ctypes.c_size_t(inner)], stream_handle)
-                    launch("bb200_reduce_partials_cols_vec", native.U3(-(-(inner // partial_vec) // vec_threads), 1, 1), vec_block,
+                    # the fold over the slabs is a short serial walk per thread: one warp per CTA spreads it over more SMs
+                    launch("bb200_reduce_partials_cols_vec", native.U3(-(-(inner // partial_vec) // 32), 1, 1), native.U3(32, 1, 1),
                            [scratch] + dst + [ctypes.c_size_t(vec_slabs), ctypes.c_size_t(inner), init], stream_handle)
             else:
                 columns = native.U3(-(-inner // threads), slabs, 1)
