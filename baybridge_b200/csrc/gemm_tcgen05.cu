@@ -1,9 +1,9 @@
 // gemm_tcgen05.cu — BF16 GEMM for sm_100a: C[m,n] = sum_k A'[m,k] * B'[k,n], fp32 accumulate.
 //
-// Native forms: A is [M,K] row-major (K contiguous); B is either [N,K] (K contiguous, "A · B^T") or
-// [K,N] (N contiguous, "A · B") — tcgen05 consumes both through its K-major / MN-major shared-memory
-// descriptors.  A stored [K,M] is brought to [M,K] by a tiled transpose into a stream-ordered
-// workspace.
+// Native forms: A is [M,K] (K contiguous) or [K,M] (M contiguous); B is [N,K] (K contiguous, "A · B^T")
+// or [K,N] (N contiguous, "A · B") — tcgen05 consumes all four through its K-major / MN-major
+// shared-memory descriptors.  Only A stored [K,M] with M not a multiple of 8 (rows that are not 16-byte
+// multiples, which TMA cannot read) is brought to [M,K] by a tiled transpose into a workspace.
 //
 // Kernel structure (one persistent CTA per SM, 192 threads):
 //   warp 0      TMA producer: streams 128x64 A tiles and 256x64 B tiles (128-byte swizzle) into a
@@ -90,8 +90,9 @@ template <> __device__ __forceinline__ void store_chunk<float>(float* row_ptr, c
 }
 
 // B_MN = false: B tile is [BN n-rows, 64 k] (K-major).  B_MN = true: B is stored [K, N]; a stage holds
-// BN/64 sub-tiles of [64 k-rows, 64 n] (MN-major), each 8 KB, consecutive in shared memory.
-template <typename OutT, bool B_MN>
+// BN/64 sub-tiles of [64 k-rows, 64 n] (MN-major), each 8 KB, consecutive in shared memory.  A_MN is the
+// same for A stored [K, M]: BM/64 sub-tiles of [64 k-rows, 64 m].
+template <typename OutT, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_abt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, OutT* __restrict__ c,
                 int m, int n, int k, int group_m, int* status_word) {
@@ -150,7 +151,13 @@ gemm_abt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           const uint32_t a_dst = smem_base + stage * STAGE_BYTES;
           const uint32_t b_dst = a_dst + A_TILE_BYTES;
           mbar_arrive_expect_tx(full_bar(stage), STAGE_BYTES);
-          tma_load_2d(a_dst, &map_a, full_bar(stage), kb * BK, coord.m_block * BM);
+          if constexpr (A_MN) {
+#pragma unroll
+            for (int t = 0; t < BM / 64; ++t)
+              tma_load_2d(a_dst + t * (BK * 128), &map_a, full_bar(stage), coord.m_block * BM + t * 64, kb * BK);
+          } else {
+            tma_load_2d(a_dst, &map_a, full_bar(stage), kb * BK, coord.m_block * BM);
+          }
           if constexpr (B_MN) {
 #pragma unroll
             for (int t = 0; t < BN / 64; ++t)
@@ -165,7 +172,7 @@ gemm_abt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (elect_one()) {
-      constexpr uint32_t idesc = umma_idesc_bf16_f32(BM, BN, false, B_MN);
+      constexpr uint32_t idesc = umma_idesc_bf16_f32(BM, BN, A_MN, B_MN);
       int stage = 0;
       uint32_t phase = 0;
       int local_tile = 0;
@@ -180,14 +187,15 @@ gemm_abt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           if (!(ok = mbar_wait(full_bar(stage), phase, abort_flag, status_word, kWaitFull))) break;
           tcgen05_fence_after();
           const uint32_t a_src = smem_base + stage * STAGE_BYTES;
-          const uint64_t desc_a = umma_desc_k_major_sw128(a_src);
+          const uint64_t desc_a = A_MN ? umma_desc_mn_major_sw128(a_src, BK * 128) : umma_desc_k_major_sw128(a_src);
           const uint64_t desc_b = B_MN ? umma_desc_mn_major_sw128(a_src + A_TILE_BYTES, BK * 128)
                                        : umma_desc_k_major_sw128(a_src + A_TILE_BYTES);
           // one K step of 16: 32 bytes along a K-major row, or 16 rows of 128 bytes in an MN-major tile
+          constexpr uint32_t a_step = A_MN ? UMMA_K * 128 : UMMA_K * 2;
           constexpr uint32_t b_step = B_MN ? UMMA_K * 128 : UMMA_K * 2;
 #pragma unroll
           for (int kk = 0; kk < BK / UMMA_K; ++kk)
-            umma_bf16_ss(tmem_acc, umma_desc_advance_k(desc_a, kk * UMMA_K * 2), umma_desc_advance_k(desc_b, kk * b_step),
+            umma_bf16_ss(tmem_acc, umma_desc_advance_k(desc_a, kk * a_step), umma_desc_advance_k(desc_b, kk * b_step),
                          idesc, (kb | kk) != 0 ? 1u : 0u);
           umma_commit(empty_bar(stage));  // the stage may be refilled once these MMAs have read it
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -260,7 +268,7 @@ constexpr int PAIR_STAGE_BYTES = A_TILE_BYTES + PAIR_B_BYTES;
 constexpr int PAIR_SMEM_BYTES = PAIR_STAGES * PAIR_STAGE_BYTES + 1024 + 256;
 constexpr int PAIR_BM = 2 * BM;
 
-template <typename OutT, bool B_MN>
+template <typename OutT, bool A_MN, bool B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 gemm_abt_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, OutT* __restrict__ c,
                      int m, int n, int k, int group_m, int* status_word) {
@@ -324,7 +332,13 @@ gemm_abt_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
           const uint32_t a_dst = smem_base + stage * PAIR_STAGE_BYTES;
           const uint32_t signal = leader_cta_address(full_bar(stage));
           if (leader) mbar_arrive_expect_tx(full_bar(stage), 2 * PAIR_STAGE_BYTES);
-          tma_load_2d_pair(a_dst, &map_a, signal, kb * BK, a_row);
+          if constexpr (A_MN) {
+#pragma unroll
+            for (int t = 0; t < BM / 64; ++t)
+              tma_load_2d_pair(a_dst + t * (BK * 128), &map_a, signal, a_row + t * 64, kb * BK);
+          } else {
+            tma_load_2d_pair(a_dst, &map_a, signal, kb * BK, a_row);
+          }
           if constexpr (B_MN) {
 #pragma unroll
             for (int t = 0; t < PAIR_B_ROWS / 64; ++t)
@@ -339,7 +353,8 @@ gemm_abt_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   } else if (warp == 1) {
     // ---------------- MMA issuer (CTA 0 only) ----------------
     if (leader && elect_one()) {
-      constexpr uint32_t idesc = umma_idesc_bf16_f32(PAIR_BM, BN, false, B_MN);
+      constexpr uint32_t idesc = umma_idesc_bf16_f32(PAIR_BM, BN, A_MN, B_MN);
+      constexpr uint32_t a_step = A_MN ? UMMA_K * 128 : UMMA_K * 2;
       constexpr uint32_t b_step = B_MN ? UMMA_K * 128 : UMMA_K * 2;
       int stage = 0;
       uint32_t phase = 0;
@@ -355,12 +370,12 @@ gemm_abt_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
           if (!(ok = mbar_wait(full_bar(stage), phase, abort_flag, status_word, kWaitFull))) break;
           tcgen05_fence_after();
           const uint32_t a_src = smem_base + stage * PAIR_STAGE_BYTES;
-          const uint64_t desc_a = umma_desc_k_major_sw128(a_src);
+          const uint64_t desc_a = A_MN ? umma_desc_mn_major_sw128(a_src, BK * 128) : umma_desc_k_major_sw128(a_src);
           const uint64_t desc_b = B_MN ? umma_desc_mn_major_sw128(a_src + A_TILE_BYTES, BK * 128)
                                        : umma_desc_k_major_sw128(a_src + A_TILE_BYTES);
 #pragma unroll
           for (int kk = 0; kk < BK / UMMA_K; ++kk)
-            umma_bf16_ss_pair(tmem_acc, umma_desc_advance_k(desc_a, kk * UMMA_K * 2), umma_desc_advance_k(desc_b, kk * b_step),
+            umma_bf16_ss_pair(tmem_acc, umma_desc_advance_k(desc_a, kk * a_step), umma_desc_advance_k(desc_b, kk * b_step),
                               idesc, (kb | kk) != 0 ? 1u : 0u);
           umma_commit_pair(empty_bar(stage), 0x3);
           if (++stage == PAIR_STAGES) { stage = 0; phase ^= 1u; }
@@ -479,32 +494,37 @@ bool use_pair_kernel(int m, int n, int sms) {
   return (sms % 2) == 0 && tiles >= sms / 2;
 }
 
-template <typename OutT, bool B_MN>
-int launch_pair(const void* a_mk, const void* b, void* c, int m, int n, int k, int device, int sms, cudaStream_t stream) {
+template <typename OutT, bool A_MN, bool B_MN>
+int launch_pair(const void* a_operand, const void* b, void* c, int m, int n, int k, int device, int sms, cudaStream_t stream) {
   alignas(64) CUtensorMap map_a, map_b;
-  if (int status = encode_tensormap_2d(&map_a, BB200_BF16, a_mk, (uint64_t)m, (uint64_t)k, (uint64_t)k * 2, BM, BK, 3)) return status;
+  if (int status = A_MN ? encode_tensormap_2d(&map_a, BB200_BF16, a_operand, (uint64_t)k, (uint64_t)m, (uint64_t)m * 2, BK, 64, 3)
+                        : encode_tensormap_2d(&map_a, BB200_BF16, a_operand, (uint64_t)m, (uint64_t)k, (uint64_t)k * 2, BM, BK, 3))
+    return status;
   if (int status = B_MN ? encode_tensormap_2d(&map_b, BB200_BF16, b, (uint64_t)k, (uint64_t)n, (uint64_t)n * 2, BK, 64, 3)
                         : encode_tensormap_2d(&map_b, BB200_BF16, b, (uint64_t)n, (uint64_t)k, (uint64_t)k * 2, PAIR_B_ROWS, BK, 3))
     return status;
   static bool configured[kMaxDevices] = {};
   if (!configured[device]) {
-    if (int status = check_runtime(cudaFuncSetAttribute(gemm_abt_pair_kernel<OutT, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM_BYTES),
+    if (int status = check_runtime(cudaFuncSetAttribute(gemm_abt_pair_kernel<OutT, A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM_BYTES),
                                    "cudaFuncSetAttribute(gemm pair smem)"))
       return status;
     configured[device] = true;
   }
   const int tiles = ((m + PAIR_BM - 1) / PAIR_BM) * ((n + BN - 1) / BN);
   const int pairs = tiles < sms / 2 ? tiles : sms / 2;
-  gemm_abt_pair_kernel<OutT, B_MN><<<2 * pairs, THREADS, PAIR_SMEM_BYTES, stream>>>(map_a, map_b, static_cast<OutT*>(c), m, n, k, raster_group_m() / 2 > 0 ? raster_group_m() / 2 : 1,
+  gemm_abt_pair_kernel<OutT, A_MN, B_MN><<<2 * pairs, THREADS, PAIR_SMEM_BYTES, stream>>>(map_a, map_b, static_cast<OutT*>(c), m, n, k, raster_group_m() / 2 > 0 ? raster_group_m() / 2 : 1,
                                                                              device_status_word());
   return check_launch("gemm pair kernel launch");
 }
 
-// b_is_kn: B is stored [k, n] (n contiguous) and consumed as an MN-major operand; otherwise [n, k].
-template <typename OutT, bool B_MN>
-int launch_native(const void* a_mk, const void* b, void* c, int m, int n, int k, cudaStream_t stream) {
+// A_MN: A is stored [k, m] (m contiguous) and consumed as an MN-major operand; otherwise [m, k].
+// B_MN: B is stored [k, n] (n contiguous), MN-major; otherwise [n, k].
+template <typename OutT, bool A_MN, bool B_MN>
+int launch_native(const void* a_operand, const void* b, void* c, int m, int n, int k, cudaStream_t stream) {
   alignas(64) CUtensorMap map_a, map_b;
-  if (int status = encode_tensormap_2d(&map_a, BB200_BF16, a_mk, (uint64_t)m, (uint64_t)k, (uint64_t)k * 2, BM, BK, 3)) return status;
+  if (int status = A_MN ? encode_tensormap_2d(&map_a, BB200_BF16, a_operand, (uint64_t)k, (uint64_t)m, (uint64_t)m * 2, BK, 64, 3)
+                        : encode_tensormap_2d(&map_a, BB200_BF16, a_operand, (uint64_t)m, (uint64_t)k, (uint64_t)k * 2, BM, BK, 3))
+    return status;
   if (int status = B_MN ? encode_tensormap_2d(&map_b, BB200_BF16, b, (uint64_t)k, (uint64_t)n, (uint64_t)n * 2, BK, 64, 3)
                         : encode_tensormap_2d(&map_b, BB200_BF16, b, (uint64_t)n, (uint64_t)k, (uint64_t)k * 2, BN, BK, 3))
     return status;
@@ -512,18 +532,37 @@ int launch_native(const void* a_mk, const void* b, void* c, int m, int n, int k,
   if (device < 0) return fail(BB200_E_NO_DRIVER, "gemm: no CUDA device is current");
   static bool configured[kMaxDevices] = {};  // per template instantiation and device
   if (!configured[device]) {
-    if (int status = check_runtime(cudaFuncSetAttribute(gemm_abt_kernel<OutT, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES),
+    if (int status = check_runtime(cudaFuncSetAttribute(gemm_abt_kernel<OutT, A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES),
                                    "cudaFuncSetAttribute(gemm smem)"))
       return status;
     configured[device] = true;
   }
   const int sms = cached_sm_count(device);
   if (sms <= 0) return fail(BB200_E_NO_DRIVER, "gemm: could not query the SM count");
-  if (use_pair_kernel(m, n, sms)) return launch_pair<OutT, B_MN>(a_mk, b, c, m, n, k, device, sms, stream);
+  if (use_pair_kernel(m, n, sms)) return launch_pair<OutT, A_MN, B_MN>(a_operand, b, c, m, n, k, device, sms, stream);
   const int tiles = ((m + BM - 1) / BM) * ((n + BN - 1) / BN);
   const int grid = tiles < sms ? tiles : sms;
-  gemm_abt_kernel<OutT, B_MN><<<grid, THREADS, SMEM_BYTES, stream>>>(map_a, map_b, static_cast<OutT*>(c), m, n, k, raster_group_m(), device_status_word());
+  gemm_abt_kernel<OutT, A_MN, B_MN><<<grid, THREADS, SMEM_BYTES, stream>>>(map_a, map_b, static_cast<OutT*>(c), m, n, k, raster_group_m(), device_status_word());
   return check_launch("gemm kernel launch");
+}
+
+int dispatch_native(const void* a_operand, const void* b, void* c, int m, int n, int k, bool a_is_km, bool b_is_kn,
+                    bb200_dtype c_dtype, cudaStream_t s) {
+#define BB200_GEMM_CASE(OUT, A_MN, B_MN) \
+  if (a_is_km == A_MN && b_is_kn == B_MN) return launch_native<OUT, A_MN, B_MN>(a_operand, b, c, m, n, k, s)
+  if (c_dtype == BB200_BF16) {
+    BB200_GEMM_CASE(__nv_bfloat16, false, false);
+    BB200_GEMM_CASE(__nv_bfloat16, false, true);
+    BB200_GEMM_CASE(__nv_bfloat16, true, false);
+    BB200_GEMM_CASE(__nv_bfloat16, true, true);
+  } else {
+    BB200_GEMM_CASE(float, false, false);
+    BB200_GEMM_CASE(float, false, true);
+    BB200_GEMM_CASE(float, true, false);
+    BB200_GEMM_CASE(float, true, true);
+  }
+#undef BB200_GEMM_CASE
+  return fail(BB200_E_INVALID_ARGUMENT, "gemm: unreachable operand layout");
 }
 
 }  // namespace
@@ -539,24 +578,23 @@ extern "C" int bb200_gemm_bf16(const void* a, const void* b, void* c, int m, int
   if (k % 8) return fail(BB200_E_UNSUPPORTED_SHAPE, "gemm: k=%d must be a multiple of 8 (16-byte rows for TMA)", k);
   if (!aligned16(a) || !aligned16(b)) return fail(BB200_E_MISALIGNED, "gemm: A and B must be 16-byte aligned");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  // B is consumed in place in either layout; only A stored [k, m] needs a transposed copy
+  // Both operands are consumed in place in either layout (MN-major descriptors).  The one exception is A
+  // stored [k, m] with m not a multiple of 8: its rows are not 16-byte multiples, which TMA needs, so it is
+  // transposed into a workspace first.
   const bool b_is_kn = !transpose_b;
   if (b_is_kn && (n % 8)) return fail(BB200_E_UNSUPPORTED_SHAPE, "gemm: n=%d must be a multiple of 8 when B is stored [k, n]", n);
-  const void* a_mk = a;
+  const bool a_in_place = transpose_a && (m % 8) == 0;
+  const void* a_operand = a;
   void* workspace = nullptr;
-  if (transpose_a) {  // stored [k, m] -> [m, k]
+  if (transpose_a && !a_in_place) {  // stored [k, m] -> [m, k]
     if (int status = check_runtime(cudaMallocAsync(&workspace, (size_t)m * k * 2, s), "cudaMallocAsync(gemm workspace)")) return status;
     if (int status = launch_transpose(a, workspace, k, m, s)) {
       cudaFreeAsync(workspace, s);
       return status;
     }
-    a_mk = workspace;
+    a_operand = workspace;
   }
-  int status;
-  if (c_dtype == BB200_BF16)
-    status = b_is_kn ? launch_native<__nv_bfloat16, true>(a_mk, b, c, m, n, k, s) : launch_native<__nv_bfloat16, false>(a_mk, b, c, m, n, k, s);
-  else
-    status = b_is_kn ? launch_native<float, true>(a_mk, b, c, m, n, k, s) : launch_native<float, false>(a_mk, b, c, m, n, k, s);
+  int status = dispatch_native(a_operand, b, c, m, n, k, a_in_place, b_is_kn, c_dtype, s);
   if (workspace) {
     const int freed = check_runtime(cudaFreeAsync(workspace, s), "cudaFreeAsync(gemm workspace)");
     if (!status) status = freed;
@@ -566,7 +604,7 @@ extern "C" int bb200_gemm_bf16(const void* a, const void* b, void* c, int m, int
 
 // ---- allocation-free variant -------------------------------------------------------------------------
 // bb200_gemm_bf16 above borrows a stream-ordered workspace (cudaMallocAsync) whenever A arrives stored
-// [k, m].  That is a problem for embedders that must not allocate while they run: an inference server
+// [k, m] with m not a multiple of 8 (the one layout TMA cannot read in place).  That is a problem for embedders that must not allocate while they run: an inference server
 // that has already sized its own pools to fill the device (so a late driver allocation can fail or
 // evict), a host framework whose caching allocator is meant to be the only owner of device memory, or
 // a latency-critical loop where an allocation call may stall behind other work on the device.  For
@@ -614,20 +652,19 @@ extern "C" int bb200_gemm_bf16_noalloc(const void* a, const void* b, void* c, in
   const bool b_is_kn = !transpose_b;
   if (b_is_kn && (n % 8)) return fail(BB200_E_UNSUPPORTED_SHAPE, "gemm (no-alloc): n=%d must be a multiple of 8 when B is stored [k, n]", n);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const void* a_mk = a;
-  if (transpose_a) {
+  const bool a_in_place = transpose_a && (m % 8) == 0;  // consumed as an MN-major operand: nothing to stage
+  const void* a_operand = a;
+  if (transpose_a && !a_in_place) {
     const size_t needed = (size_t)m * (size_t)k * 2;
     if (needed > kGemmStaticScratchBytes)
       return fail(BB200_E_TOO_LARGE,
                   "gemm (no-alloc): A stored [k, m] needs a %zu-byte transposed copy but the built-in buffer holds %zu bytes "
-                  "(m*k <= %zu); pass A as [m, k] or use bb200_gemm_bf16",
+                  "(m*k <= %zu); pass A as [m, k], make m a multiple of 8, or use bb200_gemm_bf16",
                   needed, kGemmStaticScratchBytes, kGemmStaticScratchBytes / 2);
     void* scratch = nullptr;
     if (int status = gemm_static_scratch(&scratch)) return status;
     if (int status = launch_transpose(a, scratch, k, m, s)) return status;
-    a_mk = scratch;
+    a_operand = scratch;
   }
-  if (c_dtype == BB200_BF16)
-    return b_is_kn ? launch_native<__nv_bfloat16, true>(a_mk, b, c, m, n, k, s) : launch_native<__nv_bfloat16, false>(a_mk, b, c, m, n, k, s);
-  return b_is_kn ? launch_native<float, true>(a_mk, b, c, m, n, k, s) : launch_native<float, false>(a_mk, b, c, m, n, k, s);
+  return dispatch_native(a_operand, b, c, m, n, k, a_in_place, b_is_kn, c_dtype, s);
 }

@@ -192,7 +192,9 @@ int bb200_layernorm(bb200_dtype dtype, const void* x, const void* residual, cons
 
 /* C[m, n] = sum_k A'[m, k] * B'[k, n]; A' = A or A^T, B' = B or B^T per the transpose flags;
  * A, B bf16 row-major as stored ([m,k] or [k,m]; [k,n] or [n,k]); C row-major [m, n] of
- * c_dtype bf16 or f32; fp32 accumulation on tcgen05 tensor cores; C is overwritten.
+ * c_dtype bf16 or f32; fp32 accumulation on tcgen05 tensor cores; C is overwritten.  Every layout is
+ * read in place except A stored [k, m] with m not a multiple of 8, which is first transposed into a
+ * stream-ordered workspace taken from the driver.
  * Replaces launch_<kernel> of the GEMM template (src/baybridge/backends/hipkittens_exec.py:
  * 994-1044; semantics src/baybridge/frontend.py:3684-3716). */
 int bb200_gemm_bf16(const void* a, const void* b, void* c, int m, int n, int k, int transpose_a, int transpose_b,
@@ -202,11 +204,12 @@ int bb200_gemm_bf16(const void* a, const void* b, void* c, int m, int n, int k, 
  * while they run — a server whose own pools already fill the GPU, a framework whose allocator has to
  * stay the sole owner of device memory, a latency-critical loop that cannot afford a driver
  * allocation stalling or failing late.  bb200_gemm_bf16 takes a stream-ordered workspace from the
- * driver when A is stored [k, m]; this entry point puts that transposed copy of A into a 32 MiB
- * buffer built into the library instead, and performs no cudaMalloc / cudaFree / pool operation of
- * any kind.  Limits and rules:
- *   - with transpose_a != 0, m*k must not exceed 16,777,216 elements (32 MiB of bf16); larger requests
- *     return BB200_E_TOO_LARGE.  With transpose_a == 0 the buffer is not used and any size is accepted.
+ * driver when A is stored [k, m] with m not a multiple of 8; this entry point puts that transposed
+ * copy of A into a 32 MiB buffer built into the library instead, and performs no cudaMalloc /
+ * cudaFree / pool operation of any kind.  Limits and rules:
+ *   - with transpose_a != 0 and m % 8 != 0, m*k must not exceed 16,777,216 elements (32 MiB of bf16);
+ *     larger requests return BB200_E_TOO_LARGE.  In every other case the buffer is not used and any
+ *     size is accepted.
  *   - the buffer exists once per GPU and every call uses it, so two calls whose GPU work may overlap
  *     (different streams or threads) must be serialised by the caller; it keeps the previous call's
  *     contents between calls, which is harmless because each call overwrites what it reads.

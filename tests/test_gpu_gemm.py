@@ -62,11 +62,16 @@ def test_c_abi_gemm_abt_shapes(m, n, k, c_dtype):
     assert oracle.rel_l2(to_host(d_c), reference) <= (REL_L2_BF16 if c_dtype == "bf16" else REL_L2_F32)
 
 
-def test_c_abi_gemm_transpose_variants_agree():
+@pytest.mark.parametrize("m,n,k", [
+    (160, 264, 96),      # everything read in place (m and n multiples of 8)
+    (156, 264, 96),      # A stored [k, m] with m % 8 != 0: the transposed-copy path
+    (640, 1032, 200),    # several tiles, ragged edges in m, n and k
+    (2560, 2048, 136),   # enough 256x256 tiles for the CTA-pair kernel
+])
+def test_c_abi_gemm_transpose_variants_agree(m, n, k):
     from baybridge_b200.backend import native
 
-    m, n, k = 160, 264, 96
-    rng = np.random.default_rng(11)
+    rng = np.random.default_rng(11 + m)
     a = oracle.bf16_round(rng.standard_normal((m, k)).astype(np.float32))
     b = oracle.bf16_round(rng.standard_normal((k, n)).astype(np.float32))
     reference = oracle.gemm(a, b)

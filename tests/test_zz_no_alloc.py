@@ -3,8 +3,9 @@
 ``bb200_gemm_bf16_noalloc`` exists for embedders that may not allocate device memory at run time
 (their own pools already own the GPU, or an allocation could stall or fail in a latency-critical
 loop).  It stages the transposed copy of A in a buffer built into the library instead of asking the
-driver for a workspace.  The check here: through the C ABI, with A stored [k, m] so the built-in
-buffer is really used, the result must be identical to ``bb200_gemm_bf16`` — twice in a row, with
+driver for a workspace.  The check here: through the C ABI, with A stored [k, m] and m not a multiple
+of 8 (the one layout the kernel cannot read in place) so the built-in buffer is really used, the
+result must be identical to ``bb200_gemm_bf16`` — twice in a row, with
 different inputs, because the buffer keeps the previous call's contents.  The file sorts last so a
 ``-x`` run has already exercised every other test when it gets here; it also passes when run alone.
 """
@@ -35,7 +36,8 @@ def test_noalloc_gemm_equals_regular_gemm_on_two_calls_in_a_row(c_dtype):
     from baybridge_b200.backend import native
 
     code = native.DTYPE_CODES[c_dtype]
-    for call, (m, n, k) in enumerate([(384, 520, 264), (200, 136, 72)]):  # second call is smaller: stale bytes stay behind it
+    # m % 8 != 0: the staged-copy path; the second call is smaller, so stale bytes of the first stay behind it
+    for call, (m, n, k) in enumerate([(380, 520, 264), (196, 136, 72)]):
         a_km, b_nk = _pair(100 + call, m, n, k)
         a, b = to_device(a_km, "bf16"), to_device(b_nk, "bf16")
         expected, got = device_zeros((m, n), c_dtype), device_zeros((m, n), c_dtype)
@@ -65,8 +67,32 @@ def test_noalloc_gemm_without_transposed_a_and_size_limit():
     native.call("bb200_gemm_bf16_noalloc", void_p(a_mk), void_p(b), void_p(got), m, n, k, 0, 1, 1, current_stream())
     torch.cuda.synchronize()
     assert torch.equal(got, expected)
-    # 8192 x 4096 transposed elements = 64 MiB > the 32 MiB built-in buffer: rejected before anything is launched
+    # 8188 x 4096 transposed elements = 64 MiB > the 32 MiB built-in buffer: rejected before anything is launched
     with pytest.raises(CudaDriverError) as info:
-        native.call("bb200_gemm_bf16_noalloc", void_p(a_mk), void_p(b), void_p(got), 8192, 256, 4096, 1, 1, 1, current_stream())
+        native.call("bb200_gemm_bf16_noalloc", void_p(a_mk), void_p(b), void_p(got), 8188, 256, 4096, 1, 1, 1, current_stream())
     assert info.value.status == -7  # BB200_E_TOO_LARGE
     assert "built-in buffer" in info.value.message
+
+
+@pytest.mark.parametrize("c_dtype", ["bf16", "f32"])
+def test_noalloc_gemm_reads_aligned_transposed_a_in_place(c_dtype):
+    """A stored [k, m] with m a multiple of 8 needs no staged copy at all: no size limit applies, and both entry
+    points agree with the oracle."""
+    import torch
+
+    from baybridge_b200.backend import native
+
+    code = native.DTYPE_CODES[c_dtype]
+    m, n, k = 384, 520, 264
+    a_km, b_nk = _pair(11, m, n, k)
+    a, b = to_device(a_km, "bf16"), to_device(b_nk, "bf16")
+    expected, got = device_zeros((m, n), c_dtype), device_zeros((m, n), c_dtype)
+    native.call("bb200_gemm_bf16", void_p(a), void_p(b), void_p(expected), m, n, k, 1, 1, code, current_stream())
+    native.call("bb200_gemm_bf16_noalloc", void_p(a), void_p(b), void_p(got), m, n, k, 1, 1, code, current_stream())
+    torch.cuda.synchronize()
+    assert torch.equal(got, expected)
+    assert oracle.rel_l2(to_host(got), oracle.gemm(a_km, b_nk, transpose_a=True, transpose_b=True)) <= (1e-2 if c_dtype == "bf16" else 1e-5)
+    # 8192 x 4096 elements would not fit the built-in buffer, but nothing is staged for this layout
+    big_a, big_b, big_c = device_zeros((4096, 8192), "bf16"), device_zeros((256, 4096), "bf16"), device_zeros((8192, 256), c_dtype)
+    native.call("bb200_gemm_bf16_noalloc", void_p(big_a), void_p(big_b), void_p(big_c), 8192, 256, 4096, 1, 1, code, current_stream())
+    torch.cuda.synchronize()
