@@ -366,10 +366,13 @@ def _match_attention(ir, op) -> AttentionPlan:
 # ---------------------------------------------------------------------------------------------
 @dataclass(frozen=True)
 class Digit:
-    """``(i // div) % mod`` of the global linear thread id ``i`` (``mod is None`` = no wrap)."""
+    """``(v // div) % mod`` of a launch variable ``v`` (``mod is None`` = no wrap).  For a one-dimensional
+    launch the only variable is ``"i"``, the global linear thread id; a multi-dimensional launch has one
+    variable per axis, ``block_idx.a * block_dim.a + thread_idx.a`` for ``a`` in x, y, z."""
 
     div: int
     mod: int | None
+    var: str = "i"
 
 
 class Sym:
@@ -401,9 +404,50 @@ class Sym:
     def scaled(self, factor: int) -> "Sym":
         return Sym({digit: coef * factor for digit, coef in self.terms.items()}, self.const * factor)
 
+    def same_as(self, other: "Sym") -> bool:
+        return self.const == other.const and self.terms == other.terms
+
+    def bijection_extent(self, extents: dict[str, int]) -> int | None:
+        """If the expression is a mixed-radix number whose digits are exactly the digits of the launch
+        variables (``extents``: variable → number of values), it maps the launched threads one-to-one onto
+        ``[0, N)``: returns N, else None.  Variables of extent 1 may be absent."""
+        if self.const != 0 or not self.terms:
+            return None
+        by_var: dict[str, list[Digit]] = {}
+        for digit in self.terms:
+            by_var.setdefault(digit.var, []).append(digit)
+        ranges: dict[Digit, int] = {}
+        for var, extent in extents.items():
+            digits = sorted(by_var.pop(var, []), key=lambda d: d.div)
+            if not digits:
+                if extent != 1:
+                    return None  # threads that differ only in this variable would collide
+                continue
+            expected_div = 1
+            for position, digit in enumerate(digits):  # the digits must tile the variable's range exactly
+                if digit.div != expected_div:
+                    return None
+                if position == len(digits) - 1:
+                    if extent % digit.div or (digit.mod is not None and digit.div * digit.mod != extent):
+                        return None
+                    ranges[digit] = extent // digit.div
+                else:
+                    if digit.mod is None:
+                        return None
+                    ranges[digit] = digit.mod
+                    expected_div = digit.div * digit.mod
+        if by_var:
+            return None
+        weight = 1
+        for digit, coef in sorted(self.terms.items(), key=lambda item: item[1]):
+            if coef != weight:
+                return None
+            weight *= ranges[digit]
+        return weight
+
     def equals_linear_id(self, threads: int) -> bool:
         """True iff the expression equals ``i`` for every ``0 <= i < threads`` (digits tile exactly)."""
-        if self.const != 0 or not self.terms:
+        if self.const != 0 or not self.terms or any(digit.var != "i" for digit in self.terms):
             return False
         expected_div = 1
         ordered = sorted(self.terms.items(), key=lambda item: item[0].div)
@@ -473,7 +517,9 @@ class _Elementwise:
             # i = block_idx.x * block + thread_idx.x  ⇒  thread_idx.x = i % block, block_idx.x = i // block
             self.sym[name] = Sym({Digit(1, block): 1}) if kind == "thread_idx" else Sym({Digit(block, None): 1})
         else:
-            self.sym[name] = None
+            # one independent variable per axis: v_a = block_idx.a * block_dim.a + thread_idx.a
+            block = self.launch.block[index]
+            self.sym[name] = Sym({Digit(1, block, axis): 1}) if kind == "thread_idx" else Sym({Digit(block, None, axis): 1})
 
     def scalar_arith(self, op) -> None:
         name = op.outputs[0]
@@ -505,20 +551,23 @@ class _Elementwise:
     def _divmod(value: Sym, divisor: int, op: str) -> Sym | None:
         # reassemble "i // d" style sums (e.g. block_idx*block + thread_idx) into a single digit first
         digit = value.single_digit()
-        if digit is None:
-            probe = Sym(dict(value.terms), value.const)
-            if probe.const == 0 and probe.equals_linear_id(1 << 62):
-                digit = Digit(1, None)
+        if digit is None and value.const == 0 and value.terms:
+            variables = {d.var for d in value.terms}
+            if len(variables) == 1:
+                (var,) = variables
+                renamed = Sym({Digit(d.div, d.mod): coef for d, coef in value.terms.items()})
+                if renamed.equals_linear_id(1 << 62):
+                    digit = Digit(1, None, var)
         if digit is None:
             return None
         if op == "floordiv":
             if digit.mod is None:
-                return Sym({Digit(digit.div * divisor, None): 1})
+                return Sym({Digit(digit.div * divisor, None, digit.var): 1})
             if digit.mod % divisor == 0:
-                return Sym({Digit(digit.div * divisor, digit.mod // divisor): 1})
+                return Sym({Digit(digit.div * divisor, digit.mod // divisor, digit.var): 1})
             return None
         if digit.mod is None or digit.mod % divisor == 0:
-            return Sym({Digit(digit.div, divisor): 1})
+            return Sym({Digit(digit.div, divisor, digit.var): 1})
         if divisor % digit.mod == 0:
             return Sym({digit: 1})
         return None
@@ -577,15 +626,34 @@ class _Elementwise:
         if not any(access["kind"] == "store" for access in self.accesses):
             raise _unsupported("the kernel body stores nothing")
         threads = self.launch.threads
-        if not self.one_d:
-            self.not_flat("a multi-dimensional launch")
-        for access in self.accesses:
-            if access["offset"] is None or not access["offset"].equals_linear_id(threads):
-                self.not_flat("an access whose offset is not provably the linear thread id")
         scalars = tuple(position for position, argument in enumerate(self.ir.arguments) if argument.kind == "scalar")
-        if self.flat_ok:
+        identity = self.flat_ok and self.one_d and all(
+            access["offset"] is not None and access["offset"].equals_linear_id(threads) for access in self.accesses)
+        if identity:
             return self._flat_plan(threads, scalars)
+        # Any launch shape: if every access uses the same offset expression and that expression maps the
+        # launched threads one-to-one onto [0, numel) of every tensor, the body is an elementwise map and the
+        # order in which threads visit the elements does not matter.
+        if self.flat_ok and self.bound is None and self._is_permutation_map(threads):
+            return self._flat_plan(threads, scalars)
+        if self.one_d:
+            self.not_flat("an access whose offset is not provably the linear thread id")
+        else:
+            self.not_flat("a multi-dimensional launch whose accesses are not provably one shared one-to-one map")
         return self._literal_plan(scalars)
+
+    def _is_permutation_map(self, threads: int) -> bool:
+        first = self.accesses[0]["offset"]
+        if first is None or any(access["predicate"] is not None for access in self.accesses):
+            return False
+        if any(access["offset"] is None or not access["offset"].same_as(first) for access in self.accesses):
+            return False
+        if self.one_d:
+            extents = {"i": threads}
+        else:
+            extents = {axis: self.launch.grid[k] * self.launch.block[k] for k, axis in enumerate("xyz")}
+        covered = first.bijection_extent(extents)
+        return covered is not None and covered == threads and all(access["numel"] == covered for access in self.accesses)
 
     def _flat_plan(self, threads: int, scalars: tuple[int, ...]) -> ElementwisePlan:
         extent = min([threads] + [access["numel"] for access in self.accesses] + ([self.bound] if self.bound is not None else []))

@@ -234,7 +234,7 @@ def test_literal_lowering_reversed_and_strided_indices(tmp_path):
                         {"src": "bf16", "dst": "bf16"}, tmp_path)
 
 
-def test_literal_lowering_two_dimensional_launch(tmp_path):
+def test_two_dimensional_launch_with_scalar_argument(tmp_path):
     import baybridge_b200 as cute
 
     rows, cols = 48, 80
@@ -252,6 +252,60 @@ def test_literal_lowering_two_dimensional_launch(tmp_path):
          "out": np.zeros((rows, cols), np.float32)},
         {"x": "f32", "y": "f32", "out": "f32"}, tmp_path, scalars=(0.1,),  # 0.1 is not an f32: the f64 path keeps it exact
     )
+
+
+def test_multi_dimensional_launches_flat_when_one_shared_bijection_else_literal(tmp_path):
+    import baybridge_b200 as cute
+    from baybridge_b200.backend.matcher import match
+
+    rng = np.random.default_rng(24)
+    rows, cols = 48, 80
+
+    # covers [48, 80] exactly with one thread per element and the same (row, col) in every access: vectorised form
+    @cute.kernel(launch=cute.LaunchConfig(grid=(5, 3, 1), block=(16, 16, 1)))
+    def scale_shift_2d(x: cute.Tensor, out: cute.Tensor):
+        col = cute.block_idx("x") * cute.block_dim("x") + cute.thread_idx("x")
+        row = cute.block_idx("y") * cute.block_dim("y") + cute.thread_idx("y")
+        value = x[row, col]
+        out[row, col] = value * value + value
+
+    artifact = _run_against_oracle(scale_shift_2d, {"x": oracle.bf16_round(rng.standard_normal((rows, cols)).astype(np.float32)),
+                                                    "out": np.zeros((rows, cols), np.float32)}, {"x": "bf16", "out": "bf16"}, tmp_path)
+    assert match(artifact.ir).mode == "flat"
+
+    # three launch axes onto a rank-3 tensor
+    @cute.kernel(launch=cute.LaunchConfig(grid=(2, 5, 6), block=(8, 2, 1)))
+    def add_3d(a: cute.Tensor, b: cute.Tensor, c: cute.Tensor):
+        x = cute.block_idx("x") * cute.block_dim("x") + cute.thread_idx("x")
+        y = cute.block_idx("y") * cute.block_dim("y") + cute.thread_idx("y")
+        z = cute.block_idx("z")
+        c[z, y, x] = a[z, y, x] + b[z, y, x]
+
+    shape = (6, 10, 16)
+    artifact = _run_against_oracle(add_3d, {"a": rng.uniform(-1, 1, shape).astype(np.float32), "b": rng.uniform(-1, 1, shape).astype(np.float32),
+                                            "c": np.zeros(shape, np.float32)}, {"a": "f32", "b": "f32", "c": "f32"}, tmp_path)
+    assert match(artifact.ir).mode == "flat"
+
+    # a 1-D launch walking a row-major tensor column by column: a permutation, still one shared map
+    @cute.kernel(launch=cute.LaunchConfig(grid=(15, 1, 1), block=(256, 1, 1)))
+    def column_walk(a: cute.Tensor, c: cute.Tensor):
+        i = cute.block_idx("x") * cute.block_dim("x") + cute.thread_idx("x")
+        c[i % 48, i // 48] = cute.math.exp(a[i % 48, i // 48])
+
+    artifact = _run_against_oracle(column_walk, {"a": rng.uniform(-1, 1, (rows, cols)).astype(np.float32), "c": np.zeros((rows, cols), np.float32)},
+                                   {"a": "f32", "c": "f32"}, tmp_path)
+    assert match(artifact.ir).mode == "flat"
+
+    # the transposed write uses two different maps: literal lowering
+    @cute.kernel(launch=cute.LaunchConfig(grid=(5, 3, 1), block=(16, 16, 1)))
+    def transpose_2d(a: cute.Tensor, c: cute.Tensor):
+        col = cute.block_idx("x") * cute.block_dim("x") + cute.thread_idx("x")
+        row = cute.block_idx("y") * cute.block_dim("y") + cute.thread_idx("y")
+        c[col, row] = a[row, col]
+
+    artifact = _run_against_oracle(transpose_2d, {"a": rng.uniform(-1, 1, (rows, cols)).astype(np.float32), "c": np.zeros((cols, rows), np.float32)},
+                                   {"a": "f32", "c": "f32"}, tmp_path)
+    assert match(artifact.ir).mode == "literal"
 
 
 def test_flat_lowering_rank3_digits_and_in_place_update(tmp_path):

@@ -145,9 +145,40 @@ def test_non_bijective_indexing_is_lowered_literally_and_unknown_ops_are_rejecte
         row = cute.block_idx("y") * cute.block_dim("y") + cute.thread_idx("y")
         c[row, col] = a[row, col] + 1.0
 
-    assert match(cute.compile(add_2d_launch, backend="portable", cache_dir=tmp_path).ir).mode == "literal"
-    lowered = cute.compile(add_2d_launch, backend="b200", cache_dir=tmp_path)  # lowering + nvcc need no GPU
+    # a 2-D launch that covers the tensor exactly, every access at the same (row, col): one shared one-to-one map,
+    # so it is an elementwise map whatever the visiting order and takes the vectorised form
+    covered = match(cute.compile(add_2d_launch, backend="portable", cache_dir=tmp_path).ir)
+    assert covered.mode == "flat" and covered.extent == 1024
+
+    # the same launch writing the transposed position: two different maps, lowered literally (one device thread
+    # per traced thread, traced index arithmetic)
+    @cute.kernel(launch=cute.LaunchConfig(grid=(2, 2, 1), block=(16, 16, 1)))
+    def transpose_2d_launch(a: cute.TensorSpec(shape=(32, 32), dtype="f32"), c: cute.TensorSpec(shape=(32, 32), dtype="f32")):
+        col = cute.block_idx("x") * cute.block_dim("x") + cute.thread_idx("x")
+        row = cute.block_idx("y") * cute.block_dim("y") + cute.thread_idx("y")
+        c[col, row] = a[row, col]
+
+    assert match(cute.compile(transpose_2d_launch, backend="portable", cache_dir=tmp_path).ir).mode == "literal"
+    lowered = cute.compile(transpose_2d_launch, backend="b200", cache_dir=tmp_path)  # lowering + nvcc need no GPU
     assert "blockIdx.y" in json.loads(lowered.lowered_module.text)["source"]
+
+    # a grid larger than the tensor (no guard) is not a one-to-one map onto it: literal
+    @cute.kernel(launch=cute.LaunchConfig(grid=(4, 2, 1), block=(16, 16, 1)))
+    def oversized_2d_launch(a: cute.TensorSpec(shape=(32, 32), dtype="f32"), c: cute.TensorSpec(shape=(32, 32), dtype="f32")):
+        col = cute.block_idx("x") * cute.block_dim("x") + cute.thread_idx("x")
+        row = cute.block_idx("y") * cute.block_dim("y") + cute.thread_idx("y")
+        c[row, col] = a[row, col] + 1.0
+
+    assert match(cute.compile(oversized_2d_launch, backend="portable", cache_dir=tmp_path).ir).mode == "literal"
+
+    # a 1-D launch that visits the elements in a permuted order (column-major walk of a row-major tensor) with the
+    # same map for every access is still an elementwise map
+    @cute.kernel(launch=cute.LaunchConfig(grid=(4, 1, 1), block=(256, 1, 1)))
+    def column_major_walk(a: cute.TensorSpec(shape=(32, 32), dtype="f32"), c: cute.TensorSpec(shape=(32, 32), dtype="f32")):
+        i = cute.block_idx("x") * cute.block_dim("x") + cute.thread_idx("x")
+        c[i % 32, i // 32] = a[i % 32, i // 32] * 2.0
+
+    assert match(cute.compile(column_major_walk, backend="portable", cache_dir=tmp_path).ir).mode == "flat"
 
     @cute.kernel
     def two_ops(a: cute.TensorSpec(shape=(64, 64), dtype="bf16"), b: cute.TensorSpec(shape=(64, 64), dtype="bf16"),
