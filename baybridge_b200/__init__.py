@@ -44,7 +44,6 @@ from .host_values import (
     TensorHandle,
     clone,
     from_dlpack,
-    full,
     tensor,
     zeros,
 )
@@ -52,7 +51,7 @@ from .trace import ReductionOp, ScalarValue, TensorValue
 from .dsl import (
     KernelDefinition,
     KernelLaunch,
-    acos, arch, asin, atan, atan2, attention, block_dim, block_idx, ceil, copy, cos, dim, erf, exp, exp2, floor,
+    acos, arch, asin, empty_like, full, full_like, ones_like, zeros_like, atan, atan2, attention, block_dim, block_idx, ceil, copy, cos, dim, erf, exp, exp2, floor,
     gemm, grid_dim, jit, kernel, lane_id, layernorm, load, log, log10, log2, make_tensor, math, maximum, minimum, mma,
     partition, partition_program, partition_thread, barrier, program_id, rmsnorm, round, rsqrt, sin, sqrt, store, thread_idx, trunc, where,
 )

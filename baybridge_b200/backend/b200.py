@@ -33,7 +33,8 @@ from ..scalar_types import DEVICE_NUMPY, byte_width, normalize_dtype_name
 from . import native
 from .elementwise import THREADS, UNROLL, compile_cubin, render
 from . import reduction as reduction_lowering
-from .matcher import AttentionPlan, ElementwisePlan, GemmPlan, LayerNormPlan, ReductionPlan, RmsNormPlan, adopt, match
+from .matcher import (AttentionPlan, ElementwisePlan, GemmPlan, LayerNormPlan, ReductionBundlePlan, ReductionPlan, RmsNormPlan,
+                      adopt, match)
 
 _thread_state = threading.local()
 
@@ -107,21 +108,28 @@ class B200Backend:
                 mode=rendered.mode, compute=rendered.compute, vector_elements=rendered.vec, extent=plan.extent,
                 entry=rendered.entry, tensor_order=list(rendered.tensor_order), scalar_order=list(rendered.scalar_order),
                 scalar_ctypes=list(rendered.scalar_ctypes), source=rendered.source,
+                gathers=list(rendered.relaxed),  # operands only read element by element: they need no 16-byte alignment
             )
         elif isinstance(plan, ReductionPlan):
-            rendered = reduction_lowering.render(plan, ir)
-            record.update(
-                form=plan.form, op=plan.op, outer=plan.outer, inner=plan.inner, compute=rendered.compute,
-                compute_bytes=rendered.compute_bytes, vector_elements=rendered.vec, entry=f"bb200_reduce_{plan.form}",
-                tensor_order=list(rendered.tensor_order), scalar_order=list(rendered.scalar_order),
-                scalar_ctypes=list(rendered.scalar_ctypes), source=rendered.source,
-            )
+            record.update(self._reduction_record(plan, ir))
+        elif isinstance(plan, ReductionBundlePlan):
+            record.update(entry="bb200_reduce_bundle", parts=[self._reduction_record(part, ir) for part in plan.parts])
         else:
             record.update(asdict(plan))
             record["entry"] = {"gemm": "bb200_gemm_bf16", "rmsnorm": "bb200_rmsnorm", "layernorm": "bb200_layernorm",
                                "attention": "bb200_attention_fwd"}[plan.kind]
         text = json.dumps(record, indent=1, sort_keys=True) + "\n"
         return _lowered_module_type()(backend_name=self.name, entry_point=record["entry"], dialect="b200.plan", text=text)
+
+    @staticmethod
+    def _reduction_record(plan: ReductionPlan, ir: Any) -> dict[str, Any]:
+        rendered = reduction_lowering.render(plan, ir)
+        return dict(
+            form=plan.form, op=plan.op, outer=plan.outer, inner=plan.inner, compute=rendered.compute,
+            compute_bytes=rendered.compute_bytes, vector_elements=rendered.vec, entry=f"bb200_reduce_{plan.form}",
+            tensor_order=list(rendered.tensor_order), scalar_order=list(rendered.scalar_order),
+            scalar_ctypes=list(rendered.scalar_ctypes), source=rendered.source,
+        )
 
     # -- contract: launcher ------------------------------------------------------------------------
     def build_launcher(self, ir: Any, target: Any, lowered_module: Any, lowered_path: Path | None = None) -> Callable[..., None]:
@@ -131,7 +139,8 @@ class B200Backend:
         record = json.loads(lowered_module.text)
         state: dict[str, Any] = {"slots": {}}
         runner = {
-            "elementwise": self._elementwise_runner, "reduction": self._reduction_runner, "gemm": self._gemm_runner,
+            "elementwise": self._elementwise_runner, "reduction": self._reduction_runner,
+            "reduction_bundle": self._reduction_bundle_runner, "gemm": self._gemm_runner,
             "rmsnorm": self._rmsnorm_runner, "layernorm": self._layernorm_runner, "attention": self._attention_runner,
         }[plan.kind](ir, plan, record, state)
         arguments = ir.arguments
@@ -253,6 +262,7 @@ class B200Backend:
         scalar_ctypes = [ctype_of[name] for name in record["scalar_ctypes"]]
         flat = record["mode"] == "flat"
         extent = int(record["extent"])
+        gathers = set(record.get("gathers", ()))
         if flat:
             tile = THREADS * int(record["vector_elements"]) * UNROLL
             grid = native.U3(max(1, -(-extent // tile)), 1, 1)
@@ -274,10 +284,21 @@ class B200Backend:
             values: list[Any] = [ctypes.c_void_p(pointers[position]) for position in tensor_order]
             values += [ctype(scalars[position]) for position, ctype in zip(scalar_order, scalar_ctypes)]
             if flat:
-                aligned = all(pointers[position] % 16 == 0 for position in tensor_order)
+                aligned = all(pointers[position] % 16 == 0 for position in tensor_order if position not in gathers)
                 values += [ctypes.c_size_t(extent), ctypes.c_int(1 if aligned else 0)]
             params = (ctypes.c_void_p * len(values))(*[ctypes.cast(ctypes.byref(v), ctypes.c_void_p) for v in values])
             native.call("bb200_launch", function, grid, block, cluster, 0, stream_handle, params)
+
+        return run
+
+    def _reduction_bundle_runner(self, ir, plan: ReductionBundlePlan, record: dict[str, Any], state: dict[str, Any]):
+        """The folds of a bundle are independent of each other: one after the other on the caller's stream."""
+        runners = [self._reduction_runner(ir, part, part_record, state.setdefault(f"part{index}", {"slots": {}}))
+                   for index, (part, part_record) in enumerate(zip(plan.parts, record["parts"]))]
+
+        def run(pointers: dict[int, int], scalars: dict[int, Any], stream_handle) -> None:
+            for runner in runners:
+                runner(pointers, scalars, stream_handle)
 
         return run
 

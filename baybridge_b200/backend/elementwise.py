@@ -67,6 +67,7 @@ class RenderedKernel:
     scalar_order: tuple[int, ...]  # IR argument positions of the scalar parameters, in order
     scalar_ctypes: tuple[str, ...]
     compute: str
+    relaxed: tuple[int, ...] = ()  # tensor positions only read element by element: no 16-byte alignment needed
 
 
 def _ident(name: str) -> str:
@@ -173,9 +174,29 @@ def _widen(dtype: str, compute: str, expr: str) -> str:
     return f"({_repr_type(dtype, compute)})({expr})"
 
 
+def gather_read(tensor: int, offset: str) -> str:
+    """A read of a small operand that many elements share (kept in cache, so the read-only path is used)."""
+    return f"__ldg(p{tensor} + {offset})"
+
+
+def broadcast_offset(source_shape, target_shape, index: str) -> str:
+    """Offset into a row-major tensor of ``source_shape`` (same rank as ``target_shape``, extent 1 on the broadcast
+    axes) for the element whose linear index in the row-major ``target_shape`` space is ``index``."""
+    terms = []
+    suffix = 1       # elements per step of this axis in the target space
+    stride = 1       # stride of this axis in the source tensor
+    for source_extent, target_extent in zip(reversed(tuple(source_shape)), reversed(tuple(target_shape))):
+        if source_extent != 1:
+            digit = f"(({index} / {suffix}ULL) % {target_extent}ULL)" if suffix > 1 else f"({index} % {target_extent}ULL)"
+            terms.append(f"{digit} * {stride}ULL" if stride > 1 else digit)
+            stride *= source_extent
+        suffix *= target_extent
+    return " + ".join(terms) if terms else "0"
+
+
 def render(plan: ElementwisePlan, ir, entry: str = "bb200_elementwise_kernel") -> RenderedKernel:
     arguments = ir.arguments
-    tensors_used = list(dict.fromkeys(list(plan.inputs) + [store[0] for store in plan.stores]))
+    tensors_used = list(dict.fromkeys(list(plan.inputs) + list(getattr(plan, "gathers", ())) + [store[0] for store in plan.stores]))
     tensor_dtypes = [arguments[position].spec.dtype for position in tensors_used]
     compute = choose_compute_type(plan, tensor_dtypes)
     by_name = {node.name: node for node in plan.nodes}
@@ -214,24 +235,57 @@ def render(plan: ElementwisePlan, ir, entry: str = "bb200_elementwise_kernel") -
         body = ["struct Body {", f"  static constexpr int VEC = {vec};"]
         for param in pointer_params + scalar_params:
             body.append(f"  {param};")
+        # Broadcast operands in the vector path.  A vector step covers VEC consecutive elements of one row when the
+        # innermost extent is a multiple of VEC: an operand that is dense along that axis (a row vector) is then one
+        # 16-byte load at its own offset, and one that is broadcast along it (a column vector) is one value per step.
+        row_like = {}   # node name -> (tensor, ctype, offset expression of the step's first element)
+        per_step = {}
+        for node in plan.nodes:
+            if node.op != "broadcast_input" or node.attrs["target_shape"][-1] % vec:
+                continue
+            tensor, ctype = node.attrs["tensor"], STORAGE_CTYPE[arguments[node.attrs["tensor"]].spec.dtype]
+            offset = broadcast_offset(node.attrs["source_shape"], node.attrs["target_shape"], "base")
+            if node.attrs["source_shape"][-1] == node.attrs["target_shape"][-1]:
+                row_like[node.name] = (tensor, ctype, offset)
+            elif node.attrs["source_shape"][-1] == 1:
+                per_step[node.name] = (tensor, ctype, offset)
         body.append("  struct Regs {")
         for position in plan.inputs:
             body.append(f"    bb200::Pack<{STORAGE_CTYPE[arguments[position].spec.dtype]}, VEC> r{position};")
-        if not plan.inputs:
+        for name, (tensor, ctype, _) in row_like.items():
+            body.append(f"    bb200::Pack<{ctype}, VEC> g{_ident(name)};")
+        for name, (tensor, ctype, _) in per_step.items():
+            body.append(f"    {ctype} g{_ident(name)};")
+        if not plan.inputs and not row_like and not per_step:
             body.append("    int unused;")
         body.append("  };")
         body.append("  __device__ __forceinline__ void load(size_t base, Regs& r) const {")
         for position in plan.inputs:
             ctype = STORAGE_CTYPE[arguments[position].spec.dtype]
             body.append(f"    r.r{position} = bb200::load_stream<{ctype}, VEC>(p{position} + base);")
+        for name, (tensor, ctype, offset) in row_like.items():
+            body.append(f"    r.g{_ident(name)} = bb200::load_shared_operand<{ctype}, VEC>(p{tensor} + {offset});")
+        for name, (tensor, ctype, offset) in per_step.items():
+            body.append(f"    r.g{_ident(name)} = __ldg(p{tensor} + {offset});")
         body.append("  }")
 
-        def element_code(read, write, indent: str) -> list[str]:
+        def element_code(read, write, indent: str, index: str, staged: bool) -> list[str]:
+            """``index``: C expression of the element's linear index (only broadcast operands need it); ``staged``: the
+            vector path, where row-like and per-step broadcast operands were fetched by ``load``."""
             code = []
             for node in plan.nodes:
                 ident, rtype = _ident(node.name), _repr_type(node.dtype, compute)
-                if node.op == "input":
+                if staged and node.name in row_like:
+                    code.append(f"{indent}const {rtype} {ident} = {_widen(node.dtype, compute, f'r.g{ident}.v[j]')};")
+                elif staged and node.name in per_step:
+                    code.append(f"{indent}const {rtype} {ident} = {_widen(node.dtype, compute, f'r.g{ident}')};")
+                elif node.op == "input":
                     code.append(f"{indent}const {rtype} {ident} = {_widen(node.dtype, compute, read(node.attrs['tensor']))};")
+                elif node.op == "uniform_input":
+                    code.append(f"{indent}const {rtype} {ident} = {_widen(node.dtype, compute, gather_read(node.attrs['tensor'], str(int(node.attrs['offset']))))};")
+                elif node.op == "broadcast_input":
+                    offset = broadcast_offset(node.attrs["source_shape"], node.attrs["target_shape"], index)
+                    code.append(f"{indent}const {rtype} {ident} = {_widen(node.dtype, compute, gather_read(node.attrs['tensor'], offset))};")
                 elif node.op == "scalar_arg":
                     code.append(f"{indent}const {rtype} {ident} = {scalar_value(node)};")
                 else:
@@ -246,14 +300,14 @@ def render(plan: ElementwisePlan, ir, entry: str = "bb200_elementwise_kernel") -
             body.append(f"    bb200::Pack<{STORAGE_CTYPE[arguments[position].spec.dtype]}, VEC> o{position};")
         body.append("#pragma unroll")
         body.append("    for (int j = 0; j < VEC; ++j) {")
-        body.extend(element_code(lambda p: f"r.r{p}.v[j]", lambda p: f"o{p}.v[j]", "      "))
+        body.extend(element_code(lambda p: f"r.r{p}.v[j]", lambda p: f"o{p}.v[j]", "      ", "(base + j)", True))
         body.append("    }")
         for position, _ in plan.stores:
             ctype = STORAGE_CTYPE[arguments[position].spec.dtype]
             body.append(f"    bb200::store_stream<{ctype}, VEC>(p{position} + base, o{position});")
         body.append("  }")
         body.append("  __device__ __forceinline__ void scalar(size_t i) const {")
-        body.extend(element_code(lambda p: f"p{p}[i]", lambda p: f"p{p}[i]", "    "))
+        body.extend(element_code(lambda p: f"p{p}[i]", lambda p: f"p{p}[i]", "    ", "i", False))
         body.append("  }")
         body.append("};")
         lines.extend(body)
@@ -266,7 +320,10 @@ def render(plan: ElementwisePlan, ir, entry: str = "bb200_elementwise_kernel") -
             f"  bb200::flat_map<{UNROLL}>(body, n, vector_ok != 0);",
             "}",
         ]
-        return RenderedKernel("\n".join(lines) + "\n", entry, "flat", vec, tuple(tensors_used), scalar_order, scalar_ctypes, compute)
+        vector_read = {entry_[0] for entry_ in row_like.values()}
+        relaxed = tuple(position for position in getattr(plan, "gathers", ()) if position not in vector_read)
+        return RenderedKernel("\n".join(lines) + "\n", entry, "flat", vec, tuple(tensors_used), scalar_order, scalar_ctypes, compute,
+                              relaxed)
 
     # ---- literal mode: one device thread per traced thread, traced index arithmetic, guarded accesses
     signature = ", ".join(pointer_params + scalar_params)

@@ -150,6 +150,9 @@ class ElementwisePlan:
     scalars: tuple[int, ...]
     extent: int
     kind: str = "elementwise"
+    # flat mode only: tensor positions read through ``uniform_input`` nodes (one fixed element, e.g. a one-element
+    # tensor used as a scalar) or ``broadcast_input`` nodes (a smaller tensor broadcast over the element space)
+    gathers: tuple[int, ...] = ()
 
 
 @dataclass(frozen=True)
@@ -173,6 +176,15 @@ class ReductionPlan:
     source_shape: tuple[int, ...]
     dtype: str
     kind: str = "reduction"
+
+
+@dataclass(frozen=True)
+class ReductionBundlePlan:
+    """Several folds in one kernel body (e.g. the total, the row folds and the column folds of one loaded tensor):
+    each part is an independent ``ReductionPlan`` over the kernel's arguments, run one after the other."""
+
+    parts: tuple[ReductionPlan, ...]
+    kind: str = "reduction_bundle"
 
 
 # ---------------------------------------------------------------------------------------------
@@ -595,8 +607,9 @@ class _Elementwise:
                 offset = None
                 break
             offset = offset.plus(part.scaled(step))
+        uniform = is_load and not masked and offset is not None and offset.is_const and 0 <= offset.const < spec.numel
         record = {
-            "kind": "load" if is_load else "store", "tensor": self.positions[tensor], "indices": tuple(indices),
+            "kind": ("uniform" if uniform else "load") if is_load else "store", "tensor": self.positions[tensor], "indices": tuple(indices),
             "predicate": predicate, "fallback": fallback, "value": value, "offset": offset, "numel": spec.numel,
             "result": op.outputs[0] if is_load else None, "dtype": spec.dtype, "shape": spec.shape, "stride": stride,
         }
@@ -627,8 +640,14 @@ class _Elementwise:
             raise _unsupported("the kernel body stores nothing")
         threads = self.launch.threads
         scalars = tuple(position for position, argument in enumerate(self.ir.arguments) if argument.kind == "scalar")
+        # a load at a fixed position (a one-element tensor used as a scalar) is the same value for every element; it
+        # stays out of the index proofs as long as the kernel never writes that tensor
+        written = {access["tensor"] for access in self.accesses if access["kind"] == "store"}
+        if any(access["kind"] == "uniform" and access["tensor"] in written for access in self.accesses):
+            self.not_flat("a fixed-position load from a tensor the kernel also writes")
+        indexed = [access for access in self.accesses if access["kind"] != "uniform"]
         identity = self.flat_ok and self.one_d and all(
-            access["offset"] is not None and access["offset"].equals_linear_id(threads) for access in self.accesses)
+            access["offset"] is not None and access["offset"].equals_linear_id(threads) for access in indexed)
         if identity:
             return self._flat_plan(threads, scalars)
         # Any launch shape: if every access uses the same offset expression and that expression maps the
@@ -643,20 +662,22 @@ class _Elementwise:
         return self._literal_plan(scalars)
 
     def _is_permutation_map(self, threads: int) -> bool:
-        first = self.accesses[0]["offset"]
-        if first is None or any(access["predicate"] is not None for access in self.accesses):
+        accesses = [access for access in self.accesses if access["kind"] != "uniform"]
+        first = accesses[0]["offset"]
+        if first is None or any(access["predicate"] is not None for access in accesses):
             return False
-        if any(access["offset"] is None or not access["offset"].same_as(first) for access in self.accesses):
+        if any(access["offset"] is None or not access["offset"].same_as(first) for access in accesses):
             return False
         if self.one_d:
             extents = {"i": threads}
         else:
             extents = {axis: self.launch.grid[k] * self.launch.block[k] for k, axis in enumerate("xyz")}
         covered = first.bijection_extent(extents)
-        return covered is not None and covered == threads and all(access["numel"] == covered for access in self.accesses)
+        return covered is not None and covered == threads and all(access["numel"] == covered for access in accesses)
 
     def _flat_plan(self, threads: int, scalars: tuple[int, ...]) -> ElementwisePlan:
-        extent = min([threads] + [access["numel"] for access in self.accesses] + ([self.bound] if self.bound is not None else []))
+        extent = min([threads] + [access["numel"] for access in self.accesses if access["kind"] != "uniform"]
+                     + ([self.bound] if self.bound is not None else []))
         current: dict[int, str] = {}  # tensor position → value name that a later load must observe
         alias: dict[str, str] = {}
         inputs: list[int] = []
@@ -664,6 +685,8 @@ class _Elementwise:
         stores: dict[int, str] = {}
         for access in self.accesses:
             tensor = access["tensor"]
+            if access["kind"] == "uniform":
+                continue
             if access["kind"] == "load":
                 if tensor in current:
                     alias[access["result"]] = current[tensor]  # store→load forwarding inside one thread
@@ -690,7 +713,10 @@ class _Elementwise:
             node = self.nodes[name]
             if node.op == "load":
                 access = self.accesses[node.attrs["access"]]
-                nodes.append(Node(name, "input", node.dtype, attrs={"tensor": access["tensor"]}))
+                if access["kind"] == "uniform":
+                    nodes.append(Node(name, "uniform_input", node.dtype, attrs={"tensor": access["tensor"], "offset": access["offset"].const}))
+                else:
+                    nodes.append(Node(name, "input", node.dtype, attrs={"tensor": access["tensor"]}))
             elif node.op == "index":
                 raise _unsupported("a stored value depends on the thread index itself (iota-style bodies are not lowered yet)")
             else:
@@ -699,11 +725,15 @@ class _Elementwise:
             mode="flat", nodes=tuple(nodes), inputs=tuple(inputs),
             stores=tuple((tensor, resolve(value)) for tensor, value in stores.items()),
             scalars=tuple(s for s in scalars if self.ir.arguments[s].name in live), extent=extent,
+            gathers=tuple(dict.fromkeys(node.attrs["tensor"] for node in nodes if node.op == "uniform_input")),
         )
 
     def _literal_plan(self, scalars: tuple[int, ...]) -> ElementwisePlan:
         nodes: list[Node] = []
         stores: list[tuple[Any, ...]] = []
+        for access in self.accesses:
+            if access["kind"] == "uniform":
+                access["kind"] = "load"  # literal lowering treats it like any other indexed load
         for name in self.order:
             node = self.nodes[name]
             if node.op == "load":
@@ -775,7 +805,7 @@ def _match_ssa_elementwise(ir) -> ElementwisePlan:
     inputs: list[int] = []
     stores: dict[int, str] = {}
     shape: tuple[int, ...] | None = None
-    reduction: dict[str, Any] | None = None
+    reductions: list[dict[str, Any]] = []  # in program order; each is completed by the copy/store of its result
     constants: dict[str, Any] = {}
 
     def element_shape(candidate: tuple[int, ...]) -> None:
@@ -783,7 +813,7 @@ def _match_ssa_elementwise(ir) -> ElementwisePlan:
         if shape is None:
             shape = tuple(candidate)
         elif tuple(candidate) != shape:
-            raise _unsupported(f"tensor-SSA operands of different shapes ({shape} vs {tuple(candidate)}; broadcasting is not lowered yet)")
+            raise _unsupported(f"tensor-SSA values of different shapes ({shape} vs {tuple(candidate)}) without an explicit broadcast")
 
     def global_tensor(name: str):
         spec = ir.arguments[positions[name]].spec
@@ -801,32 +831,43 @@ def _match_ssa_elementwise(ir) -> ElementwisePlan:
     for op in ir.operations:
         if op.op in TOPOLOGY_OPS and not (set(op.outputs) & consumed):
             continue  # a topology query whose value is never used has no effect
-        if reduction is not None and op.op not in ("constant", "copy", "store"):
-            raise _unsupported(f"op '{op.op}' after a reduction is not lowered (only the store of the result is)")
+        pending = {record["result"]: record for record in reductions if "dst" not in record}
+        if reductions and not (op.op in ("constant", "make_tensor") or op.op.startswith("reduce_")
+                               or (op.op in ("copy", "store") and op.inputs[0] in pending)
+                               or (op.op == "copy" and op.inputs[0] in positions and op.inputs[1] not in positions)):
+            raise _unsupported(f"op '{op.op}' after a reduction is not lowered (only further reductions and the stores of their results are)")
         if op.op.startswith("reduce_"):
-            if reduction is not None:
-                raise _unsupported("more than one reduction in a kernel is not lowered")
             source, init = op.inputs
+            if source in positions and ir.arguments[positions[source]].kind == "tensor" and source not in known:
+                # a fold taken straight from the kernel argument: an implicit whole-tensor load
+                spec = global_tensor(source)
+                node = f"{source}__elem"
+                if positions[source] not in inputs:
+                    inputs.append(positions[source])
+                    nodes.append(Node(node, "input", spec.dtype, attrs={"tensor": positions[source]}))
+                known[source], dtypes[source], shapes[source] = node, spec.dtype, tuple(spec.shape)
             if source not in known or init not in constants:
                 raise _unsupported("a reduction must consume a tensor value and a literal init value")
             profile = op.attrs.get("reduction_profile", 0)
             source_shape = tuple(shapes.get(source, shape or ()))
             rank = len(source_shape)
             keep = () if profile == 0 else tuple(axis for axis, item in enumerate(profile) if item is None)
-            reduction = {"value": known[source], "op": op.op[len("reduce_"):], "init": constants[init], "keep": keep,
-                         "shape": source_shape, "result": op.outputs[0], "dtype": op.attrs["result"]["dtype"], "rank": rank}
-        elif reduction is not None and op.op == "copy":
+            reductions.append({"value": known[source], "op": op.op[len("reduce_"):], "init": constants[init], "keep": keep,
+                               "shape": source_shape, "result": op.outputs[0], "dtype": op.attrs["result"]["dtype"], "rank": rank})
+        elif op.op == "copy" and op.inputs[0] in pending:
             source, destination = op.inputs
-            if source != reduction["result"] or destination not in positions:
+            reduction = pending[source]
+            if destination not in positions:
                 raise _unsupported("the result of a reduction must be stored straight into a kernel tensor argument")
             spec = global_tensor(destination)
             kept_shape = tuple(reduction["shape"][axis] for axis in reduction["keep"])
             if tuple(spec.shape) != kept_shape or spec.dtype != reduction["dtype"]:
                 raise _unsupported("reduction result and destination differ in shape or dtype")
             reduction["dst"], reduction["dst_offset"] = positions[destination], 0
-        elif reduction is not None and op.op == "store":
+        elif op.op == "store" and op.inputs[0] in pending:
             value, destination, *indices = op.inputs
-            if value != reduction["result"] or destination not in positions or any(i not in constants for i in indices):
+            reduction = pending[value]
+            if destination not in positions or any(i not in constants for i in indices):
                 raise _unsupported("a scalar reduction result must be stored at a constant index of a kernel tensor argument")
             spec = global_tensor(destination)
             if spec.dtype != reduction["dtype"]:
@@ -843,8 +884,8 @@ def _match_ssa_elementwise(ir) -> ElementwisePlan:
             source, destination = op.inputs
             if source in positions and ir.arguments[positions[source]].kind == "tensor":
                 spec = global_tensor(source)
-                element_shape(spec.shape)
                 if destination in positions:  # global → global copy
+                    element_shape(spec.shape)
                     node = f"{source}__elem"
                     if positions[source] not in inputs:
                         inputs.append(positions[source])
@@ -878,6 +919,44 @@ def _match_ssa_elementwise(ir) -> ElementwisePlan:
                     raise _unsupported(f"copy into unknown tensor '{destination}'")
             else:
                 raise _unsupported(f"copy from unknown value '{source}'")
+        elif op.op == "fill":
+            buffer, value = op.inputs
+            if buffer not in register_buffers or value not in known:
+                raise _unsupported("fill of something that is not a register tensor, or with an unknown value")
+            known[buffer] = known[value]
+            dtypes[buffer], shapes[buffer] = register_buffers[buffer]["dtype"], tuple(register_buffers[buffer]["shape"])
+        elif op.op == "broadcast_to":
+            (source,) = op.inputs
+            target = tuple(op.attrs["target_shape"])
+            if source not in known:
+                raise _unsupported(f"broadcast of unknown value '{source}'")
+            origin = next((node for node in nodes if node.name == known[source]), None)
+            if origin is not None and origin.op == "input":
+                source_shape = tuple(shapes[source])
+                padded = (1,) * (len(target) - len(source_shape)) + source_shape
+                if len(padded) != len(target) or any(extent not in (1, wanted) for extent, wanted in zip(padded, target)):
+                    raise _unsupported(f"shape {source_shape} does not broadcast to {target}")
+                nodes.append(Node(op.outputs[0], "broadcast_input", origin.dtype,
+                                  attrs={"tensor": origin.attrs["tensor"], "source_shape": padded, "target_shape": target}))
+                known[op.outputs[0]] = op.outputs[0]
+            elif origin is not None and origin.op in ("constant", "scalar_arg", "uniform_input"):
+                known[op.outputs[0]] = known[source]  # one value for every element already
+            else:
+                raise _unsupported("broadcast of a computed tensor value is not lowered (broadcast the loaded operand instead)")
+            dtypes[op.outputs[0]], shapes[op.outputs[0]] = dtypes[source], target
+        elif op.op == "load":
+            tensor, *indices = op.inputs
+            if tensor not in positions or any(index not in constants for index in indices):
+                raise _unsupported("a scalar load inside a tensor-SSA body must read a kernel tensor at constant indices")
+            spec = global_tensor(tensor)
+            offset = sum(int(constants[index]) * step for index, step in zip(indices, spec.resolved_layout().stride))
+            if not 0 <= offset < spec.numel:
+                raise _unsupported("scalar load out of bounds")
+            if positions[tensor] in stores:
+                raise _unsupported("a scalar load from a tensor the kernel has already stored to")
+            nodes.append(Node(op.outputs[0], "uniform_input", spec.dtype, attrs={"tensor": positions[tensor], "offset": offset}))
+            known[op.outputs[0]] = op.outputs[0]
+            dtypes[op.outputs[0]] = spec.dtype
         elif op.op == "constant":
             dtype = op.attrs["result"]["dtype"]
             nodes.append(Node(op.outputs[0], "constant", dtype, attrs={"value": op.attrs["value"]}))
@@ -901,8 +980,11 @@ def _match_ssa_elementwise(ir) -> ElementwisePlan:
             dtypes[op.outputs[0]], shapes[op.outputs[0]] = result["dtype"], tuple(result["shape"])
         else:
             raise _unsupported(f"op '{op.op}' is not part of a tensor-SSA elementwise body")
-    if reduction is not None:
-        return _reduction_plan(ir, reduction, nodes, inputs)
+    if reductions:
+        if stores:
+            raise _unsupported("whole-tensor stores next to reductions in one kernel are not lowered")
+        parts = tuple(_reduction_plan(ir, record, nodes, inputs) for record in reductions)
+        return parts[0] if len(parts) == 1 else ReductionBundlePlan(parts)
     if not stores or shape is None:
         raise _unsupported("the kernel body stores nothing")
     by_name = {node.name: node for node in nodes}
@@ -911,10 +993,16 @@ def _match_ssa_elementwise(ir) -> ElementwisePlan:
     for dim in shape:
         extent *= dim
     kept = tuple(node for node in nodes if node.name in live)
+    gathers = tuple(dict.fromkeys(node.attrs["tensor"] for node in kept if node.op in ("uniform_input", "broadcast_input")))
+    if set(gathers) & set(stores):
+        raise _unsupported("a broadcast or fixed-position read of a tensor the kernel also writes")
+    dense = tuple(position for position in inputs if f"{ir.arguments[position].name}__elem" in live)
+    for position in dense:  # a loaded tensor used directly must have the element shape
+        if tuple(ir.arguments[position].spec.shape) != shape:
+            raise _unsupported(f"tensor '{ir.arguments[position].name}' of shape {ir.arguments[position].spec.shape} is used without a broadcast to {shape}")
     return ElementwisePlan(
-        mode="flat", nodes=kept, inputs=tuple(position for position in inputs if f"{ir.arguments[position].name}__elem" in live),
-        stores=tuple(stores.items()),
-        scalars=tuple(node.attrs["position"] for node in kept if node.op == "scalar_arg"), extent=extent,
+        mode="flat", nodes=kept, inputs=dense, stores=tuple(stores.items()),
+        scalars=tuple(node.attrs["position"] for node in kept if node.op == "scalar_arg"), extent=extent, gathers=gathers,
     )
 
 
@@ -943,6 +1031,8 @@ def _reduction_plan(ir, reduction: dict[str, Any], nodes: list[Node], inputs: li
     by_name = {node.name: node for node in nodes}
     live = _live_set(by_name, [reduction["value"]], lambda name: name)
     kept_nodes = tuple(node for node in nodes if node.name in live)
+    if any(node.op in ("broadcast_input", "uniform_input") for node in kept_nodes):
+        raise _unsupported("a reduction whose mapped value reads a broadcast or fixed-position operand is not lowered")
     return ReductionPlan(
         nodes=kept_nodes,
         inputs=tuple(p for p in inputs if f"{ir.arguments[p].name}__elem" in live),
@@ -984,6 +1074,8 @@ def match(ir):
         return EXPLICIT[explicit[0].op](ir, explicit[0])
     names = {op.op for op in operations}
     if any(name.startswith("reduce_") for name in names):
+        return _match_ssa_elementwise(ir)
+    if names & {"copy", "make_tensor", "fill"}:  # whole-tensor form (scalar loads at fixed positions are allowed inside it)
         return _match_ssa_elementwise(ir)
     if names & {"load", "store", "masked_load", "masked_store"}:
         return _match_scalar_elementwise(ir)

@@ -95,6 +95,21 @@ template <typename T, int VEC> __device__ __forceinline__ Pack<T, VEC> load_stre
   return out;
 }
 
+// The same access without the streaming hint, for small operands that many elements share (a row vector
+// broadcast over the rows): they should stay in cache.
+template <typename T, int VEC> __device__ __forceinline__ Pack<T, VEC> load_shared_operand(const T* __restrict__ p) {
+  Pack<T, VEC> out;
+  constexpr int BYTES = sizeof(T) * VEC;
+  if constexpr (BYTES % 16 == 0) {
+#pragma unroll
+    for (int i = 0; i < BYTES / 16; ++i) reinterpret_cast<uint4*>(&out)[i] = __ldg(reinterpret_cast<const uint4*>(p) + i);
+  } else {
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) out.v[i] = __ldg(p + i);
+  }
+  return out;
+}
+
 template <typename T, int VEC> __device__ __forceinline__ void store_stream(T* __restrict__ p, const Pack<T, VEC>& in) {
   constexpr int BYTES = sizeof(T) * VEC;
   if constexpr (BYTES % 16 == 0) {

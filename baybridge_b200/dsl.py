@@ -245,6 +245,43 @@ def make_tensor(name: str, shape: tuple[int, ...] | None = None, dtype: str | No
 
 
 # ---------------------------------------------------------------------------------------------
+# register tensors filled with a constant (``frontend.py:2803-2854`` upstream)
+# ---------------------------------------------------------------------------------------------
+def empty_like(value: TensorValue, dtype: str | None = None) -> TensorValue:
+    if not isinstance(value, TensorValue):
+        raise BackendNotImplementedError("empty_like on a host tensor would execute on the host; baybridge_b200 has no CPU runtime")
+    return make_tensor("empty_like", tuple(value.spec.shape), dtype or value.spec.dtype, layout=value.spec.layout,
+                       address_space=AddressSpace.REGISTER)
+
+
+def full_like(value: TensorValue, fill_value: Any, dtype: str | None = None) -> TensorValue:
+    target = empty_like(value, dtype=dtype)
+    target.fill(fill_value)
+    return target
+
+
+def zeros_like(value: TensorValue, dtype: str | None = None) -> TensorValue:
+    return full_like(value, 0, dtype=dtype or value.spec.dtype)
+
+
+def ones_like(value: TensorValue, dtype: str | None = None) -> TensorValue:
+    return full_like(value, 1, dtype=dtype or value.spec.dtype)
+
+
+def full(shape: tuple[int, ...], fill_value: Any, *, dtype: str = "f32") -> TensorValue | RuntimeTensor:
+    """Inside a traced body: a register tensor filled with ``fill_value``.  Outside: a host tensor container."""
+    builder = active_builder()
+    if builder is None:
+        from .host_values import full as host_full
+
+        return host_full(shape, fill_value, dtype=dtype)
+    tensor = builder.make_tensor(f"full_{builder.next_temp_preview()}",
+                                 TensorSpec(tuple(int(extent) for extent in shape), str(dtype), None, AddressSpace.REGISTER))
+    tensor.fill(fill_value)
+    return tensor
+
+
+# ---------------------------------------------------------------------------------------------
 # tile views and barriers
 # ---------------------------------------------------------------------------------------------
 _DEFAULT_AXES = {1: ("x",), 2: ("y", "x"), 3: ("z", "y", "x")}

@@ -46,7 +46,13 @@ def shard_spec(plan: Any, ir: Any) -> ShardSpec:
         if len(shapes) != 1:
             raise ValueError("elementwise sharding needs tensors of one shape")
         shape = next(iter(shapes))
-        return ShardSpec(kind, shape[0], tuple((p, 0) for p in tensors), (), tuple(store[0] for store in plan.stores))
+        # operands read by address arithmetic (a one-element tensor used as a scalar, a row vector broadcast over the
+        # rows) are the same for every shard; one that varies along the split axis would have to be split with it
+        gathers = tuple(getattr(plan, "gathers", ()))
+        for node in plan.nodes:
+            if node.op == "broadcast_input" and node.attrs["source_shape"][0] != 1:
+                raise ValueError("an operand broadcast along the columns varies along the shard axis; this kernel does not shard")
+        return ShardSpec(kind, shape[0], tuple((p, 0) for p in tensors), gathers, tuple(store[0] for store in plan.stores))
     if kind == "rmsnorm":
         full = (plan.gamma,) if plan.gamma_is_full else ()
         shape = ir.arguments[plan.x].spec.shape
@@ -68,6 +74,8 @@ def shard_spec(plan: Any, ir: Any) -> ShardSpec:
         full = tuple(p for p, is_full in ((plan.weight, plan.weight_is_full), (plan.bias, plan.bias_is_full)) if is_full)
         shared = tuple(p for p, is_full in ((plan.weight, plan.weight_is_full), (plan.bias, plan.bias_is_full)) if not is_full)
         return ShardSpec(kind, shape[0], tuple((p, 0) for p in per_row + full), shared, (plan.out, plan.out_resid))
+    if kind == "reduction_bundle":
+        raise ValueError("a bundle of reductions folds over different axes of one tensor; it does not shard")
     if kind == "reduction":
         # only a fold that keeps the leading axis splits without an exchange step (each rank folds its own rows);
         # folds over the leading axis run whole on one GPU

@@ -407,6 +407,10 @@ class IRBuilder:
         self._temp_index += 1
         return self._temp_index
 
+    def next_temp_preview(self) -> int:
+        """The number the next temporary will get, without taking it."""
+        return self._temp_index + 1
+
     def bind_argument(self, name: str, spec: TensorSpec | ScalarSpec) -> TensorValue | ScalarValue:
         is_tensor = isinstance(spec, TensorSpec)
         self.arguments.append(KernelArgument(name=name, kind="tensor" if is_tensor else "scalar", spec=spec))

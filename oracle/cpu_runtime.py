@@ -61,6 +61,8 @@ def round_to_dtype(x: np.ndarray, dtype: str) -> np.ndarray:
         return np.where(np.isfinite(x), rounded, x)
     if dtype in ("i32", "i64", "index", "i8"):
         return np.asarray(x).astype(np.int64).astype(F64)
+    if dtype == "i1":
+        return (np.asarray(x) != 0).astype(F64)
     raise ValueError(dtype)
 
 
@@ -160,6 +162,10 @@ def run_kernel_ir(ir: dict[str, Any], arguments: dict[str, Any]) -> None:
             result = lhs // rhs if op == "floordiv" else lhs % rhs
         elif op == "div":
             result = np.asarray(env[ins[0]], dtype=F64) / np.asarray(env[ins[1]], dtype=F64)
+        elif op in ("bitand", "bitor", "bitxor"):  # Python int semantics (two's complement, unbounded)
+            result = _SCALAR_BINARY[op](_as_index(env[ins[0]]), _as_index(env[ins[1]]))
+        elif op == "bitnot":
+            result = np.invert(_as_index(env[ins[0]]))
         elif op in _SCALAR_BINARY:
             result = _SCALAR_BINARY[op](np.asarray(env[ins[0]]), np.asarray(env[ins[1]]))
         elif op in _UNARY:
@@ -196,6 +202,9 @@ def run_kernel_ir(ir: dict[str, Any], arguments: dict[str, Any]) -> None:
             else:
                 env[ins[1]] = np.array(source, dtype=F64)
             continue
+        elif op == "fill":
+            env[ins[0]] = np.full(np.shape(env[ins[0]]), env[ins[1]], dtype=F64)
+            continue
         elif op == "broadcast_to":
             result = np.broadcast_to(env[ins[0]], attrs["target_shape"])
         elif op.startswith("reduce_"):
@@ -215,6 +224,8 @@ def run_kernel_ir(ir: dict[str, Any], arguments: dict[str, Any]) -> None:
         elif op in _TENSOR_ALIAS:
             base = _TENSOR_ALIAS[op]
             operands = [np.asarray(env[n]) for n in ins]
+            if base in ("bitand", "bitor", "bitxor", "bitnot"):
+                operands = [_as_index(v) for v in operands]
             if base == "div":
                 result = operands[0] / operands[1]
             elif base in _UNARY:

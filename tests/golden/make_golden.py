@@ -64,6 +64,10 @@ def main() -> None:
     cache = Path(tempfile.mkdtemp(prefix="bb_golden_"))
 
     def rt(array: np.ndarray, dtype: str):
+        if dtype in ("i32", "i64", "i8"):
+            return bb.tensor(np.asarray(array, dtype=np.int64).tolist(), dtype=dtype)
+        if dtype == "i1":
+            return bb.tensor(np.asarray(array, dtype=bool).tolist(), dtype=dtype)
         return bb.tensor(np.asarray(array, dtype=np.float64).tolist(), dtype=dtype)
 
     def out_array(t) -> np.ndarray:
@@ -217,6 +221,37 @@ def main() -> None:
     run_case("reduce_col_max_24x64_bf16", zoo.column_max,
              {"src": (bf16_round(rng.uniform(-4, 4, (24, 64)).astype(np.float32)), "bf16"), "dst": (np.zeros(64), "bf16")}, ["dst"])
     run_case("reduce_total_sum_8x96_f32", zoo.total_sum, {"src": (rsrc[:8], "f32"), "dst": (np.zeros(1), "f32")}, ["dst"])
+
+    # integer / predicate / broadcast / factory / bundled-reduction families of upstream's PTX conformance tests
+    rng = np.random.default_rng(1010)
+    ia = rng.integers(-2**31, 2**31 - 1, 256, dtype=np.int64)
+    ib = rng.integers(-2**31, 2**31 - 1, 256, dtype=np.int64)
+    for op in ("and", "or", "xor", "not"):
+        run_case(f"bitwise_{op}_256_i32", zoo.make_indexed_bitwise(op, 256),
+                 {"a": (ia, "i32"), "b": (ib, "i32"), "c": (np.zeros(256), "i32")}, ["c"])
+    fa = rng.uniform(-1, 1, 256).astype(np.float32)
+    fb = rng.uniform(-1, 1, 256).astype(np.float32)
+    run_case("cmpsel_256_f32", zoo.make_indexed_compare_select(256),
+             {"a": (fa, "f32"), "b": (fb, "f32"), "mask": (np.zeros(256), "i1"), "c": (np.zeros(256), "f32")}, ["mask", "c"])
+    run_case("ext1_indexed_256_f32", zoo.make_indexed_extent1_scalar(256),
+             {"src": (fa, "f32"), "alpha": (np.array([0.375], np.float32), "f32"), "dst": (np.zeros(256), "f32")}, ["dst"])
+    m2 = rng.uniform(-1, 1, (6, 40)).astype(np.float32)
+    run_case("ext1_ssa_6x40_f32", zoo.ssa_extent1_scalar,
+             {"a": (m2, "f32"), "alpha": (np.array([-1.5], np.float32), "f32"), "c": (np.zeros((6, 40)), "f32")}, ["c"])
+    run_case("bcast_rowcol_6x40_f32", zoo.ssa_broadcast_row_col,
+             {"a": (m2, "f32"), "row": (rng.uniform(-1, 1, (1, 40)).astype(np.float32), "f32"),
+              "col": (rng.uniform(-1, 1, (6, 1)).astype(np.float32), "f32"), "c": (np.zeros((6, 40)), "f32")}, ["c"])
+    run_case("factory_bundle_6x40_f32", zoo.factory_bundle,
+             {"dst_zero": (np.full((6, 40), 3.0), "f32"), "dst_one": (np.full((6, 40), 3.0), "f32"), "dst_full": (np.full((6, 40), 3.0), "f32")},
+             ["dst_zero", "dst_one", "dst_full"])
+    im = rng.integers(-2**31, 2**31 - 1, (6, 40), dtype=np.int64)
+    run_case("rbundle_xor_6x40_i32", zoo.reduce_bundle_xor,
+             {"src": (im, "i32"), "dst_scalar": (np.zeros(1), "i32"), "dst_rows": (np.zeros(6), "i32"), "dst_cols": (np.zeros(40), "i32")},
+             ["dst_scalar", "dst_rows", "dst_cols"])
+    run_case("rbundle_add_6x40_f32", zoo.reduce_bundle_add,
+             {"src": (m2, "f32"), "dst_scalar": (np.zeros(1), "f32"), "dst_rows": (np.zeros(6), "f32"), "dst_cols": (np.zeros(40), "f32")},
+             ["dst_scalar", "dst_rows", "dst_cols"])
+    run_case("rarg_max_256_i32", zoo.reduce_argument_max, {"src": (ia % 1000, "i32"), "dst": (np.zeros(1), "i32")}, ["dst"])
 
     # ---------------- config 3 (reduced) + upstream's own known-answer GEMMs ---------------------
     rng = np.random.default_rng(1003)

@@ -166,6 +166,105 @@ def build_zoo(cute) -> SimpleNamespace:
 
     zoo.ssa_exp_max = ssa_exp_max
 
+    # ---- integer / predicate families of upstream's PTX conformance tests (tests/test_backend_ptx_exec.py:70-215) ----
+    def make_indexed_bitwise(op: str, n: int, block: int = 64):
+        @cute.kernel(launch=cute.LaunchConfig(grid=((n + block - 1) // block, 1, 1), block=(block, 1, 1)))
+        def indexed_bitwise_kernel(a: cute.Tensor, b: cute.Tensor, c: cute.Tensor):
+            tidx, _, _ = cute.arch.thread_idx()
+            bidx, _, _ = cute.arch.block_idx()
+            bdim, _, _ = cute.arch.block_dim()
+            idx = bidx * bdim + tidx
+            if op == "and":
+                c[idx] = a[idx] & b[idx]
+            elif op == "or":
+                c[idx] = a[idx] | b[idx]
+            elif op == "xor":
+                c[idx] = a[idx] ^ b[idx]
+            else:
+                c[idx] = ~a[idx]
+
+        return indexed_bitwise_kernel
+
+    zoo.make_indexed_bitwise = make_indexed_bitwise
+
+    def make_indexed_compare_select(n: int, block: int = 64):
+        """mask[i] = a[i] < b[i] (an i1 tensor), then c[i] = mask[i] ? a[i] : b[i] read back from that tensor."""
+
+        @cute.kernel(launch=cute.LaunchConfig(grid=((n + block - 1) // block, 1, 1), block=(block, 1, 1)))
+        def indexed_compare_select_kernel(a: cute.Tensor, b: cute.Tensor, mask: cute.Tensor, c: cute.Tensor):
+            tidx, _, _ = cute.arch.thread_idx()
+            bidx, _, _ = cute.arch.block_idx()
+            bdim, _, _ = cute.arch.block_dim()
+            idx = bidx * bdim + tidx
+            mask[idx] = a[idx] < b[idx]
+            c[idx] = cute.where(mask[idx], a[idx], b[idx])
+
+        return indexed_compare_select_kernel
+
+    zoo.make_indexed_compare_select = make_indexed_compare_select
+
+    # a one-element tensor used as a broadcast scalar (tests/test_backend_ptx_exec.py:195-201)
+    def make_indexed_extent1_scalar(n: int, block: int = 64):
+        @cute.kernel(launch=cute.LaunchConfig(grid=((n + block - 1) // block, 1, 1), block=(block, 1, 1)))
+        def indexed_extent1_scalar_kernel(src: cute.Tensor, alpha: cute.Tensor, dst: cute.Tensor):
+            tidx, _, _ = cute.arch.thread_idx()
+            bidx, _, _ = cute.arch.block_idx()
+            bdim, _, _ = cute.arch.block_dim()
+            idx = bidx * bdim + tidx
+            dst[idx] = src[idx] * alpha[0]
+
+        return indexed_extent1_scalar_kernel
+
+    zoo.make_indexed_extent1_scalar = make_indexed_extent1_scalar
+
+    @cute.kernel
+    def ssa_extent1_scalar(a: cute.Tensor, alpha: cute.Tensor, c: cute.Tensor):
+        c.store(a.load() + alpha[0])
+
+    zoo.ssa_extent1_scalar = ssa_extent1_scalar
+
+    # rank-2 broadcasting: a row vector [1, C] and a column vector [R, 1] against [R, C]
+    @cute.kernel
+    def ssa_broadcast_row_col(a: cute.Tensor, row: cute.Tensor, col: cute.Tensor, c: cute.Tensor):
+        c.store((a.load() + row.load()) * col.load())
+
+    zoo.ssa_broadcast_row_col = ssa_broadcast_row_col
+
+    # register tensors filled with constants (tests/test_backend_ptx_exec.py:2382-2393)
+    @cute.kernel
+    def factory_bundle(dst_zero: cute.Tensor, dst_one: cute.Tensor, dst_full: cute.Tensor):
+        dst_zero.store(cute.zeros_like(dst_zero))
+        dst_one.store(cute.ones_like(dst_one))
+        dst_full.store(cute.full_like(dst_full, 7.0))
+
+    zoo.factory_bundle = factory_bundle
+
+    # several folds of one loaded tensor (tests/test_backend_ptx_exec.py:2370-2379)
+    @cute.kernel
+    def reduce_bundle_xor(src: cute.Tensor, dst_scalar: cute.Tensor, dst_rows: cute.Tensor, dst_cols: cute.Tensor):
+        src_vec = src.load()
+        dst_scalar[0] = src_vec.reduce(cute.ReductionOp.XOR, 0, reduction_profile=0)
+        dst_rows.store(src_vec.reduce(cute.ReductionOp.XOR, 0, reduction_profile=(None, 1)))
+        dst_cols.store(src_vec.reduce(cute.ReductionOp.XOR, 0, reduction_profile=(1, None)))
+
+    zoo.reduce_bundle_xor = reduce_bundle_xor
+
+    @cute.kernel
+    def reduce_bundle_add(src: cute.Tensor, dst_scalar: cute.Tensor, dst_rows: cute.Tensor, dst_cols: cute.Tensor):
+        src_vec = src.load()
+        dst_scalar[0] = src_vec.reduce(cute.ReductionOp.ADD, 0.0, reduction_profile=0)
+        dst_rows.store(src_vec.reduce(cute.ReductionOp.ADD, 0.0, reduction_profile=(None, 1)))
+        dst_cols.store(src_vec.reduce(cute.ReductionOp.MAX, -1000.0, reduction_profile=(1, None)))
+
+    zoo.reduce_bundle_add = reduce_bundle_add
+
+    # a fold taken straight from the kernel argument, no explicit load (tests/test_backend_ptx_exec.py:2410-2412)
+    @cute.kernel
+    def reduce_argument_max(src: cute.Tensor, dst: cute.Tensor):
+        dst[0] = src.reduce(cute.ReductionOp.MAX, -99, reduction_profile=0)
+
+    zoo.reduce_argument_max = reduce_argument_max
+
     # ---- reductions (map, then fold) ----------------------------------------------------------------
     @cute.kernel
     def row_sum_of_squares(src: cute.Tensor, dst: cute.Tensor):

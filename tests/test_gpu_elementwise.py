@@ -29,10 +29,19 @@ def _kernel_for(case: str, zoo):
         return zoo.make_fused_mul_add_indexed(int(parts[3])), "fma"
     if case.startswith("c2_fused_ssa"):
         return zoo.fused_mul_add_ssa, "fma"
+    families = {
+        "bitwise": lambda: zoo.make_indexed_bitwise(parts[1], int(parts[2])), "cmpsel": lambda: zoo.make_indexed_compare_select(int(parts[1])),
+        "ext1_indexed": lambda: zoo.make_indexed_extent1_scalar(int(parts[2])), "ext1_ssa": lambda: zoo.ssa_extent1_scalar,
+        "bcast_rowcol": lambda: zoo.ssa_broadcast_row_col, "factory_bundle": lambda: zoo.factory_bundle,
+    }
+    for prefix, make in families.items():
+        if case.startswith(prefix + "_"):
+            return make(), "mul"  # integer ops, selects and single-rounded f32 arithmetic: exact
     raise KeyError(case)
 
 
-ELEMENTWISE_CASES = [c for c in golden_cases() if c.startswith(("bin_", "un_", "clamp_", "masked_", "ssa_", "c2_"))]
+ELEMENTWISE_CASES = [c for c in golden_cases() if c.startswith(
+    ("bin_", "un_", "clamp_", "masked_", "ssa_", "c2_", "bitwise_", "cmpsel_", "ext1_", "bcast_", "factory_"))]
 
 
 @pytest.mark.parametrize("case", ELEMENTWISE_CASES)
@@ -306,6 +315,31 @@ def test_multi_dimensional_launches_flat_when_one_shared_bijection_else_literal(
     artifact = _run_against_oracle(transpose_2d, {"a": rng.uniform(-1, 1, (rows, cols)).astype(np.float32), "c": np.zeros((cols, rows), np.float32)},
                                    {"a": "f32", "c": "f32"}, tmp_path)
     assert match(artifact.ir).mode == "literal"
+
+
+@pytest.mark.parametrize("dtype,shape", [("bf16", (512, 1024)), ("f32", (300, 4096)), ("f32", (37, 50)), ("f16", (64, 24))])
+def test_broadcast_operands_row_vector_column_vector_and_one_element_tensor(dtype, shape, zoo, tmp_path):
+    """(a + row) * col with row [1, C] and col [R, 1], then + alpha[0]: the vector path fetches the row operand with
+    16-byte loads and the column operand once per step; odd widths take the element-by-element path."""
+    import baybridge_b200 as cute
+    from baybridge_b200.backend.matcher import match
+
+    rng = np.random.default_rng(shape[0] * 131 + shape[1])
+    rows, cols = shape
+    host = {
+        "a": oracle.round_to_dtype(rng.uniform(-1, 1, shape), dtype), "row": oracle.round_to_dtype(rng.uniform(-1, 1, (1, cols)), dtype),
+        "col": oracle.round_to_dtype(rng.uniform(-1, 1, (rows, 1)), dtype), "c": np.zeros(shape),
+    }
+    artifact = _run_against_oracle(zoo.ssa_broadcast_row_col, host, {name: dtype for name in host}, tmp_path)
+    plan = match(artifact.ir)
+    assert plan.mode == "flat" and plan.inputs == (0,) and plan.gathers == (1, 2)
+
+    @cute.kernel
+    def scaled_shift(a: cute.Tensor, row: cute.Tensor, alpha: cute.Tensor, c: cute.Tensor):
+        c.store(a.load() * alpha[0] - row.load())
+
+    host = {"a": host["a"], "row": host["row"], "alpha": oracle.round_to_dtype(np.array([0.625]), dtype), "c": np.zeros(shape)}
+    _run_against_oracle(scaled_shift, host, {name: dtype for name in host}, tmp_path)
 
 
 def test_flat_lowering_rank3_digits_and_in_place_update(tmp_path):

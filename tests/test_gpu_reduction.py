@@ -32,6 +32,34 @@ def test_compiled_reductions_match_upstream_vectors(case, kernel, dtype, exact, 
     expect_rounded(to_host(dst), vec["out_dst"], dtype, max_ulp=0 if exact else 1)
 
 
+@pytest.mark.parametrize("case,kernel,dtype", [
+    ("rbundle_xor_6x40_i32", "reduce_bundle_xor", "i32"), ("rbundle_add_6x40_f32", "reduce_bundle_add", "f32"),
+])
+def test_bundled_reductions_match_upstream_vectors(case, kernel, dtype, zoo, tmp_path):
+    """Total, row folds and column folds of one loaded tensor in a single kernel body."""
+    import baybridge_b200 as cute
+
+    vec = golden_vec(case)
+    src = to_device(vec["in_src"], dtype)
+    outputs = {name: device_zeros(vec[f"out_{name}"].shape, dtype) for name in ("dst_scalar", "dst_rows", "dst_cols")}
+    artifact = cute.compile(getattr(zoo, kernel), src, *outputs.values(), backend="b200", cache_dir=tmp_path)
+    assert artifact.ir.to_dict()["operations"] == golden_ir(case)["ir"]["operations"]
+    artifact(src, *outputs.values())
+    for name, tensor in outputs.items():
+        expect_rounded(to_host(tensor), vec[f"out_{name}"], dtype, max_ulp=0 if dtype == "i32" or name == "dst_cols" else 1)
+
+
+def test_reduction_taken_straight_from_the_argument(zoo, tmp_path):
+    import baybridge_b200 as cute
+
+    vec = golden_vec("rarg_max_256_i32")
+    src, dst = to_device(vec["in_src"], "i32"), device_zeros((1,), "i32")
+    artifact = cute.compile(zoo.reduce_argument_max, src, dst, backend="b200", cache_dir=tmp_path)
+    assert artifact.ir.to_dict()["operations"] == golden_ir("rarg_max_256_i32")["ir"]["operations"]
+    artifact(src, dst)
+    assert int(to_host(dst)[0]) == int(vec["out_dst"][0])
+
+
 def _run(kernel, src, dst_shape, dtype, tmp_path):
     import baybridge_b200 as cute
 

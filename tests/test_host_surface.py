@@ -41,7 +41,7 @@ class FakeCudaTensor:
 
 
 def _carriers(ir: dict):
-    names = {"f32": "float32", "bf16": "bfloat16", "f16": "float16"}
+    names = {"f32": "float32", "bf16": "bfloat16", "f16": "float16", "i32": "int32", "i1": "bool"}
     out = []
     for argument in ir["arguments"]:
         if argument["kind"] == "scalar":
@@ -74,6 +74,15 @@ def _zoo_kernel(case: str, zoo):
         return getattr(zoo, "_".join(parts[:-2]))
     if case.startswith(("c5_", "attn_")):
         return zoo.attention_causal if "causal" in case else zoo.attention_full
+    families = {
+        "bitwise": lambda: zoo.make_indexed_bitwise(parts[1], int(parts[2])), "cmpsel": lambda: zoo.make_indexed_compare_select(int(parts[1])),
+        "ext1_indexed": lambda: zoo.make_indexed_extent1_scalar(int(parts[2])), "ext1_ssa": lambda: zoo.ssa_extent1_scalar,
+        "bcast_rowcol": lambda: zoo.ssa_broadcast_row_col, "factory_bundle": lambda: zoo.factory_bundle,
+        "rbundle_xor": lambda: zoo.reduce_bundle_xor, "rbundle_add": lambda: zoo.reduce_bundle_add, "rarg_max": lambda: zoo.reduce_argument_max,
+    }
+    for prefix, make in families.items():
+        if case.startswith(prefix + "_"):
+            return make()
     if case.startswith("api_"):
         return next(getattr(zoo, name) for name in ("api_vector_copy", "api_tile_mma", "api_topology") if case.startswith(name))
     if case.startswith("gemm_"):
@@ -108,6 +117,10 @@ def test_matcher_classifies_every_listing(case):
         assert plan.kind == "rmsnorm"
     elif case.startswith("layernorm_"):
         assert plan.kind == "layernorm"
+    elif case.startswith("rbundle_"):
+        assert plan.kind == "reduction_bundle" and [part.form for part in plan.parts] == ["all", "rows", "cols"]
+    elif case.startswith("rarg_"):
+        assert plan.kind == "reduction" and plan.form == "all"
     elif case.startswith("reduce_"):
         assert plan.kind == "reduction" and plan.form == {"row": "rows", "col": "cols", "total": "all"}[case.split("_")[1]]
     elif case.startswith(("c5_", "attn_")):
