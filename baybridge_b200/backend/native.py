@@ -209,11 +209,18 @@ def device_available() -> bool:
         return False
 
 
+_device_seen = False
+
+
 def require_device() -> None:
     """Fail loudly (no fallback) when launches are impossible on this machine."""
+    global _device_seen
+    if _device_seen:
+        return
     count = ctypes.c_int(0)
     lib = library()
     status = lib.bb200_device_count(ctypes.byref(count))
     if status != 0 or count.value < 1:
         detail = (lib.bb200_last_error() or b"").decode("utf-8", "replace") if status else "no CUDA device is visible"
         raise BackendNotImplementedError(f"the b200 backend needs a CUDA device and driver: {detail}")
+    _device_seen = True

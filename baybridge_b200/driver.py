@@ -258,7 +258,18 @@ def _bind_user_arguments(definition, backend_launcher: Callable[..., Any], bindi
                 value = value[step]
         return value
 
+    parameters = list(signature.parameters.values())
+    positional = [p.name for p in parameters if p.kind in (p.POSITIONAL_ONLY, p.POSITIONAL_OR_KEYWORD)]
+    # the common call — every parameter given positionally, each binding a whole parameter — needs no signature binding
+    direct = (len(positional) == len(parameters) and "stream" not in signature.parameters
+              and all(not binding["path"] and binding["parameter"] in positional for binding in bindings))
+    order = [positional.index(binding["parameter"]) for binding in bindings] if direct else []
+
     def launcher(*args: Any, **kwargs: Any) -> Any:
+        if direct and len(args) == len(positional) and (not kwargs or (len(kwargs) == 1 and "stream" in kwargs)):
+            stream = kwargs.get("stream") if kwargs else None
+            leaves = [normalize_runtime_argument(args[index], stream=stream) for index in order]
+            return backend_launcher(*leaves) if stream is None else backend_launcher(*leaves, stream=stream)
         stream = None if "stream" in signature.parameters else kwargs.pop("stream", None)
         bound = signature.bind_partial(*args, **kwargs).arguments
         if stream is None and "stream" in bound:
