@@ -640,7 +640,7 @@ def main() -> None:
     warmup = max(args.warmup, 3)
     steps = max(args.steps, 1)
     zoo = build_zoo(cute)
-    cache_dir = str(ROOT / "gpurun_out" / f"bench_cache_rank{rank}")
+    cache_dir = str(ROOT / ".bench_cache" / f"rank{rank}")
     workload.setup(torch, cute, zoo, rank, cache_dir)
     flush = torch.empty(L2_FLUSH_BYTES, device="cuda", dtype=torch.uint8) if workload.needs_l2_flush else None
 

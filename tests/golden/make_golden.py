@@ -52,7 +52,7 @@ ROUNDERS = {"f32": lambda x: np.asarray(x, dtype=np.float32), "bf16": bf16_round
 
 
 def main() -> None:
-    upstream_src = sys.argv[1] if len(sys.argv) > 1 else "/root/reference/src"
+    upstream_src = sys.argv[1] if len(sys.argv) > 1 else str(HERE.parents[2] / "reference" / "src")  # a checkout next to this repository
     sys.path.insert(0, upstream_src)
     import baybridge as bb  # noqa: E402  (upstream)
     from baybridge.compiler import _cache_key, _trace_cache_payload  # noqa: E402

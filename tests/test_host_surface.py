@@ -5,6 +5,7 @@ test_interop.py, test_backend_ptx_exec.py's fake-DLPack launcher tests) for the 
 """
 
 import json
+import os
 import sys
 from pathlib import Path
 
@@ -319,7 +320,8 @@ def test_from_dlpack_handle_fields():
         cute.from_dlpack(object())
 
 
-REFERENCE_SRC = Path("/root/reference/src")
+# an upstream checkout next to this repository (or wherever BAYBRIDGE_UPSTREAM_SRC points)
+REFERENCE_SRC = Path(os.environ.get("BAYBRIDGE_UPSTREAM_SRC") or Path(__file__).resolve().parents[2] / "reference" / "src")
 
 
 @pytest.mark.skipif(not REFERENCE_SRC.exists(), reason="upstream checkout not present on this machine")
