@@ -194,8 +194,21 @@ def broadcast_offset(source_shape, target_shape, index: str) -> str:
     return " + ".join(terms) if terms else "0"
 
 
-def render(plan: ElementwisePlan, ir, entry: str = "bb200_elementwise_kernel") -> RenderedKernel:
+MAX_FANOUT = 8  # destinations per stored tensor in the fan-out form (one per GPU of a box)
+
+
+def render(plan: ElementwisePlan, ir, entry: str = "bb200_elementwise_kernel", fanout: int = 0) -> RenderedKernel:
+    """``fanout == 0``: the ordinary kernel.  ``fanout >= 1`` (flat plans only): every stored tensor is written to
+    ``fanout`` destination buffers at ``shard_offset + i`` instead of to its argument — the form a rank uses to put
+    its output shard straight into every rank's gathered output (peer memory) while it computes.  The pointer
+    parameter of a stored tensor becomes a by-value table of ``MAX_FANOUT`` pointers, and ``size_t shard_offset``
+    follows ``n`` in the signature."""
     arguments = ir.arguments
+    if fanout:
+        if plan.mode != "flat" or not 1 <= fanout <= MAX_FANOUT:
+            raise BackendNotImplementedError("b200: the fan-out form needs a flat elementwise plan and 1..8 destinations")
+        if {store[0] for store in plan.stores} & (set(plan.inputs) | set(getattr(plan, "gathers", ()))):
+            raise BackendNotImplementedError("b200: the fan-out form does not take kernels that update a tensor in place")
     tensors_used = list(dict.fromkeys(list(plan.inputs) + list(getattr(plan, "gathers", ())) + [store[0] for store in plan.stores]))
     tensor_dtypes = [arguments[position].spec.dtype for position in tensors_used]
     compute = choose_compute_type(plan, tensor_dtypes)
@@ -216,7 +229,10 @@ def render(plan: ElementwisePlan, ir, entry: str = "bb200_elementwise_kernel") -
     for position in tensors_used:
         ctype = STORAGE_CTYPE[arguments[position].spec.dtype]
         const = "" if position in written else "const "
-        pointer_params.append(f"{const}{ctype}* __restrict__ p{position}")
+        if fanout and position in written:
+            pointer_params.append(f"bb200::Destinations<{ctype}> q{position}")
+        else:
+            pointer_params.append(f"{const}{ctype}* __restrict__ p{position}")
     scalar_params = [f"{ctype} s{position}" for position, ctype in zip(scalar_order, scalar_ctypes)]
 
     def scalar_value(node: Node) -> str:
@@ -233,7 +249,7 @@ def render(plan: ElementwisePlan, ir, entry: str = "bb200_elementwise_kernel") -
     if plan.mode == "flat":
         vec = 16 // min(STORAGE_BYTES[dtype] for dtype in tensor_dtypes)
         body = ["struct Body {", f"  static constexpr int VEC = {vec};"]
-        for param in pointer_params + scalar_params:
+        for param in pointer_params + scalar_params + (["size_t shard_offset"] if fanout else []):
             body.append(f"  {param};")
         # Broadcast operands in the vector path.  A vector step covers VEC consecutive elements of one row when the
         # innermost extent is a multiple of VEC: an operand that is dense along that axis (a row vector) is then one
@@ -304,15 +320,27 @@ def render(plan: ElementwisePlan, ir, entry: str = "bb200_elementwise_kernel") -
         body.append("    }")
         for position, _ in plan.stores:
             ctype = STORAGE_CTYPE[arguments[position].spec.dtype]
-            body.append(f"    bb200::store_stream<{ctype}, VEC>(p{position} + base, o{position});")
+            if fanout:
+                body.append("#pragma unroll")
+                body.append(f"    for (int d = 0; d < {fanout}; ++d) bb200::store_stream<{ctype}, VEC>(q{position}.p[d] + shard_offset + base, o{position});")
+            else:
+                body.append(f"    bb200::store_stream<{ctype}, VEC>(p{position} + base, o{position});")
         body.append("  }")
         body.append("  __device__ __forceinline__ void scalar(size_t i) const {")
-        body.extend(element_code(lambda p: f"p{p}[i]", lambda p: f"p{p}[i]", "    ", "i", False))
+        if fanout:
+            for position, _ in plan.stores:
+                body.append(f"    {STORAGE_CTYPE[arguments[position].spec.dtype]} w{position};")
+            body.extend(element_code(lambda p: f"p{p}[i]", lambda p: f"w{p}", "    ", "i", False))
+            for position, _ in plan.stores:
+                body.append(f"    for (int d = 0; d < {fanout}; ++d) q{position}.p[d][shard_offset + i] = w{position};")
+        else:
+            body.extend(element_code(lambda p: f"p{p}[i]", lambda p: f"p{p}[i]", "    ", "i", False))
         body.append("  }")
         body.append("};")
         lines.extend(body)
-        signature = ", ".join(pointer_params + scalar_params + ["size_t n", "int vector_ok"])
-        init = ", ".join([f"p{position}" for position in tensors_used] + [f"s{position}" for position in scalar_order])
+        signature = ", ".join(pointer_params + scalar_params + ["size_t n"] + (["size_t shard_offset"] if fanout else []) + ["int vector_ok"])
+        init = ", ".join([(f"q{position}" if fanout and position in written else f"p{position}") for position in tensors_used]
+                         + [f"s{position}" for position in scalar_order] + (["shard_offset"] if fanout else []))
         lines += [
             "",
             f'extern "C" __global__ void __launch_bounds__({THREADS}) {entry}({signature}) {{',

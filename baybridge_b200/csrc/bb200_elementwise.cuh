@@ -127,6 +127,12 @@ template <typename T, int VEC> __device__ __forceinline__ void store_stream(T* _
   }
 }
 
+// Destination table of the fan-out form: a rank's kernel stores its output shard into the gathered output
+// buffer of every rank (its own and, through peer-mapped pointers, the others') instead of one tensor.
+template <typename T> struct Destinations {
+  T* p[8];
+};
+
 // ---- grid mapping ---------------------------------------------------------------------------------
 // Body interface:
 //   static constexpr int VEC;                                 elements per vector step (16 B of the narrowest tensor)

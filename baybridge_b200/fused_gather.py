@@ -1,0 +1,152 @@
+"""Elementwise kernel fused with the all-gather of its output: peer stores instead of a collective.
+
+The multi-GPU form of the hot path is "every rank runs the kernel on its shard, then the output shards are
+all-gathered" (``sharding.py``; upstream itself is single-device).  With NCCL that is two steps: the kernel
+writes its shard to local HBM and the collective then reads it again and pushes it to the peers.  Here the
+kernel does both: a rank's kernel stores every result vector into the gathered output buffer of *every* rank —
+its own through a local pointer, the others' through peer-mapped pointers over NVLink — at
+``rank * shard + i``.  The shard never makes the extra round trip through local HBM, the NVLink transfer
+overlaps the computation vector by vector, and the only collective left is a barrier that tells every rank the
+peers' stores have landed.
+
+Only ordinary stores to peer memory are used (no multicast, no remote loads, no TMA on peer memory).  The
+gathered buffers come from ``torch.distributed._symmetric_memory`` (plumbing: allocation, handle exchange, the
+barrier); the kernel is the generated elementwise kernel in its fan-out form
+(``backend/elementwise.py: render(..., fanout=N)``).
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Any, Sequence
+
+from .backend import native
+from .backend.elementwise import MAX_FANOUT, STORAGE_BYTES, THREADS, UNROLL, compile_cubin, render
+from .backend.matcher import ElementwisePlan, match
+from .driver import _normalize_kernel, trace
+from .errors import BackendNotImplementedError
+from .host_values import normalize_runtime_argument
+
+
+class _DestinationTable(ctypes.Structure):
+    _fields_ = [("p", ctypes.c_void_p * MAX_FANOUT)]
+
+
+class FusedGather:
+    """``fused = FusedGather(kernel, sample_args, destinations={position: [ptr, ...]}, shard_index=r)``.
+
+    ``kernel`` is a ``@kernel`` / ``@jit`` object whose body is a flat elementwise map; ``sample_args`` describe ONE
+    rank's shard (device tensors or shape carriers, scalars as numbers).  For every stored tensor argument
+    ``destinations`` gives the base pointers of the gathered buffers to write (``len == fan-out``, each holding
+    ``fan-out * shard`` elements... or more); the shard lands at element offset ``shard_index * shard_numel``.
+    ``run(*args, stream=)`` takes the same arguments as the ordinary artifact; stored tensor arguments are ignored
+    (their results go to the destinations).  Use ``FusedGather.over_group`` to get destinations from symmetric memory.
+    """
+
+    def __init__(self, kernel: Any, sample_args: Sequence[Any], *, destinations: dict[int, Sequence[int]], shard_index: int,
+                 device: int = 0):
+        definition = _normalize_kernel(kernel)
+        self.ir = trace(definition, tuple(normalize_runtime_argument(arg) for arg in sample_args))
+        plan = match(self.ir)
+        if not isinstance(plan, ElementwisePlan) or plan.mode != "flat":
+            raise BackendNotImplementedError("FusedGather needs a kernel that lowers to a flat elementwise map")
+        self.plan = plan
+        self.stored = [position for position, _ in plan.stores]
+        fanouts = {len(destinations.get(position, ())) for position in self.stored}
+        if len(fanouts) != 1 or not 1 <= next(iter(fanouts)) <= MAX_FANOUT:
+            raise ValueError("every stored tensor needs the same number (1..8) of destination pointers")
+        self.fanout = next(iter(fanouts))
+        self.shard_offset = int(shard_index) * plan.extent
+        rendered = render(plan, self.ir, fanout=self.fanout)
+        self.rendered = rendered
+        self.device = device
+        self._cubin = compile_cubin(rendered.source)
+        self._function = None
+        arguments = self.ir.arguments
+        self._tables = {}
+        aligned = True
+        for position in self.stored:
+            table = _DestinationTable()
+            element = STORAGE_BYTES[arguments[position].spec.dtype]
+            for slot, pointer in enumerate(destinations[position]):
+                table.p[slot] = int(pointer)
+                aligned &= (int(pointer) + self.shard_offset * element) % 16 == 0
+            self._tables[position] = table
+        self._destinations_aligned = aligned
+        tile = THREADS * rendered.vec * UNROLL
+        self._grid = native.U3(max(1, -(-plan.extent // tile)), 1, 1)
+        self._block = native.U3(THREADS, 1, 1)
+        ctype_of = {"double": ctypes.c_double, "int32_t": ctypes.c_int32, "int64_t": ctypes.c_int64}
+        self._scalar_ctypes = [ctype_of[name] for name in rendered.scalar_ctypes]
+
+    # -- construction over a process group ---------------------------------------------------------------
+    @classmethod
+    def over_group(cls, kernel: Any, sample_args: Sequence[Any], *, group=None):
+        """One gathered buffer per stored tensor in symmetric memory (``world * shard`` elements on every rank);
+        returns ``(fused, gathered)`` with ``gathered[position]`` this rank's full buffer as a torch tensor."""
+        import torch
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symmetric
+
+        group = group or dist.group.WORLD
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        if world > MAX_FANOUT:
+            raise BackendNotImplementedError(f"FusedGather fans out to at most {MAX_FANOUT} ranks")
+        definition = _normalize_kernel(kernel)
+        ir = trace(definition, tuple(normalize_runtime_argument(arg) for arg in sample_args))
+        plan = match(ir)
+        if not isinstance(plan, ElementwisePlan) or plan.mode != "flat":
+            raise BackendNotImplementedError("FusedGather needs a kernel that lowers to a flat elementwise map")
+        device = torch.device("cuda", torch.cuda.current_device())
+        names = {"f32": torch.float32, "bf16": torch.bfloat16, "f16": torch.float16, "i32": torch.int32, "i1": torch.bool}
+        gathered, handles, destinations = {}, {}, {}
+        for position, _ in plan.stores:
+            spec = ir.arguments[position].spec
+            buffer = symmetric.empty(world * plan.extent, dtype=names[spec.dtype], device=device)
+            handle = symmetric.rendezvous(buffer, group)
+            gathered[position], handles[position] = buffer, handle
+            destinations[position] = [int(pointer) for pointer in handle.buffer_ptrs]
+        fused = cls(kernel, sample_args, destinations=destinations, shard_index=rank, device=device.index or 0)
+        fused._handles = handles
+        return fused, gathered
+
+    def barrier(self) -> None:
+        """After ``run``: every rank's stores into every gathered buffer are complete and visible (enqueued on the
+        current stream; nothing is read back on the host)."""
+        for handle in getattr(self, "_handles", {}).values():
+            handle.barrier()
+            break  # one barrier orders all earlier stores of the stream
+
+    # -- launch ----------------------------------------------------------------------------------------
+    def run(self, *args: Any, stream: Any = None) -> None:
+        arguments = self.ir.arguments
+        if len(args) != len(arguments):
+            raise TypeError(f"{self.ir.name} expects {len(arguments)} arguments, got {len(args)}")
+        native.require_device()
+        if self._function is None:
+            image = self._cubin.read_bytes()
+            module, function = ctypes.c_void_p(), ctypes.c_void_p()
+            native.call("bb200_init", self.device)
+            native.call("bb200_module_load", image, len(image), ctypes.byref(module))
+            native.call("bb200_get_function", module, self.rendered.entry.encode(), ctypes.byref(function))
+            self._module, self._function = module, function
+        values: list[Any] = []
+        aligned = self._destinations_aligned
+        for position in self.rendered.tensor_order:
+            if position in self._tables:
+                values.append(self._tables[position])
+                continue
+            value = args[position]
+            if not hasattr(value, "data_ptr"):  # anything that is not already a device tensor or handle
+                value = normalize_runtime_argument(value)
+            pointer = int(value.data_ptr() or getattr(value, "raw_address", 0))
+            if not pointer:
+                raise TypeError(f"argument {position} does not expose a device pointer")
+            if position not in self.rendered.relaxed:
+                aligned &= pointer % 16 == 0
+            values.append(ctypes.c_void_p(pointer))
+        for position, ctype in zip(self.rendered.scalar_order, self._scalar_ctypes):
+            value = args[position]
+            values.append(ctype(getattr(value, "value", value)))
+        values += [ctypes.c_size_t(self.plan.extent), ctypes.c_size_t(self.shard_offset), ctypes.c_int(1 if aligned else 0)]
+        params = (ctypes.c_void_p * len(values))(*[ctypes.cast(ctypes.byref(value), ctypes.c_void_p) for value in values])
+        native.call("bb200_launch", self._function, self._grid, self._block, native.U3(1, 1, 1), 0, native.stream_handle(stream), params)

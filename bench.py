@@ -212,6 +212,33 @@ class FusedMulAdd(Workload):
         self.pipeline = HostPipeline(lambda rows: zoo.make_fused_mul_add_indexed(rows), [self.a_host, self.b_host, self.c_host],
                                      chunks=E2E_CHUNKS, cache_dir=cache_dir)
 
+    def fused_gather_ms(self, torch, dist, cute, zoo, barrier) -> float | None:
+        """The same step with the output all-gather fused into the kernel: every rank's kernel stores its shard into the
+        gathered buffer of every rank (peer stores over NVLink), then one barrier.  Checked against the NCCL result."""
+        from baybridge_b200.fused_gather import FusedGather
+
+        fused, gathered = FusedGather.over_group(zoo.make_fused_mul_add_indexed(self.n), [self.a, self.b, self.c])
+        buffer = gathered[2]
+        stream = torch.cuda.current_stream().cuda_stream
+        for _ in range(3):
+            fused.run(self.a, self.b, self.c, stream=stream)
+            fused.barrier()
+        barrier()
+        reference = torch.empty_like(buffer)
+        dist.all_gather_into_tensor(reference, self.c)
+        if not torch.equal(buffer, reference):
+            raise RuntimeError("fused kernel + gather differs from kernel followed by the NCCL all-gather")
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 10
+        barrier()
+        begin.record()
+        for _ in range(reps):
+            fused.run(self.a, self.b, self.c, stream=stream)
+            fused.barrier()
+        end.record()
+        barrier()
+        return begin.elapsed_time(end) / reps
+
     def config(self):
         return {"workload": f"fused_mul_add c=a*b+a bf16 {self.n} (2^{self.n.bit_length() - 1}) elements per GPU (6 B/element), indexed IR form",
                 "l2": "working set 1.6 GB > 126 MB L2, no flush"}
@@ -731,6 +758,22 @@ def main() -> None:
         allgather = {"ms": float(gather_ms.item()), "output_bytes_total": total_bytes,
                      "bus_gbs": total_bytes * (world - 1) / world / (float(gather_ms.item()) * 1e-3) / 1e9,
                      "kernel_plus_allgather_ms": ms_per_step + float(gather_ms.item())}
+
+        fused = None
+        if hasattr(workload, "fused_gather_ms"):
+            try:  # an extra measurement: a box without symmetric-memory support must not lose the bench line
+                fused = workload.fused_gather_ms(torch, dist, cute, zoo, barrier)
+            except Exception as error:  # noqa: BLE001
+                allgather["fused_unavailable"] = f"{type(error).__name__}: {error}"[:200]
+        ready = torch.tensor([0.0 if fused is None else 1.0], device="cuda", dtype=torch.float64)
+        dist.all_reduce(ready, op=dist.ReduceOp.MIN)
+        if float(ready.item()) < 1.0:
+            fused = None
+        if fused is not None:
+            fused_ms = torch.tensor([fused], device="cuda", dtype=torch.float64)
+            dist.all_reduce(fused_ms, op=dist.ReduceOp.MAX)
+            allgather["fused_kernel_and_gather_ms"] = float(fused_ms.item())
+            allgather["fused_speedup_vs_kernel_plus_allgather"] = allgather["kernel_plus_allgather_ms"] / float(fused_ms.item())
 
     if rank == 0:
         if workload.bound == "hbm":

@@ -1,0 +1,59 @@
+"""The elementwise kernel in its fan-out form: a shard's results stored into several gathered buffers at once.
+
+On one GPU the "peers" are two local buffers, which checks the kernel and its launch path (the peer pointers of a
+multi-GPU run come from symmetric memory and are exercised by ``bench.py --gpus N``)."""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+from gpu_util import to_device, to_host
+
+from oracle import cpu_runtime as oracle
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("n,fanout,shard_index", [(4096, 2, 1), (100_000, 3, 2), (1003, 2, 0)])
+def test_fan_out_kernel_writes_every_destination_at_the_shard_offset(n, fanout, shard_index, zoo):
+    import torch
+
+    from baybridge_b200.fused_gather import FusedGather
+
+    rng = np.random.default_rng(n + fanout)
+    a = oracle.bf16_round(rng.standard_normal(n).astype(np.float32))
+    b = oracle.bf16_round(rng.standard_normal(n).astype(np.float32))
+    d_a, d_b = to_device(a, "bf16"), to_device(b, "bf16")
+    unused = torch.zeros(n, device="cuda", dtype=torch.bfloat16)
+    shards = 3
+    buffers = [torch.full((shards * n,), -7.0, device="cuda", dtype=torch.bfloat16) for _ in range(fanout)]
+    fused = FusedGather(zoo.make_fused_mul_add_indexed(n), [d_a, d_b, unused],
+                        destinations={2: [buffer.data_ptr() for buffer in buffers]}, shard_index=shard_index)
+    fused.run(d_a, d_b, unused)
+    torch.cuda.synchronize()
+    expected = oracle.round_to_dtype(a.astype(np.float64) * b + a, "bf16")
+    for buffer in buffers:
+        host = to_host(buffer)
+        assert np.array_equal(host[shard_index * n:(shard_index + 1) * n], expected)
+        untouched = np.delete(host, np.s_[shard_index * n:(shard_index + 1) * n])
+        assert np.all(untouched == -7.0)
+    assert not unused.any()  # the argument itself is not written in this form
+
+
+def test_fan_out_refuses_in_place_and_non_flat_kernels(zoo):
+    import torch
+
+    import baybridge_b200 as cute
+    from baybridge_b200.fused_gather import FusedGather
+
+    t = torch.zeros(256, device="cuda")
+
+    @cute.kernel(launch=cute.LaunchConfig(grid=(1, 1, 1), block=(256, 1, 1)))
+    def in_place(x: cute.Tensor):
+        i = cute.thread_idx("x")
+        x[i] = x[i] + 1.0
+
+    with pytest.raises(cute.BackendNotImplementedError, match="in place"):
+        FusedGather(in_place, [t], destinations={0: [t.data_ptr()]}, shard_index=0)
+    with pytest.raises(cute.BackendNotImplementedError, match="flat elementwise"):
+        FusedGather(zoo.gemm_abt, [torch.zeros(128, 64, device="cuda", dtype=torch.bfloat16)] * 2 + [torch.zeros(128, 128, device="cuda")],
+                    destinations={2: [t.data_ptr()]}, shard_index=0)
