@@ -41,9 +41,20 @@ constexpr int ACC_COLUMNS = BN;            // fp32 accumulator: 128 lanes x 256 
 constexpr int TMEM_COLUMNS = 2 * ACC_COLUMNS;
 constexpr int THREADS = 192;
 constexpr int DEFAULT_GROUP_M = 16;        // rasterisation: tiles advance down this many M-blocks before moving in N
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */ + 4 * 32 * 144 /* epilogue staging */;
 
 enum WaitCode { kWaitEmpty = 101, kWaitFull = 102, kWaitAccEmpty = 103, kWaitAccFull = 104 };
+
+// Where the epilogue writes C.  Ordinarily one buffer holding the [m, n] result.  In the gather form the
+// [m, n] result of this GPU is one row block of a taller matrix that every GPU of the box holds a copy of:
+// the epilogue stores each tile into all `count` copies (its own and, through peer-mapped pointers, the
+// others') at row `row_offset`, so the output all-gather rides along with the GEMM tile by tile.
+constexpr int kMaxDestinations = 8;
+struct Destinations {
+  void* p[kMaxDestinations];
+  int count;
+  int row_offset;
+};
 
 struct TileCoord { int m_block, n_block; };
 
@@ -89,12 +100,85 @@ template <> __device__ __forceinline__ void store_chunk<float>(float* row_ptr, c
   }
 }
 
+// ---- epilogue: one warp's 32 accumulator rows x BN columns to every destination ------------------------
+// tcgen05.ld 32x32b hands each lane one row, so storing straight from registers would make every warp
+// store touch 32 rows with 16 bytes each — tolerable in local HBM (L2 merges sectors), wasteful over NVLink.
+// The rows go through a small shared-memory staging area instead (128 bytes per row and pass, rows 144
+// bytes apart so neither side has bank conflicts) and leave as 128-byte contiguous row segments: eight lanes
+// per row, four rows per store instruction.
+constexpr int STAGE_ROW_BYTES = 144;
+constexpr int STAGING_BYTES_PER_WARP = 32 * STAGE_ROW_BYTES;
+constexpr int STAGING_BYTES = 4 * STAGING_BYTES_PER_WARP;
+
+template <typename OutT>
+__device__ __forceinline__ void store_accumulator_rows(const Destinations& dst, uint32_t taddr, int first_row, int lane, int m, int n,
+                                                       int col0, uint8_t* stage) {
+  constexpr int PASS_COLS = 128 / (int)sizeof(OutT);  // columns that make 128 bytes of output: 64 (bf16) or 32 (f32)
+  const bool rows_aligned = ((size_t)n * sizeof(OutT)) % 16 == 0;
+#pragma unroll 1
+  for (int pass = 0; pass < BN / PASS_COLS; ++pass) {
+    uint32_t acc[PASS_COLS];
+#pragma unroll
+    for (int q = 0; q < PASS_COLS / 32; ++q)
+      tmem_ld_32x32b_x32(taddr + (uint32_t)(pass * PASS_COLS + q * 32), *reinterpret_cast<uint32_t(*)[32]>(&acc[q * 32]));
+    tmem_ld_wait();
+    const int col = col0 + pass * PASS_COLS;
+    if (col >= n) continue;
+    bool fast = rows_aligned && col + PASS_COLS <= n;
+    for (int d = 0; fast && d < dst.count; ++d) fast = (reinterpret_cast<uintptr_t>(dst.p[d]) & 15u) == 0;
+    if (fast) {
+      uint4* mine = reinterpret_cast<uint4*>(stage + lane * STAGE_ROW_BYTES);
+      if constexpr (sizeof(OutT) == 2) {
+#pragma unroll
+        for (int v = 0; v < 8; ++v) {
+          uint32_t packed[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            __nv_bfloat162 pair = __floats2bfloat162_rn(__uint_as_float(acc[v * 8 + 2 * j]), __uint_as_float(acc[v * 8 + 2 * j + 1]));
+            packed[j] = *reinterpret_cast<uint32_t*>(&pair);
+          }
+          mine[v] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        }
+      } else {
+#pragma unroll
+        for (int v = 0; v < 8; ++v) mine[v] = make_uint4(acc[v * 4], acc[v * 4 + 1], acc[v * 4 + 2], acc[v * 4 + 3]);
+      }
+      __syncwarp();
+      const int piece = lane & 7;  // which 16 bytes of the row's 128
+#pragma unroll
+      for (int step = 0; step < 8; ++step) {
+        const int r = step * 4 + (lane >> 3);
+        const uint4 value = *reinterpret_cast<const uint4*>(stage + r * STAGE_ROW_BYTES + piece * 16);
+        const int row = first_row + r;
+        if (row < m) {
+          const size_t byte_offset = ((size_t)(row + dst.row_offset) * n + col) * sizeof(OutT) + (size_t)piece * 16;
+          for (int d = 0; d < dst.count; ++d) *reinterpret_cast<uint4*>(static_cast<uint8_t*>(dst.p[d]) + byte_offset) = value;
+        }
+      }
+      __syncwarp();  // the staging rows are rewritten by the next pass
+    } else {
+      const int row = first_row + lane;
+      if (row < m) {
+#pragma unroll
+        for (int q = 0; q < PASS_COLS / 32; ++q) {
+          const int c = col + q * 32;
+          if (c < n) {
+            const size_t offset = (size_t)(row + dst.row_offset) * n + c;
+            for (int d = 0; d < dst.count; ++d)
+              store_chunk<OutT>(static_cast<OutT*>(dst.p[d]) + offset, *reinterpret_cast<const uint32_t(*)[32]>(&acc[q * 32]), n - c);
+          }
+        }
+      }
+    }
+  }
+}
+
 // B_MN = false: B tile is [BN n-rows, 64 k] (K-major).  B_MN = true: B is stored [K, N]; a stage holds
 // BN/64 sub-tiles of [64 k-rows, 64 n] (MN-major), each 8 KB, consecutive in shared memory.  A_MN is the
 // same for A stored [K, M]: BM/64 sub-tiles of [64 k-rows, 64 m].
 template <typename OutT, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(THREADS, 1)
-gemm_abt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, OutT* __restrict__ c,
+gemm_abt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ Destinations dst,
                 int m, int n, int k, int group_m, int* status_word) {
   extern __shared__ uint8_t smem_raw[];
   // operand tiles need 1024-byte alignment for the 128-byte swizzle pattern
@@ -216,17 +300,10 @@ gemm_abt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld below is warp-collective: leave together or not at all
       if (!ok) break;
       tcgen05_fence_after();
-      const int row = coord.m_block * BM + quadrant * 32 + lane;
       const int col0 = coord.n_block * BN;
       const uint32_t taddr = tmem_base + ((uint32_t)(quadrant * 32) << 16) + (uint32_t)(buffer * ACC_COLUMNS);
-#pragma unroll 1
-      for (int chunk = 0; chunk < BN / 32; ++chunk) {
-        uint32_t acc[32];
-        tmem_ld_32x32b_x32(taddr + (uint32_t)(chunk * 32), acc);
-        tmem_ld_wait();
-        const int col = col0 + chunk * 32;
-        if (row < m && col < n) store_chunk<OutT>(c + (size_t)row * n + col, acc, n - col);
-      }
+      store_accumulator_rows<OutT>(dst, taddr, coord.m_block * BM + quadrant * 32, lane, m, n, col0,
+                                   smem_aligned + STAGES * STAGE_BYTES + 256 + (warp - 2) * STAGING_BYTES_PER_WARP);
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(acc_empty_bar(buffer));
@@ -265,12 +342,12 @@ constexpr int PAIR_STAGES = 6;
 constexpr int PAIR_B_ROWS = BN / 2;                       // rows of the B tile held by each CTA
 constexpr int PAIR_B_BYTES = PAIR_B_ROWS * BK * 2;        // 16 KB
 constexpr int PAIR_STAGE_BYTES = A_TILE_BYTES + PAIR_B_BYTES;
-constexpr int PAIR_SMEM_BYTES = PAIR_STAGES * PAIR_STAGE_BYTES + 1024 + 256;
+constexpr int PAIR_SMEM_BYTES = PAIR_STAGES * PAIR_STAGE_BYTES + 1024 + 256 + STAGING_BYTES;
 constexpr int PAIR_BM = 2 * BM;
 
 template <typename OutT, bool A_MN, bool B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
-gemm_abt_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, OutT* __restrict__ c,
+gemm_abt_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ Destinations dst,
                      int m, int n, int k, int group_m, int* status_word) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_addr(smem_raw) + 1023u) & ~1023u;
@@ -396,17 +473,10 @@ gemm_abt_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tcgen05_fence_after();
-      const int row = coord.m_block * PAIR_BM + (int)cta_rank * BM + quadrant * 32 + lane;
       const int col0 = coord.n_block * BN;
       const uint32_t taddr = tmem_base + ((uint32_t)(quadrant * 32) << 16) + (uint32_t)(buffer * ACC_COLUMNS);
-#pragma unroll 1
-      for (int chunk = 0; chunk < BN / 32; ++chunk) {
-        uint32_t acc[32];
-        tmem_ld_32x32b_x32(taddr + (uint32_t)(chunk * 32), acc);
-        tmem_ld_wait();
-        const int col = col0 + chunk * 32;
-        if (row < m && col < n) store_chunk<OutT>(c + (size_t)row * n + col, acc, n - col);
-      }
+      store_accumulator_rows<OutT>(dst, taddr, coord.m_block * PAIR_BM + (int)cta_rank * BM + quadrant * 32, lane, m, n, col0,
+                                   smem_aligned + PAIR_STAGES * PAIR_STAGE_BYTES + 256 + (warp - 2) * STAGING_BYTES_PER_WARP);
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_remote(acc_empty_bar(buffer), 0);
@@ -495,7 +565,7 @@ bool use_pair_kernel(int m, int n, int sms) {
 }
 
 template <typename OutT, bool A_MN, bool B_MN>
-int launch_pair(const void* a_operand, const void* b, void* c, int m, int n, int k, int device, int sms, cudaStream_t stream) {
+int launch_pair(const void* a_operand, const void* b, const Destinations& dst, int m, int n, int k, int device, int sms, cudaStream_t stream) {
   alignas(64) CUtensorMap map_a, map_b;
   if (int status = A_MN ? encode_tensormap_2d(&map_a, BB200_BF16, a_operand, (uint64_t)k, (uint64_t)m, (uint64_t)m * 2, BK, 64, 3)
                         : encode_tensormap_2d(&map_a, BB200_BF16, a_operand, (uint64_t)m, (uint64_t)k, (uint64_t)k * 2, BM, BK, 3))
@@ -512,7 +582,7 @@ int launch_pair(const void* a_operand, const void* b, void* c, int m, int n, int
   }
   const int tiles = ((m + PAIR_BM - 1) / PAIR_BM) * ((n + BN - 1) / BN);
   const int pairs = tiles < sms / 2 ? tiles : sms / 2;
-  gemm_abt_pair_kernel<OutT, A_MN, B_MN><<<2 * pairs, THREADS, PAIR_SMEM_BYTES, stream>>>(map_a, map_b, static_cast<OutT*>(c), m, n, k, raster_group_m() / 2 > 0 ? raster_group_m() / 2 : 1,
+  gemm_abt_pair_kernel<OutT, A_MN, B_MN><<<2 * pairs, THREADS, PAIR_SMEM_BYTES, stream>>>(map_a, map_b, dst, m, n, k, raster_group_m() / 2 > 0 ? raster_group_m() / 2 : 1,
                                                                              device_status_word());
   return check_launch("gemm pair kernel launch");
 }
@@ -520,7 +590,7 @@ int launch_pair(const void* a_operand, const void* b, void* c, int m, int n, int
 // A_MN: A is stored [k, m] (m contiguous) and consumed as an MN-major operand; otherwise [m, k].
 // B_MN: B is stored [k, n] (n contiguous), MN-major; otherwise [n, k].
 template <typename OutT, bool A_MN, bool B_MN>
-int launch_native(const void* a_operand, const void* b, void* c, int m, int n, int k, cudaStream_t stream) {
+int launch_native(const void* a_operand, const void* b, const Destinations& dst, int m, int n, int k, cudaStream_t stream) {
   alignas(64) CUtensorMap map_a, map_b;
   if (int status = A_MN ? encode_tensormap_2d(&map_a, BB200_BF16, a_operand, (uint64_t)k, (uint64_t)m, (uint64_t)m * 2, BK, 64, 3)
                         : encode_tensormap_2d(&map_a, BB200_BF16, a_operand, (uint64_t)m, (uint64_t)k, (uint64_t)k * 2, BM, BK, 3))
@@ -539,17 +609,17 @@ int launch_native(const void* a_operand, const void* b, void* c, int m, int n, i
   }
   const int sms = cached_sm_count(device);
   if (sms <= 0) return fail(BB200_E_NO_DRIVER, "gemm: could not query the SM count");
-  if (use_pair_kernel(m, n, sms)) return launch_pair<OutT, A_MN, B_MN>(a_operand, b, c, m, n, k, device, sms, stream);
+  if (use_pair_kernel(m, n, sms)) return launch_pair<OutT, A_MN, B_MN>(a_operand, b, dst, m, n, k, device, sms, stream);
   const int tiles = ((m + BM - 1) / BM) * ((n + BN - 1) / BN);
   const int grid = tiles < sms ? tiles : sms;
-  gemm_abt_kernel<OutT, A_MN, B_MN><<<grid, THREADS, SMEM_BYTES, stream>>>(map_a, map_b, static_cast<OutT*>(c), m, n, k, raster_group_m(), device_status_word());
+  gemm_abt_kernel<OutT, A_MN, B_MN><<<grid, THREADS, SMEM_BYTES, stream>>>(map_a, map_b, dst, m, n, k, raster_group_m(), device_status_word());
   return check_launch("gemm kernel launch");
 }
 
-int dispatch_native(const void* a_operand, const void* b, void* c, int m, int n, int k, bool a_is_km, bool b_is_kn,
+int dispatch_native(const void* a_operand, const void* b, const Destinations& dst, int m, int n, int k, bool a_is_km, bool b_is_kn,
                     bb200_dtype c_dtype, cudaStream_t s) {
 #define BB200_GEMM_CASE(OUT, A_MN, B_MN) \
-  if (a_is_km == A_MN && b_is_kn == B_MN) return launch_native<OUT, A_MN, B_MN>(a_operand, b, c, m, n, k, s)
+  if (a_is_km == A_MN && b_is_kn == B_MN) return launch_native<OUT, A_MN, B_MN>(a_operand, b, dst, m, n, k, s)
   if (c_dtype == BB200_BF16) {
     BB200_GEMM_CASE(__nv_bfloat16, false, false);
     BB200_GEMM_CASE(__nv_bfloat16, false, true);
@@ -565,14 +635,22 @@ int dispatch_native(const void* a_operand, const void* b, void* c, int m, int n,
   return fail(BB200_E_INVALID_ARGUMENT, "gemm: unreachable operand layout");
 }
 
+Destinations single_destination(void* c) {
+  Destinations dst = {};
+  dst.p[0] = c;
+  dst.count = 1;
+  dst.row_offset = 0;
+  return dst;
+}
+
 }  // namespace
 }  // namespace bb200
 
 using namespace bb200;
 
-extern "C" int bb200_gemm_bf16(const void* a, const void* b, void* c, int m, int n, int k, int transpose_a, int transpose_b,
-                               bb200_dtype c_dtype, void* stream) {
-  if (!a || !b || !c) return fail(BB200_E_INVALID_ARGUMENT, "gemm: null tensor pointer");
+static int gemm_bf16_into(const void* a, const void* b, const Destinations& destinations, int m, int n, int k, int transpose_a,
+                          int transpose_b, bb200_dtype c_dtype, void* stream) {
+  if (!a || !b) return fail(BB200_E_INVALID_ARGUMENT, "gemm: null tensor pointer");
   if (m <= 0 || n <= 0 || k <= 0) return fail(BB200_E_INVALID_ARGUMENT, "gemm: m, n, k must be > 0 (got %d, %d, %d)", m, n, k);
   if (c_dtype != BB200_BF16 && c_dtype != BB200_F32) return fail(BB200_E_INVALID_ARGUMENT, "gemm: C must be bf16 or f32");
   if (k % 8) return fail(BB200_E_UNSUPPORTED_SHAPE, "gemm: k=%d must be a multiple of 8 (16-byte rows for TMA)", k);
@@ -594,12 +672,33 @@ extern "C" int bb200_gemm_bf16(const void* a, const void* b, void* c, int m, int
     }
     a_operand = workspace;
   }
-  int status = dispatch_native(a_operand, b, c, m, n, k, a_in_place, b_is_kn, c_dtype, s);
+  int status = dispatch_native(a_operand, b, destinations, m, n, k, a_in_place, b_is_kn, c_dtype, s);
   if (workspace) {
     const int freed = check_runtime(cudaFreeAsync(workspace, s), "cudaFreeAsync(gemm workspace)");
     if (!status) status = freed;
   }
   return status;
+}
+
+extern "C" int bb200_gemm_bf16(const void* a, const void* b, void* c, int m, int n, int k, int transpose_a, int transpose_b,
+                               bb200_dtype c_dtype, void* stream) {
+  if (!c) return fail(BB200_E_INVALID_ARGUMENT, "gemm: null tensor pointer");
+  return gemm_bf16_into(a, b, single_destination(c), m, n, k, transpose_a, transpose_b, c_dtype, stream);
+}
+
+extern "C" int bb200_gemm_bf16_gather(const void* a, const void* b, void* const* c_destinations, int destination_count, int row_offset,
+                                      int m, int n, int k, int transpose_a, int transpose_b, bb200_dtype c_dtype, void* stream) {
+  if (!c_destinations || destination_count < 1 || destination_count > kMaxDestinations)
+    return fail(BB200_E_INVALID_ARGUMENT, "gemm (gather): 1..%d destination buffers are needed (got %d)", kMaxDestinations, destination_count);
+  if (row_offset < 0) return fail(BB200_E_INVALID_ARGUMENT, "gemm (gather): row_offset must be >= 0");
+  Destinations destinations = {};
+  for (int d = 0; d < destination_count; ++d) {
+    if (!c_destinations[d]) return fail(BB200_E_INVALID_ARGUMENT, "gemm (gather): destination %d is null", d);
+    destinations.p[d] = c_destinations[d];
+  }
+  destinations.count = destination_count;
+  destinations.row_offset = row_offset;
+  return gemm_bf16_into(a, b, destinations, m, n, k, transpose_a, transpose_b, c_dtype, stream);
 }
 
 // ---- allocation-free variant -------------------------------------------------------------------------
@@ -666,5 +765,5 @@ extern "C" int bb200_gemm_bf16_noalloc(const void* a, const void* b, void* c, in
     if (int status = launch_transpose(a, scratch, k, m, s)) return status;
     a_operand = scratch;
   }
-  return dispatch_native(a_operand, b, c, m, n, k, a_in_place, b_is_kn, c_dtype, s);
+  return dispatch_native(a_operand, b, single_destination(c), m, n, k, a_in_place, b_is_kn, c_dtype, s);
 }

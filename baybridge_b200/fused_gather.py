@@ -27,6 +27,64 @@ from .errors import BackendNotImplementedError
 from .host_values import normalize_runtime_argument
 
 
+class FusedGatherGemm:
+    """The BF16 GEMM with the output all-gather fused into its epilogue (``bb200_gemm_bf16_gather``).
+
+    Every rank multiplies its own row block ``A_r [m, k]`` by the replicated ``B``; the epilogue stores each tile of
+    ``C_r`` into the full ``C [world·m, n]`` of every rank (peer stores over NVLink) at row ``rank·m``.
+    ``FusedGatherGemm.over_group(kernel, sample_args)`` allocates the full ``C`` in symmetric memory; ``run(a, b)``
+    launches; ``barrier()`` makes all ranks' tiles visible."""
+
+    def __init__(self, kernel: Any, sample_args: Sequence[Any], *, destinations: Sequence[int], shard_index: int):
+        definition = _normalize_kernel(kernel)
+        self.ir = trace(definition, tuple(normalize_runtime_argument(arg) for arg in sample_args))
+        plan = match(self.ir)
+        if plan.kind != "gemm":
+            raise BackendNotImplementedError("FusedGatherGemm needs a kernel that lowers to the BF16 GEMM")
+        if not 1 <= len(destinations) <= MAX_FANOUT:
+            raise ValueError("1..8 destination buffers are needed")
+        self.plan = plan
+        self.row_offset = int(shard_index) * plan.m
+        self._table = (ctypes.c_void_p * len(destinations))(*[int(pointer) for pointer in destinations])
+        self._count = len(destinations)
+
+    @classmethod
+    def over_group(cls, kernel: Any, sample_args: Sequence[Any], *, group=None):
+        import torch
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symmetric
+
+        group = group or dist.group.WORLD
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        if world > MAX_FANOUT:
+            raise BackendNotImplementedError(f"FusedGatherGemm fans out to at most {MAX_FANOUT} ranks")
+        probe = cls(kernel, sample_args, destinations=[1], shard_index=0)  # trace + match only
+        plan = probe.plan
+        dtype = torch.bfloat16 if plan.c_dtype == "bf16" else torch.float32
+        device = torch.device("cuda", torch.cuda.current_device())
+        full = symmetric.empty((world * plan.m, plan.n), dtype=dtype, device=device)
+        handle = symmetric.rendezvous(full, group)
+        fused = cls(kernel, sample_args, destinations=[int(pointer) for pointer in handle.buffer_ptrs], shard_index=rank)
+        fused._handle = handle
+        return fused, full
+
+    def barrier(self) -> None:
+        handle = getattr(self, "_handle", None)
+        if handle is not None:
+            handle.barrier()
+
+    def run(self, a: Any, b: Any, *, stream: Any = None) -> None:
+        plan = self.plan
+        native.require_device()
+        pointers = []
+        for value in (a, b):
+            if not hasattr(value, "data_ptr"):
+                value = normalize_runtime_argument(value)
+            pointers.append(ctypes.c_void_p(int(value.data_ptr() or getattr(value, "raw_address", 0))))
+        native.call("bb200_gemm_bf16_gather", pointers[0], pointers[1], self._table, self._count, self.row_offset, plan.m, plan.n, plan.k,
+                    int(plan.transpose_a), int(plan.transpose_b), native.DTYPE_CODES[plan.c_dtype], native.stream_handle(stream))
+
+
 class _DestinationTable(ctypes.Structure):
     _fields_ = [("p", ctypes.c_void_p * MAX_FANOUT)]
 

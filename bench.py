@@ -382,6 +382,32 @@ class Gemm(Workload):
         return (lambda: oracle.gemm(a, b, transpose_b=True)), 2.0 * size**3, f"M=N=K={size} (of 8192), numpy f64 BLAS port"
 
 
+    def fused_gather_ms(self, torch, dist, cute, zoo, barrier) -> float | None:
+        """The same GEMM with the all-gather of C fused into its epilogue (peer stores of every tile), then one barrier."""
+        from baybridge_b200.fused_gather import FusedGatherGemm
+
+        fused, full = FusedGatherGemm.over_group(zoo.gemm_abt, [self.a, self.b, self.c])
+        stream = torch.cuda.current_stream().cuda_stream
+        for _ in range(3):
+            fused.run(self.a, self.b, stream=stream)
+            fused.barrier()
+        barrier()
+        reference = torch.empty_like(full)
+        dist.all_gather_into_tensor(reference, self.c)
+        if not torch.equal(full, reference):
+            raise RuntimeError("fused GEMM + gather differs from the GEMM followed by the NCCL all-gather")
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 10
+        barrier()
+        begin.record()
+        for _ in range(reps):
+            fused.run(self.a, self.b, stream=stream)
+            fused.barrier()
+        end.record()
+        barrier()
+        return begin.elapsed_time(end) / reps
+
+
 class Attention(Workload):
     name, unit, bound = "attention", "TFLOP/s", "tensor"
     batch, heads, seq, dim = 16, 32, 4096, 128

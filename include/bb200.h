@@ -219,6 +219,18 @@ int bb200_gemm_bf16(const void* a, const void* b, void* c, int m, int n, int k, 
 int bb200_gemm_bf16_noalloc(const void* a, const void* b, void* c, int m, int n, int k, int transpose_a,
                             int transpose_b, bb200_dtype c_dtype, void* stream);
 
+/* bb200_gemm_bf16 fused with the all-gather of its output across the GPUs of one box.  Each GPU multiplies its
+ * own row block A_r [m, k] (B is the same everywhere) and the full result is the row-wise concatenation
+ * C = [C_0; C_1; ...] that every GPU wants a copy of.  Instead of writing C_r locally and all-gathering
+ * afterwards, the epilogue stores every tile of C_r into all `destination_count` copies of C — the GPU's own
+ * buffer and, through peer-mapped pointers (CUDA IPC / symmetric memory; ordinary stores over NVLink), the
+ * others' — at row `row_offset` (= r * m).  c_destinations[d] is the base of copy d, a row-major
+ * [rows >= row_offset + m, n] matrix of c_dtype; 1 <= destination_count <= 8.  The caller still needs a
+ * barrier across the GPUs before anyone reads C.  Other arguments as bb200_gemm_bf16.
+ * No upstream counterpart (upstream is single-device: src/baybridge/backends/cuda_driver.py:292-300). */
+int bb200_gemm_bf16_gather(const void* a, const void* b, void* const* c_destinations, int destination_count, int row_offset,
+                           int m, int n, int k, int transpose_a, int transpose_b, bb200_dtype c_dtype, void* stream);
+
 /* Softmax attention forward.  q/out: [batch, seq, heads, head_dim]; k/v: [batch, seq, kv_heads,
  * head_dim] (heads % kv_heads == 0), all bf16 row-major; lse: fp32 [batch, heads, seq]
  * (identical memory layout to [batch, heads, 1, seq]), natural log.  Scale is fixed at

@@ -57,3 +57,29 @@ def test_fan_out_refuses_in_place_and_non_flat_kernels(zoo):
     with pytest.raises(cute.BackendNotImplementedError, match="flat elementwise"):
         FusedGather(zoo.gemm_abt, [torch.zeros(128, 64, device="cuda", dtype=torch.bfloat16)] * 2 + [torch.zeros(128, 128, device="cuda")],
                     destinations={2: [t.data_ptr()]}, shard_index=0)
+
+
+@pytest.mark.parametrize("m,n,k,c_dtype", [(256, 512, 128, "bf16"), (200, 136, 72, "f32"), (2560, 2048, 136, "bf16")])
+def test_gemm_epilogue_stores_its_row_block_into_every_destination(m, n, k, c_dtype, zoo):
+    """bb200_gemm_bf16_gather with two local destination buffers standing in for two GPUs' copies of C."""
+    import torch
+
+    from baybridge_b200.fused_gather import FusedGatherGemm
+
+    rng = np.random.default_rng(m + n + k)
+    a = oracle.bf16_round((rng.standard_normal((m, k)) / np.sqrt(k)).astype(np.float32))
+    b = oracle.bf16_round((rng.standard_normal((n, k)) / np.sqrt(k)).astype(np.float32))
+    d_a, d_b = to_device(a, "bf16"), to_device(b, "bf16")
+    dtype = torch.bfloat16 if c_dtype == "bf16" else torch.float32
+    blocks, mine = 3, 1
+    copies = [torch.full((blocks * m, n), -3.0, device="cuda", dtype=dtype) for _ in range(2)]
+    sample_c = torch.zeros((m, n), device="cuda", dtype=dtype)
+    fused = FusedGatherGemm(zoo.gemm_abt, [d_a, d_b, sample_c], destinations=[c.data_ptr() for c in copies], shard_index=mine)
+    fused.run(d_a, d_b)
+    torch.cuda.synchronize()
+    reference = oracle.gemm(a, b, transpose_b=True)
+    for copy in copies:
+        host = to_host(copy)
+        assert oracle.rel_l2(host[mine * m:(mine + 1) * m], reference) <= (1e-2 if c_dtype == "bf16" else 1e-5)
+        assert np.all(host[:mine * m] == -3.0) and np.all(host[(mine + 1) * m:] == -3.0)
+    assert torch.equal(copies[0], copies[1])
