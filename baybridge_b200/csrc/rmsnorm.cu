@@ -29,10 +29,22 @@ template <int THREADS> __device__ __forceinline__ float block_sum(float v, float
   return warp_sum(total);
 }
 
+// Where the normalised rows go.  Ordinarily one [rows, hidden] tensor.  In the gather form this GPU's rows are a
+// row block of a taller tensor that every GPU of the box holds a copy of: each output vector is stored into all
+// `count` copies (its own and, through peer-mapped pointers, the others') at row `row_offset + row`, so the output
+// all-gather rides along with the kernel.
+constexpr int kMaxDestinations = 8;
+struct RowDestinations {
+  void* p[kMaxDestinations];
+  int count;
+  size_t row_offset;
+};
+
 // VPT = 16-byte vectors per thread held in registers.  CACHED=false re-reads x in the second pass.
-template <typename T, int THREADS, int VPT, bool CACHED>
+// GATHER = false is the single-destination kernel: its store is one instruction with no loop around it.
+template <typename T, int THREADS, int VPT, bool CACHED, bool GATHER>
 __global__ void __launch_bounds__(THREADS)
-rmsnorm_rows(const T* __restrict__ x, const T* __restrict__ gamma, T* __restrict__ out, size_t rows, int hidden,
+rmsnorm_rows(const T* __restrict__ x, const T* __restrict__ gamma, const __grid_constant__ RowDestinations dst, size_t rows, int hidden,
              size_t gamma_row_stride, float epsilon) {
   constexpr int VEC = 16 / sizeof(T);
   __shared__ float scratch[32];
@@ -40,7 +52,7 @@ rmsnorm_rows(const T* __restrict__ x, const T* __restrict__ gamma, T* __restrict
   if (row >= rows) return;
   const T* __restrict__ xr = x + row * (size_t)hidden;
   const T* __restrict__ gr = gamma + row * gamma_row_stride;
-  T* __restrict__ orow = out + row * (size_t)hidden;
+  const size_t out_offset = (dst.row_offset + row) * (size_t)hidden;
   const int nvec = hidden / VEC;
 
   Pack<T, VEC> held[CACHED ? VPT : 1];
@@ -82,7 +94,11 @@ rmsnorm_rows(const T* __restrict__ x, const T* __restrict__ gamma, T* __restrict
 #pragma unroll
     for (int e = 0; e < VEC; ++e)
       o.v[e] = Conv<float, T>::narrow(Conv<float, T>::widen(p.v[e]) * inv_rms * Conv<float, T>::widen(g.v[e]));
-    store_stream<T, VEC>(orow + (size_t)v * VEC, o);
+    if constexpr (GATHER) {
+      for (int d = 0; d < dst.count; ++d) store_stream<T, VEC>(static_cast<T*>(dst.p[d]) + out_offset + (size_t)v * VEC, o);
+    } else {
+      store_stream<T, VEC>(static_cast<T*>(dst.p[0]) + out_offset + (size_t)v * VEC, o);
+    }
   };
   if constexpr (CACHED) {
 #pragma unroll
@@ -96,16 +112,19 @@ rmsnorm_rows(const T* __restrict__ x, const T* __restrict__ gamma, T* __restrict
 }
 
 template <typename T, int THREADS, int VPT, bool CACHED>
-int launch(const void* x, const void* gamma, void* out, size_t rows, size_t hidden, int gamma_is_full, float epsilon,
+int launch(const void* x, const void* gamma, const RowDestinations& out, size_t rows, size_t hidden, int gamma_is_full, float epsilon,
            cudaStream_t stream) {
-  rmsnorm_rows<T, THREADS, VPT, CACHED><<<(unsigned)rows, THREADS, 0, stream>>>(
-      static_cast<const T*>(x), static_cast<const T*>(gamma), static_cast<T*>(out), rows, (int)hidden,
-      gamma_is_full ? hidden : 0, epsilon);
+  if (out.count == 1 && out.row_offset == 0)
+    rmsnorm_rows<T, THREADS, VPT, CACHED, false><<<(unsigned)rows, THREADS, 0, stream>>>(
+        static_cast<const T*>(x), static_cast<const T*>(gamma), out, rows, (int)hidden, gamma_is_full ? hidden : 0, epsilon);
+  else
+    rmsnorm_rows<T, THREADS, VPT, CACHED, true><<<(unsigned)rows, THREADS, 0, stream>>>(
+        static_cast<const T*>(x), static_cast<const T*>(gamma), out, rows, (int)hidden, gamma_is_full ? hidden : 0, epsilon);
   return check_launch("rmsnorm kernel launch");
 }
 
 template <typename T>
-int dispatch(const void* x, const void* gamma, void* out, size_t rows, size_t hidden, int gamma_is_full, float epsilon,
+int dispatch(const void* x, const void* gamma, const RowDestinations& out, size_t rows, size_t hidden, int gamma_is_full, float epsilon,
              cudaStream_t stream) {
   constexpr size_t VEC = 16 / sizeof(T);
   if (hidden % VEC) return fail(BB200_E_UNSUPPORTED_SHAPE, "rmsnorm: hidden=%zu must be a multiple of %zu", hidden, VEC);
@@ -129,14 +148,17 @@ int dispatch(const void* x, const void* gamma, void* out, size_t rows, size_t hi
 
 using namespace bb200;
 
-extern "C" int bb200_rmsnorm(bb200_dtype dtype, const void* x, const void* gamma, void* out, size_t rows, size_t hidden,
-                             int gamma_is_full, float epsilon, void* stream) {
-  if (!x || !gamma || !out) return fail(BB200_E_INVALID_ARGUMENT, "rmsnorm: null tensor pointer");
+static int rmsnorm_into(bb200_dtype dtype, const void* x, const void* gamma, const RowDestinations& out, size_t rows, size_t hidden,
+                        int gamma_is_full, float epsilon, void* stream) {
+  if (!x || !gamma) return fail(BB200_E_INVALID_ARGUMENT, "rmsnorm: null tensor pointer");
   if (rows == 0 || hidden == 0) return fail(BB200_E_INVALID_ARGUMENT, "rmsnorm: rows and hidden must be > 0");
   if (rows > 0x7fffffffu) return fail(BB200_E_UNSUPPORTED_SHAPE, "rmsnorm: more than 2^31-1 rows");
   if (hidden > 0x7fffffffu) return fail(BB200_E_UNSUPPORTED_SHAPE, "rmsnorm: hidden exceeds 2^31-1");
-  if (!aligned16(x) || !aligned16(gamma) || !aligned16(out))
-    return fail(BB200_E_MISALIGNED, "rmsnorm: x, gamma and out must be 16-byte aligned");
+  if (!aligned16(x) || !aligned16(gamma)) return fail(BB200_E_MISALIGNED, "rmsnorm: x, gamma and out must be 16-byte aligned");
+  for (int d = 0; d < out.count; ++d) {
+    if (!out.p[d]) return fail(BB200_E_INVALID_ARGUMENT, "rmsnorm: null tensor pointer");
+    if (!aligned16(out.p[d])) return fail(BB200_E_MISALIGNED, "rmsnorm: x, gamma and out must be 16-byte aligned");
+  }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   switch (dtype) {
     case BB200_BF16: return dispatch<__nv_bfloat16>(x, gamma, out, rows, hidden, gamma_is_full, epsilon, s);
@@ -144,4 +166,25 @@ extern "C" int bb200_rmsnorm(bb200_dtype dtype, const void* x, const void* gamma
     case BB200_F32: return dispatch<float>(x, gamma, out, rows, hidden, gamma_is_full, epsilon, s);
     default: return fail(BB200_E_INVALID_ARGUMENT, "rmsnorm: dtype %d is not bf16/f16/f32", (int)dtype);
   }
+}
+
+extern "C" int bb200_rmsnorm(bb200_dtype dtype, const void* x, const void* gamma, void* out, size_t rows, size_t hidden,
+                             int gamma_is_full, float epsilon, void* stream) {
+  RowDestinations single = {};
+  single.p[0] = out;
+  single.count = 1;
+  single.row_offset = 0;
+  return rmsnorm_into(dtype, x, gamma, single, rows, hidden, gamma_is_full, epsilon, stream);
+}
+
+extern "C" int bb200_rmsnorm_gather(bb200_dtype dtype, const void* x, const void* gamma, void* const* out_destinations,
+                                    int destination_count, size_t row_offset, size_t rows, size_t hidden, int gamma_is_full,
+                                    float epsilon, void* stream) {
+  if (!out_destinations || destination_count < 1 || destination_count > kMaxDestinations)
+    return fail(BB200_E_INVALID_ARGUMENT, "rmsnorm (gather): 1..%d destination buffers are needed (got %d)", kMaxDestinations, destination_count);
+  RowDestinations all = {};
+  for (int d = 0; d < destination_count; ++d) all.p[d] = out_destinations[d];
+  all.count = destination_count;
+  all.row_offset = row_offset;
+  return rmsnorm_into(dtype, x, gamma, all, rows, hidden, gamma_is_full, epsilon, stream);
 }

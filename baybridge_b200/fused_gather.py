@@ -85,6 +85,58 @@ class FusedGatherGemm:
                     int(plan.transpose_a), int(plan.transpose_b), native.DTYPE_CODES[plan.c_dtype], native.stream_handle(stream))
 
 
+class FusedGatherRmsNorm:
+    """RMSNorm with the output all-gather fused into the kernel (``bb200_rmsnorm_gather``): every rank normalises its
+    own rows and stores each output vector into the full ``[world·rows, hidden]`` output of every rank."""
+
+    def __init__(self, kernel: Any, sample_args: Sequence[Any], *, destinations: Sequence[int], shard_index: int):
+        definition = _normalize_kernel(kernel)
+        self.ir = trace(definition, tuple(normalize_runtime_argument(arg) for arg in sample_args))
+        plan = match(self.ir)
+        if plan.kind != "rmsnorm":
+            raise BackendNotImplementedError("FusedGatherRmsNorm needs a kernel that lowers to RMSNorm")
+        if not 1 <= len(destinations) <= MAX_FANOUT:
+            raise ValueError("1..8 destination buffers are needed")
+        self.plan = plan
+        self.row_offset = int(shard_index) * plan.rows
+        self._table = (ctypes.c_void_p * len(destinations))(*[int(pointer) for pointer in destinations])
+        self._count = len(destinations)
+
+    @classmethod
+    def over_group(cls, kernel: Any, sample_args: Sequence[Any], *, group=None):
+        import torch
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symmetric
+
+        group = group or dist.group.WORLD
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        if world > MAX_FANOUT:
+            raise BackendNotImplementedError(f"FusedGatherRmsNorm fans out to at most {MAX_FANOUT} ranks")
+        plan = cls(kernel, sample_args, destinations=[1], shard_index=0).plan  # trace + match only
+        dtype = {"bf16": torch.bfloat16, "f16": torch.float16, "f32": torch.float32}[plan.dtype]
+        full = symmetric.empty((world * plan.rows, plan.hidden), dtype=dtype, device=torch.device("cuda", torch.cuda.current_device()))
+        handle = symmetric.rendezvous(full, group)
+        fused = cls(kernel, sample_args, destinations=[int(pointer) for pointer in handle.buffer_ptrs], shard_index=rank)
+        fused._handle = handle
+        return fused, full
+
+    def barrier(self) -> None:
+        handle = getattr(self, "_handle", None)
+        if handle is not None:
+            handle.barrier()
+
+    def run(self, x: Any, gamma: Any, *, stream: Any = None) -> None:
+        plan = self.plan
+        native.require_device()
+        pointers = []
+        for value in (x, gamma):
+            if not hasattr(value, "data_ptr"):
+                value = normalize_runtime_argument(value)
+            pointers.append(ctypes.c_void_p(int(value.data_ptr() or getattr(value, "raw_address", 0))))
+        native.call("bb200_rmsnorm_gather", native.DTYPE_CODES[plan.dtype], pointers[0], pointers[1], self._table, self._count,
+                    self.row_offset, plan.rows, plan.hidden, 1 if plan.gamma_is_full else 0, plan.epsilon, native.stream_handle(stream))
+
+
 class _DestinationTable(ctypes.Structure):
     _fields_ = [("p", ctypes.c_void_p * MAX_FANOUT)]
 

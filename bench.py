@@ -311,6 +311,31 @@ class RmsNorm(Workload):
         self.pipeline = HostPipeline(lambda rows: zoo.make_rmsnorm(1e-6), [self.x_host, self.out_host, self.w_host],
                                      chunks=E2E_CHUNKS, cache_dir=cache_dir)
 
+    def fused_gather_ms(self, torch, dist, cute, zoo, barrier) -> float | None:
+        """RMSNorm with the all-gather of its output fused into the kernel (peer stores of every vector), then one barrier."""
+        from baybridge_b200.fused_gather import FusedGatherRmsNorm
+
+        fused, full = FusedGatherRmsNorm.over_group(zoo.make_rmsnorm(1e-6), [self.x, self.out, self.w])
+        stream = torch.cuda.current_stream().cuda_stream
+        for _ in range(3):
+            fused.run(self.x, self.w, stream=stream)
+            fused.barrier()
+        barrier()
+        reference = torch.empty_like(full)
+        dist.all_gather_into_tensor(reference, self.out)
+        if not torch.equal(full, reference):
+            raise RuntimeError("fused RMSNorm + gather differs from RMSNorm followed by the NCCL all-gather")
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 10
+        barrier()
+        begin.record()
+        for _ in range(reps):
+            fused.run(self.x, self.w, stream=stream)
+            fused.barrier()
+        end.record()
+        barrier()
+        return begin.elapsed_time(end) / reps
+
     def config(self):
         return {"workload": f"rmsnorm bf16 [{self.rows}, {self.hidden}] per GPU, weight [{self.hidden}], eps 1e-6",
                 "l2": "working set 2.1 GB > 126 MB L2, no flush"}

@@ -180,6 +180,16 @@ int bb200_elementwise_mul_add(bb200_dtype dtype, const void* a, const void* b, v
 int bb200_rmsnorm(bb200_dtype dtype, const void* x, const void* gamma, void* out, size_t rows, size_t hidden,
                   int gamma_is_full, float epsilon, void* stream);
 
+/* bb200_rmsnorm fused with the all-gather of its output across the GPUs of one box: this GPU's [rows, hidden]
+ * result is the row block starting at `row_offset` of a taller tensor of which every GPU holds a copy, and each
+ * normalised vector is stored into all `destination_count` (1..8) copies — out_destinations[d] is the base of
+ * copy d (the GPU's own buffer or a peer-mapped pointer; ordinary 16-byte stores over NVLink).  The caller
+ * still needs a barrier across the GPUs before the gathered tensor is read.  Other arguments as bb200_rmsnorm.
+ * No upstream counterpart (upstream is single-device: src/baybridge/backends/cuda_driver.py:292-300). */
+int bb200_rmsnorm_gather(bb200_dtype dtype, const void* x, const void* gamma, void* const* out_destinations,
+                         int destination_count, size_t row_offset, size_t rows, size_t hidden, int gamma_is_full,
+                         float epsilon, void* stream);
+
 /* mixed = x + residual; out_resid = mixed; out = (mixed - mean) / sqrt(var + eps) * weight + bias, with mean and
  * (biased) variance over the last axis in fp32 and one rounding per output.  x/residual/out/out_resid: [rows, hidden]
  * row-major; weight and bias: [hidden] (…_is_full = 0) or [rows, hidden] (…_is_full = 1).  dtype bf16 / f16 / f32;

@@ -83,3 +83,28 @@ def test_gemm_epilogue_stores_its_row_block_into_every_destination(m, n, k, c_dt
         assert oracle.rel_l2(host[mine * m:(mine + 1) * m], reference) <= (1e-2 if c_dtype == "bf16" else 1e-5)
         assert np.all(host[:mine * m] == -3.0) and np.all(host[(mine + 1) * m:] == -3.0)
     assert torch.equal(copies[0], copies[1])
+
+
+@pytest.mark.parametrize("dtype,rows,hidden", [("bf16", 16, 8192), ("f32", 7, 1020), ("f16", 33, 2048)])
+def test_rmsnorm_stores_its_rows_into_every_destination(dtype, rows, hidden, zoo):
+    import torch
+
+    from baybridge_b200.fused_gather import FusedGatherRmsNorm
+
+    rng = np.random.default_rng(rows + hidden)
+    x = oracle.round_to_dtype(rng.standard_normal((rows, hidden)), dtype)
+    w = oracle.round_to_dtype(1 + 0.1 * rng.standard_normal(hidden), dtype)
+    d_x, d_w = to_device(x, dtype), to_device(w, dtype)
+    torch_dtype = {"bf16": torch.bfloat16, "f16": torch.float16, "f32": torch.float32}[dtype]
+    blocks, mine = 3, 2
+    copies = [torch.full((blocks * rows, hidden), -3.0, device="cuda", dtype=torch_dtype) for _ in range(2)]
+    sample_out = torch.zeros((rows, hidden), device="cuda", dtype=torch_dtype)
+    fused = FusedGatherRmsNorm(zoo.make_rmsnorm(1e-6), [d_x, sample_out, d_w], destinations=[c.data_ptr() for c in copies], shard_index=mine)
+    fused.run(d_x, d_w)
+    torch.cuda.synchronize()
+    reference = oracle.rmsnorm(x, w, 1e-6)
+    for copy in copies:
+        host = to_host(copy)
+        assert oracle.rel_l2(host[mine * rows:], reference) <= (2e-3 if dtype != "f32" else 2e-6)
+        assert np.all(host[:mine * rows] == -3.0)
+    assert torch.equal(copies[0], copies[1])
