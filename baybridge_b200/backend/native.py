@@ -150,6 +150,7 @@ PROTOTYPES: dict[str, list[Any]] = {
     "bb200_rmsnorm_gather": [I, P, P, ctypes.POINTER(P), I, Z, Z, Z, I, ctypes.c_float, P],
     "bb200_gemm_bf16_gather": [P, P, ctypes.POINTER(P), I, I, I, I, I, I, I, I, P],
     "bb200_attention_fwd": [P, P, P, P, P, I, I, I, I, I, I, P],
+    "bb200_attention_fwd_gather": [P, P, P, ctypes.POINTER(P), ctypes.POINTER(P), I, I, I, I, I, I, I, I, P],
     "bb200_take_device_status": [P, ctypes.POINTER(I)],
 }
 

@@ -69,10 +69,25 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
   return d;
 }
 
-template <int D, bool CAUSAL>
+// Where out and lse go.  Ordinarily one pair of tensors.  In the gather form this GPU's batches are a block of
+// a larger batch of which every GPU of the box holds a copy: out rows and lse values are stored into all `count`
+// copies (its own and, through peer-mapped pointers, the others') at batch `batch_offset + b`.
+constexpr int kMaxDestinations = 8;
+struct OutputDestinations {
+  void* out[kMaxDestinations];
+  float* lse[kMaxDestinations];
+  int count;
+  int batch_offset;
+};
+
+// GATHER = false: the single-destination kernel; each thread stores its own output row straight from registers.
+// GATHER = true: rows are staged in the (by then unused) shared memory of the tile's Q and leave as whole
+// contiguous rows, sixteen (or eight) lanes per row, into every destination — 16-byte pieces of 32 different rows
+// per store instruction would waste most of an NVLink packet.
+template <int D, bool CAUSAL, bool GATHER>
 __global__ void __launch_bounds__(THREADS, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out, float* __restrict__ lse,
+                const __grid_constant__ CUtensorMap map_v, const __grid_constant__ OutputDestinations dst,
                 int seq, int heads, int kv_heads, float scale_log2e, int* status_word) {
   using L = Smem<D>;
   extern __shared__ uint8_t smem_raw[];
@@ -331,13 +346,38 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     if (ok && my_blocks > 0) {
       tcgen05_fence_after();
       const float inv = row_sum > 0.0f ? 1.0f / row_sum : 0.0f;
-      __nv_bfloat16* dst = out + (((size_t)batch * seq + query) * heads + head) * D;
+      const size_t out_batch = (size_t)(dst.batch_offset + batch);
+      if constexpr (!GATHER) {
+        __nv_bfloat16* row_out = static_cast<__nv_bfloat16*>(dst.out[0]) + ((out_batch * seq + query) * heads + head) * D;
 #pragma unroll
-      for (int chunk = 0; chunk < D / 32; ++chunk) {
-        uint32_t acc[32];
-        tmem_ld_32x32b_x32(o_addr + (uint32_t)(chunk * 32), acc);
-        tmem_ld_wait();
-        if (query < seq) {
+        for (int chunk = 0; chunk < D / 32; ++chunk) {
+          uint32_t acc[32];
+          tmem_ld_32x32b_x32(o_addr + (uint32_t)(chunk * 32), acc);
+          tmem_ld_wait();
+          if (query < seq) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              uint32_t word[4];
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const __nv_bfloat162 pair2 = __floats2bfloat162_rn(__uint_as_float(acc[v * 8 + 2 * i]) * inv,
+                                                                   __uint_as_float(acc[v * 8 + 2 * i + 1]) * inv);
+                word[i] = *reinterpret_cast<const uint32_t*>(&pair2);
+              }
+              *reinterpret_cast<uint4*>(row_out + chunk * 32 + v * 8) = make_uint4(word[0], word[1], word[2], word[3]);
+            }
+          }
+        }
+      } else {
+        // stage this warp's 32 rows in its quarter of the tile's Q buffer (all Q·K^T of this tile are complete);
+        // 16-byte pieces are XOR-swizzled by row so that neither the row-wise writes nor the piece-wise reads conflict
+        constexpr int ROW_BYTES = D * 2, PIECES = ROW_BYTES / 16;
+        uint8_t* stage = aligned + L::Q_OFF + tile * L::Q_BYTES + quadrant * 32 * ROW_BYTES;
+#pragma unroll
+        for (int chunk = 0; chunk < D / 32; ++chunk) {
+          uint32_t acc[32];
+          tmem_ld_32x32b_x32(o_addr + (uint32_t)(chunk * 32), acc);
+          tmem_ld_wait();
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
             uint32_t word[4];
@@ -347,14 +387,35 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
                                                                  __uint_as_float(acc[v * 8 + 2 * i + 1]) * inv);
               word[i] = *reinterpret_cast<const uint32_t*>(&pair2);
             }
-            *reinterpret_cast<uint4*>(dst + chunk * 32 + v * 8) = make_uint4(word[0], word[1], word[2], word[3]);
+            const int piece = chunk * 4 + v;
+            *reinterpret_cast<uint4*>(stage + lane * ROW_BYTES + ((piece ^ (lane & (PIECES - 1))) * 16)) =
+                make_uint4(word[0], word[1], word[2], word[3]);
+          }
+        }
+        __syncwarp();
+        constexpr int ROWS_PER_STEP = 32 / PIECES;
+        const int piece = lane % PIECES;
+#pragma unroll
+        for (int step = 0; step < PIECES; ++step) {
+          const int r = step * ROWS_PER_STEP + lane / PIECES;
+          const uint4 value = *reinterpret_cast<const uint4*>(stage + r * ROW_BYTES + ((piece ^ (r & (PIECES - 1))) * 16));
+          const int row_query = q0 + quadrant * 32 + r;
+          if (row_query < seq) {
+            const size_t offset = (((out_batch * seq + row_query) * heads + head) * D) * 2 + (size_t)piece * 16;
+            for (int d = 0; d < dst.count; ++d) *reinterpret_cast<uint4*>(static_cast<uint8_t*>(dst.out[d]) + offset) = value;
           }
         }
       }
       // natural-log sum of exponentials of the scaled scores
-      if (query < seq)
-        lse[((size_t)batch * heads + head) * seq + query] =
-            row_sum > 0.0f ? (used_max + log2f(row_sum)) * 0.6931471805599453f : -INFINITY;
+      if (query < seq) {
+        const float value = row_sum > 0.0f ? (used_max + log2f(row_sum)) * 0.6931471805599453f : -INFINITY;
+        const size_t offset = (out_batch * heads + head) * seq + query;
+        if constexpr (GATHER) {
+          for (int d = 0; d < dst.count; ++d) dst.lse[d][offset] = value;
+        } else {
+          dst.lse[0][offset] = value;
+        }
+      }
     }
   }
 
@@ -428,9 +489,9 @@ __global__ void attn_fwd_generic_kernel(const __nv_bfloat16* __restrict__ q, con
 
 constexpr int kMaxDevices = 64;
 
-template <int D, bool CAUSAL>
-int launch_tensor(const void* q, const void* k, const void* v, void* out, float* lse, int batch, int seq, int heads,
-                  int kv_heads, cudaStream_t stream) {
+template <int D, bool CAUSAL, bool GATHER>
+int launch_tensor_to(const void* q, const void* k, const void* v, const OutputDestinations& dst, int batch, int seq, int heads,
+                     int kv_heads, cudaStream_t stream) {
   alignas(64) CUtensorMap map_q, map_k, map_v;
   if (int status = encode_tensormap_3d(&map_q, BB200_BF16, q, (uint64_t)heads * D, (uint64_t)seq, (uint64_t)batch,
                                        (uint64_t)heads * D * 2, (uint64_t)seq * heads * D * 2, 64, BLOCK_M, 1, 3))
@@ -446,7 +507,7 @@ int launch_tensor(const void* q, const void* k, const void* v, void* out, float*
     return fail(BB200_E_NO_DRIVER, "attention: no CUDA device is current");
   static bool configured[kMaxDevices] = {};
   if (!configured[device]) {
-    if (int status = check_runtime(cudaFuncSetAttribute(attn_fwd_kernel<D, CAUSAL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (int status = check_runtime(cudaFuncSetAttribute(attn_fwd_kernel<D, CAUSAL, GATHER>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                         Smem<D>::TOTAL),
                                    "cudaFuncSetAttribute(attention smem)"))
       return status;
@@ -455,9 +516,17 @@ int launch_tensor(const void* q, const void* k, const void* v, void* out, float*
   const float scale_log2e = (1.0f / sqrtf((float)D)) * 1.4426950408889634f;
   const int q_blocks = (seq + BLOCK_M - 1) / BLOCK_M;
   dim3 grid((q_blocks + Q_TILES - 1) / Q_TILES, heads, batch);
-  attn_fwd_kernel<D, CAUSAL><<<grid, THREADS, Smem<D>::TOTAL, stream>>>(
-      map_q, map_k, map_v, static_cast<__nv_bfloat16*>(out), lse, seq, heads, kv_heads, scale_log2e, device_status_word());
+  attn_fwd_kernel<D, CAUSAL, GATHER><<<grid, THREADS, Smem<D>::TOTAL, stream>>>(
+      map_q, map_k, map_v, dst, seq, heads, kv_heads, scale_log2e, device_status_word());
   return check_launch("attention kernel launch");
+}
+
+template <int D, bool CAUSAL>
+int launch_tensor(const void* q, const void* k, const void* v, const OutputDestinations& dst, int batch, int seq, int heads,
+                  int kv_heads, cudaStream_t stream) {
+  if (dst.count == 1 && dst.batch_offset == 0)
+    return launch_tensor_to<D, CAUSAL, false>(q, k, v, dst, batch, seq, heads, kv_heads, stream);
+  return launch_tensor_to<D, CAUSAL, true>(q, k, v, dst, batch, seq, heads, kv_heads, stream);
 }
 
 }  // namespace
@@ -465,26 +534,60 @@ int launch_tensor(const void* q, const void* k, const void* v, void* out, float*
 
 using namespace bb200;
 
-extern "C" int bb200_attention_fwd(const void* q, const void* k, const void* v, void* out, float* lse, int batch, int seq,
-                                   int heads, int kv_heads, int head_dim, int causal, void* stream) {
-  if (!q || !k || !v || !out || !lse) return fail(BB200_E_INVALID_ARGUMENT, "attention: null tensor pointer");
+static int attention_fwd_to(const void* q, const void* k, const void* v, const OutputDestinations& dst, int batch, int seq,
+                            int heads, int kv_heads, int head_dim, int causal, void* stream) {
+  if (!q || !k || !v) return fail(BB200_E_INVALID_ARGUMENT, "attention: null tensor pointer");
   if (batch <= 0 || seq <= 0 || heads <= 0 || kv_heads <= 0 || head_dim <= 0)
     return fail(BB200_E_INVALID_ARGUMENT, "attention: extents must be > 0");
   if (heads % kv_heads) return fail(BB200_E_INVALID_ARGUMENT, "attention: heads=%d must be divisible by kv_heads=%d", heads, kv_heads);
   if (batch > 65535 || heads > 65535) return fail(BB200_E_UNSUPPORTED_SHAPE, "attention: batch and heads are limited to 65535");
+  bool outputs_aligned = true;
+  for (int d = 0; d < dst.count; ++d) {
+    if (!dst.out[d] || !dst.lse[d]) return fail(BB200_E_INVALID_ARGUMENT, "attention: null tensor pointer");
+    outputs_aligned = outputs_aligned && aligned16(dst.out[d]);
+  }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const bool tensor_path = (head_dim == 64 || head_dim == 128) && aligned16(q) && aligned16(k) && aligned16(v) && aligned16(out);
+  const bool tensor_path = (head_dim == 64 || head_dim == 128) && aligned16(q) && aligned16(k) && aligned16(v) && outputs_aligned;
   if (tensor_path) {
     if (head_dim == 128)
-      return causal ? launch_tensor<128, true>(q, k, v, out, lse, batch, seq, heads, kv_heads, s)
-                    : launch_tensor<128, false>(q, k, v, out, lse, batch, seq, heads, kv_heads, s);
-    return causal ? launch_tensor<64, true>(q, k, v, out, lse, batch, seq, heads, kv_heads, s)
-                  : launch_tensor<64, false>(q, k, v, out, lse, batch, seq, heads, kv_heads, s);
+      return causal ? launch_tensor<128, true>(q, k, v, dst, batch, seq, heads, kv_heads, s)
+                    : launch_tensor<128, false>(q, k, v, dst, batch, seq, heads, kv_heads, s);
+    return causal ? launch_tensor<64, true>(q, k, v, dst, batch, seq, heads, kv_heads, s)
+                  : launch_tensor<64, false>(q, k, v, dst, batch, seq, heads, kv_heads, s);
   }
+  if (dst.count != 1 || dst.batch_offset != 0)
+    return fail(BB200_E_UNSUPPORTED_SHAPE, "attention (gather): only head_dim 64 and 128 with 16-byte aligned tensors are supported");
   if (seq > 8192) return fail(BB200_E_UNSUPPORTED_SHAPE, "attention: head_dim=%d with seq=%d > 8192 is not supported", head_dim, seq);
   dim3 grid(seq, heads, batch);
   attn_fwd_generic_kernel<<<grid, 128, (size_t)seq * sizeof(float), s>>>(
       static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(v),
-      static_cast<__nv_bfloat16*>(out), lse, seq, heads, kv_heads, head_dim, causal, 1.0f / sqrtf((float)head_dim));
+      static_cast<__nv_bfloat16*>(dst.out[0]), dst.lse[0], seq, heads, kv_heads, head_dim, causal, 1.0f / sqrtf((float)head_dim));
   return check_launch("attention (generic) kernel launch");
+}
+
+extern "C" int bb200_attention_fwd(const void* q, const void* k, const void* v, void* out, float* lse, int batch, int seq,
+                                   int heads, int kv_heads, int head_dim, int causal, void* stream) {
+  OutputDestinations single = {};
+  single.out[0] = out;
+  single.lse[0] = lse;
+  single.count = 1;
+  single.batch_offset = 0;
+  return attention_fwd_to(q, k, v, single, batch, seq, heads, kv_heads, head_dim, causal, stream);
+}
+
+extern "C" int bb200_attention_fwd_gather(const void* q, const void* k, const void* v, void* const* out_destinations,
+                                          float* const* lse_destinations, int destination_count, int batch_offset, int batch,
+                                          int seq, int heads, int kv_heads, int head_dim, int causal, void* stream) {
+  if (!out_destinations || !lse_destinations || destination_count < 1 || destination_count > kMaxDestinations)
+    return fail(BB200_E_INVALID_ARGUMENT, "attention (gather): 1..%d destination buffers are needed (got %d)", kMaxDestinations,
+                destination_count);
+  if (batch_offset < 0) return fail(BB200_E_INVALID_ARGUMENT, "attention (gather): batch_offset must be >= 0");
+  OutputDestinations all = {};
+  for (int d = 0; d < destination_count; ++d) {
+    all.out[d] = out_destinations[d];
+    all.lse[d] = lse_destinations[d];
+  }
+  all.count = destination_count;
+  all.batch_offset = batch_offset;
+  return attention_fwd_to(q, k, v, all, batch, seq, heads, kv_heads, head_dim, causal, stream);
 }

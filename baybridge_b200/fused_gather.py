@@ -137,6 +137,69 @@ class FusedGatherRmsNorm:
                     self.row_offset, plan.rows, plan.hidden, 1 if plan.gamma_is_full else 0, plan.epsilon, native.stream_handle(stream))
 
 
+class FusedGatherAttention:
+    """Attention forward with the all-gather of ``out`` and ``lse`` fused into the kernel's epilogue
+    (``bb200_attention_fwd_gather``): every rank attends over its own sequences and stores each finished output
+    row and log-sum-exp into the full ``[world·batch, seq, heads, head_dim]`` / ``[world·batch, heads, 1, seq]``
+    tensors of every rank.  ``over_group`` returns ``(fused, (out_full, lse_full))``."""
+
+    def __init__(self, kernel: Any, sample_args: Sequence[Any], *, out_destinations: Sequence[int],
+                 lse_destinations: Sequence[int], shard_index: int):
+        definition = _normalize_kernel(kernel)
+        self.ir = trace(definition, tuple(normalize_runtime_argument(arg) for arg in sample_args))
+        plan = match(self.ir)
+        if plan.kind != "attention":
+            raise BackendNotImplementedError("FusedGatherAttention needs a kernel that lowers to the attention forward")
+        if plan.head_dim not in (64, 128):
+            raise BackendNotImplementedError("FusedGatherAttention supports head_dim 64 and 128")
+        if not 1 <= len(out_destinations) <= MAX_FANOUT or len(out_destinations) != len(lse_destinations):
+            raise ValueError("1..8 destination buffers are needed, as many for lse as for out")
+        self.plan = plan
+        self.batch_offset = int(shard_index) * plan.batch
+        self._out_table = (ctypes.c_void_p * len(out_destinations))(*[int(pointer) for pointer in out_destinations])
+        self._lse_table = (ctypes.c_void_p * len(lse_destinations))(*[int(pointer) for pointer in lse_destinations])
+        self._count = len(out_destinations)
+
+    @classmethod
+    def over_group(cls, kernel: Any, sample_args: Sequence[Any], *, group=None):
+        import torch
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symmetric
+
+        group = group or dist.group.WORLD
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        if world > MAX_FANOUT:
+            raise BackendNotImplementedError(f"FusedGatherAttention fans out to at most {MAX_FANOUT} ranks")
+        plan = cls(kernel, sample_args, out_destinations=[1], lse_destinations=[1], shard_index=0).plan  # trace + match only
+        device = torch.device("cuda", torch.cuda.current_device())
+        out_full = symmetric.empty((world * plan.batch, plan.seq, plan.heads, plan.head_dim), dtype=torch.bfloat16, device=device)
+        lse_full = symmetric.empty((world * plan.batch, plan.heads, 1, plan.seq), dtype=torch.float32, device=device)
+        out_handle = symmetric.rendezvous(out_full, group)
+        lse_handle = symmetric.rendezvous(lse_full, group)
+        fused = cls(kernel, sample_args, out_destinations=[int(pointer) for pointer in out_handle.buffer_ptrs],
+                    lse_destinations=[int(pointer) for pointer in lse_handle.buffer_ptrs], shard_index=rank)
+        fused._handle = out_handle
+        fused._lse_handle = lse_handle
+        return fused, (out_full, lse_full)
+
+    def barrier(self) -> None:
+        handle = getattr(self, "_handle", None)
+        if handle is not None:
+            handle.barrier()  # one barrier orders both tensors: it follows every store of the launch on the stream
+
+    def run(self, q: Any, k: Any, v: Any, *, stream: Any = None) -> None:
+        plan = self.plan
+        native.require_device()
+        pointers = []
+        for value in (q, k, v):
+            if not hasattr(value, "data_ptr"):
+                value = normalize_runtime_argument(value)
+            pointers.append(ctypes.c_void_p(int(value.data_ptr() or getattr(value, "raw_address", 0))))
+        native.call("bb200_attention_fwd_gather", pointers[0], pointers[1], pointers[2], self._out_table, self._lse_table,
+                    self._count, self.batch_offset, plan.batch, plan.seq, plan.heads, plan.kv_heads, plan.head_dim,
+                    int(plan.causal), native.stream_handle(stream))
+
+
 class _DestinationTable(ctypes.Structure):
     _fields_ = [("p", ctypes.c_void_p * MAX_FANOUT)]
 

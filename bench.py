@@ -478,6 +478,32 @@ class Attention(Workload):
         self.pipeline = HostPipeline(lambda rows: zoo.attention_causal, [*self.hosts, self.o_host, self.lse_host],
                                      chunks=min(E2E_CHUNKS, self.batch), cache_dir=cache_dir)
 
+    def fused_gather_ms(self, torch, dist, cute, zoo, barrier) -> float | None:
+        """Attention with the all-gather of out (and lse) fused into the epilogue (peer stores of whole rows), then one barrier."""
+        from baybridge_b200.fused_gather import FusedGatherAttention
+
+        fused, (out_full, lse_full) = FusedGatherAttention.over_group(zoo.attention_causal, [self.q, self.k, self.v, self.o, self.lse])
+        stream = torch.cuda.current_stream().cuda_stream
+        for _ in range(3):
+            fused.run(self.q, self.k, self.v, stream=stream)
+            fused.barrier()
+        barrier()
+        reference, reference_lse = torch.empty_like(out_full), torch.empty_like(lse_full)
+        dist.all_gather_into_tensor(reference, self.o)
+        dist.all_gather_into_tensor(reference_lse, self.lse)
+        if not (torch.equal(out_full, reference) and torch.equal(lse_full, reference_lse)):
+            raise RuntimeError("fused attention + gather differs from attention followed by the NCCL all-gather")
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 10
+        barrier()
+        begin.record()
+        for _ in range(reps):
+            fused.run(self.q, self.k, self.v, stream=stream)
+            fused.barrier()
+        end.record()
+        barrier()
+        return begin.elapsed_time(end) / reps
+
     def config(self):
         return {"workload": f"causal attention fwd bf16 B{self.batch} H{self.heads} S{self.seq} D{self.dim} per GPU (layout [B,S,H,D]), causal FLOPs",
                 "l2": "working set 2.1 GB > 126 MB L2, no flush"}

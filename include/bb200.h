@@ -250,6 +250,18 @@ int bb200_gemm_bf16_gather(const void* a, const void* b, void* const* c_destinat
 int bb200_attention_fwd(const void* q, const void* k, const void* v, void* out, float* lse, int batch, int seq,
                         int heads, int kv_heads, int head_dim, int causal, void* stream);
 
+/* bb200_attention_fwd fused with the all-gather of its outputs across the GPUs of one box: this GPU's `batch`
+ * sequences are the block starting at `batch_offset` of a larger batch of which every GPU holds a copy of out
+ * ([total_batch, seq, heads, head_dim] bf16) and lse ([total_batch, heads, seq] fp32).  Each finished output
+ * row and lse value is stored into all `destination_count` (1..8) copies — out_destinations[d] /
+ * lse_destinations[d] are the bases of copy d (the GPU's own buffers or peer-mapped pointers; whole rows leave
+ * as contiguous 16-byte stores over NVLink).  head_dim 64 or 128 only.  The caller still needs a barrier across
+ * the GPUs before the gathered tensors are read.  Other arguments as bb200_attention_fwd.
+ * No upstream counterpart (upstream is single-device: src/baybridge/backends/cuda_driver.py:292-300). */
+int bb200_attention_fwd_gather(const void* q, const void* k, const void* v, void* const* out_destinations,
+                               float* const* lse_destinations, int destination_count, int batch_offset, int batch,
+                               int seq, int heads, int kv_heads, int head_dim, int causal, void* stream);
+
 /* Kernels with bounded device-side waits record a give-up in a per-device status word.  This
  * reads and clears it: *status_out = 0 if no wait timed out since the last call.  Synchronises
  * `stream` first.  No upstream counterpart (its generated kernels never wait on one another). */

@@ -108,3 +108,42 @@ def test_rmsnorm_stores_its_rows_into_every_destination(dtype, rows, hidden, zoo
         assert oracle.rel_l2(host[mine * rows:], reference) <= (2e-3 if dtype != "f32" else 2e-6)
         assert np.all(host[:mine * rows] == -3.0)
     assert torch.equal(copies[0], copies[1])
+
+
+@pytest.mark.parametrize("batch,seq,heads,kv_heads,dim,causal", [
+    (2, 256, 4, 2, 128, True), (1, 200, 2, 1, 128, False), (2, 512, 2, 2, 64, True), (1, 130, 2, 2, 64, False),
+])
+def test_attention_stores_its_sequences_into_every_destination(batch, seq, heads, kv_heads, dim, causal, zoo):
+    """bb200_attention_fwd_gather with two local copies of the gathered out/lse standing in for two GPUs."""
+    import torch
+
+    from baybridge_b200.fused_gather import FusedGatherAttention
+
+    rng = np.random.default_rng(batch * 1009 + seq * 31 + heads * 7 + dim + causal)
+    q = oracle.bf16_round(rng.standard_normal((batch, seq, heads, dim), dtype=np.float32))
+    k = oracle.bf16_round(rng.standard_normal((batch, seq, kv_heads, dim), dtype=np.float32))
+    v = oracle.bf16_round(rng.standard_normal((batch, seq, kv_heads, dim), dtype=np.float32))
+    d_q, d_k, d_v = (to_device(t, "bf16") for t in (q, k, v))
+    blocks, mine = 3, 1
+    outs = [torch.full((blocks * batch, seq, heads, dim), -3.0, device="cuda", dtype=torch.bfloat16) for _ in range(2)]
+    lses = [torch.full((blocks * batch, heads, 1, seq), -3.0, device="cuda", dtype=torch.float32) for _ in range(2)]
+    sample_out = torch.zeros((batch, seq, heads, dim), device="cuda", dtype=torch.bfloat16)
+    sample_lse = torch.zeros((batch, heads, 1, seq), device="cuda", dtype=torch.float32)
+    kernel = zoo.attention_causal if causal else zoo.attention_full
+    fused = FusedGatherAttention(kernel, [d_q, d_k, d_v, sample_out, sample_lse], out_destinations=[t.data_ptr() for t in outs],
+                                 lse_destinations=[t.data_ptr() for t in lses], shard_index=mine)
+    fused.run(d_q, d_k, d_v)
+    torch.cuda.synchronize()
+    ref_out, ref_lse = oracle.attention(q, k, v, causal=causal)
+    mine_rows = slice(mine * batch, (mine + 1) * batch)
+    for out, lse in zip(outs, lses):
+        host_out, host_lse = to_host(out), to_host(lse)
+        assert oracle.rel_l2(host_out[mine_rows], ref_out) <= 1e-2
+        assert float(np.abs(host_lse[mine_rows].reshape(ref_lse.shape) - ref_lse).max()) <= 1e-2
+        assert np.all(np.delete(host_out, mine_rows, axis=0) == -3.0) and np.all(np.delete(host_lse, mine_rows, axis=0) == -3.0)
+    assert torch.equal(outs[0], outs[1]) and torch.equal(lses[0], lses[1])
+    # the gathered rows are bit-identical to what the single-destination kernel writes
+    import baybridge_b200 as cute
+    artifact = cute.compile(kernel, d_q, d_k, d_v, sample_out, sample_lse, backend="b200")
+    artifact(d_q, d_k, d_v, sample_out, sample_lse)
+    assert torch.equal(outs[0][mine_rows], sample_out) and torch.equal(lses[0][mine_rows], sample_lse)
