@@ -156,7 +156,8 @@ class B200Backend:
             if len(args) != len(arguments):
                 raise TypeError(f"{ir.name} expects {len(arguments)} arguments, got {len(args)}")
             native.require_device()
-            if all_tensors and not self.synchronize:
+            synchronize = self.synchronize and not native.recording()  # a recording stream must not be synchronised
+            if all_tensors and not synchronize:
                 # fast path: every argument is a contiguous CUDA tensor handle of the expected shape and dtype on one
                 # device; anything else takes the general path below, which also produces the error messages
                 pointers = {}
@@ -192,7 +193,7 @@ class B200Backend:
                         scalars[position] = self._scalar_value(argument, value)
                 runner(pointers, scalars, stream_handle)
                 LAUNCH_COUNTER["launches"] += 1
-                if staged or self.synchronize:
+                if staged or synchronize:
                     native.call("bb200_stream_synchronize", stream_handle)
                 for tensor, slot, foreign in staged:
                     image = np.empty(tensor.numel, dtype=DEVICE_NUMPY[tensor.dtype])
@@ -243,6 +244,9 @@ class B200Backend:
                 raise TypeError(f"b200 tensor handle for argument '{argument.name}' does not expose a usable data_ptr()")
             return int(pointer)
         if isinstance(value, RuntimeTensor):
+            if native.recording():
+                raise BackendNotImplementedError(
+                    f"b200: host tensor argument '{argument.name}' cannot be staged while a launch graph records; pass device tensors")
             if tuple(value.shape) != tuple(spec.shape) or value.dtype != spec.dtype:
                 raise TypeError(
                     f"b200 tensor argument '{argument.name}' expects {spec.dtype}{list(spec.shape)}, got {value.dtype}{list(value.shape)}"

@@ -22,6 +22,7 @@ from pathlib import Path
 from typing import Any
 
 from ..errors import BackendNotImplementedError, CudaDriverError
+from ..launch_state import recording, set_recording  # noqa: F401 - re-exported for the launchers
 
 PACKAGE_DIR = Path(__file__).resolve().parent.parent
 CSRC_DIR = PACKAGE_DIR / "csrc"
@@ -152,6 +153,10 @@ PROTOTYPES: dict[str, list[Any]] = {
     "bb200_attention_fwd": [P, P, P, P, P, I, I, I, I, I, I, P],
     "bb200_attention_fwd_gather": [P, P, P, ctypes.POINTER(P), ctypes.POINTER(P), I, I, I, I, I, I, I, I, P],
     "bb200_take_device_status": [P, ctypes.POINTER(I)],
+    "bb200_graph_capture_begin": [P],
+    "bb200_graph_capture_end": [P, ctypes.POINTER(P)],
+    "bb200_graph_launch": [P, P],
+    "bb200_graph_destroy": [P],
 }
 
 

@@ -63,6 +63,12 @@ struct DriverApi {
   CUresult (*cuEventSynchronize)(CUevent) = nullptr;
   CUresult (*cuEventElapsedTime)(float*, CUevent, CUevent) = nullptr;
   CUresult (*cuEventDestroy)(CUevent) = nullptr;
+  CUresult (*cuStreamBeginCapture)(CUstream, CUstreamCaptureMode) = nullptr;
+  CUresult (*cuStreamEndCapture)(CUstream, CUgraph*) = nullptr;
+  CUresult (*cuGraphInstantiateWithFlags)(CUgraphExec*, CUgraph, unsigned long long) = nullptr;
+  CUresult (*cuGraphLaunch)(CUgraphExec, CUstream) = nullptr;
+  CUresult (*cuGraphExecDestroy)(CUgraphExec) = nullptr;
+  CUresult (*cuGraphDestroy)(CUgraph) = nullptr;
   CUresult (*cuMemAlloc)(CUdeviceptr*, size_t) = nullptr;
   CUresult (*cuMemFree)(CUdeviceptr) = nullptr;
   CUresult (*cuMemcpyHtoDAsync)(CUdeviceptr, const void*, size_t, CUstream) = nullptr;
@@ -130,6 +136,12 @@ static void load_driver_once() {
   BB200_BIND(cuEventSynchronize, nullptr);
   BB200_BIND(cuEventElapsedTime, nullptr);
   BB200_BIND(cuEventDestroy, "cuEventDestroy_v2");
+  BB200_BIND(cuStreamBeginCapture, "cuStreamBeginCapture_v2");
+  BB200_BIND(cuStreamEndCapture, nullptr);
+  BB200_BIND(cuGraphInstantiateWithFlags, nullptr);
+  BB200_BIND(cuGraphLaunch, nullptr);
+  BB200_BIND(cuGraphExecDestroy, nullptr);
+  BB200_BIND(cuGraphDestroy, nullptr);
   BB200_BIND(cuMemAlloc, "cuMemAlloc_v2");
   BB200_BIND(cuMemFree, "cuMemFree_v2");
   BB200_BIND(cuMemcpyHtoDAsync, "cuMemcpyHtoDAsync_v2");
@@ -431,6 +443,43 @@ int bb200_event_destroy(void* event) {
   if (!event) return fail(BB200_E_INVALID_ARGUMENT, "bb200_event_destroy: event is null");
   BB200_DRIVER_OR_RETURN(api);
   return check_driver(api, api->cuEventDestroy(static_cast<CUevent>(event)), "cuEventDestroy");
+}
+
+// ---- launch graphs: a recorded sequence of launches replayed with one driver call ------------------
+int bb200_graph_capture_begin(void* stream) {
+  if (!stream) return fail(BB200_E_INVALID_ARGUMENT, "bb200_graph_capture_begin: the default stream cannot record; pass a created stream");
+  BB200_DRIVER_OR_RETURN(api);
+  // relaxed mode: the first launch of a kernel may still load its module or size its shared memory while recording
+  return check_driver(api, api->cuStreamBeginCapture(static_cast<CUstream>(stream), CU_STREAM_CAPTURE_MODE_RELAXED),
+                      "cuStreamBeginCapture");
+}
+
+int bb200_graph_capture_end(void* stream, void** graph_out) {
+  if (!stream || !graph_out) return fail(BB200_E_INVALID_ARGUMENT, "bb200_graph_capture_end: null stream or output");
+  BB200_DRIVER_OR_RETURN(api);
+  *graph_out = nullptr;
+  CUgraph recorded = nullptr;
+  if (int status = check_driver(api, api->cuStreamEndCapture(static_cast<CUstream>(stream), &recorded), "cuStreamEndCapture"))
+    return status;
+  if (!recorded) return fail(BB200_E_INVALID_ARGUMENT, "bb200_graph_capture_end: the recording was invalidated (a call that is not allowed while recording was made)");
+  CUgraphExec executable = nullptr;
+  const int status = check_driver(api, api->cuGraphInstantiateWithFlags(&executable, recorded, 0), "cuGraphInstantiate");
+  api->cuGraphDestroy(recorded);
+  if (status) return status;
+  *graph_out = executable;
+  return BB200_OK;
+}
+
+int bb200_graph_launch(void* graph, void* stream) {
+  if (!graph) return fail(BB200_E_INVALID_ARGUMENT, "bb200_graph_launch: graph is null");
+  BB200_DRIVER_OR_RETURN(api);
+  return check_driver(api, api->cuGraphLaunch(static_cast<CUgraphExec>(graph), static_cast<CUstream>(stream)), "cuGraphLaunch");
+}
+
+int bb200_graph_destroy(void* graph) {
+  if (!graph) return fail(BB200_E_INVALID_ARGUMENT, "bb200_graph_destroy: graph is null");
+  BB200_DRIVER_OR_RETURN(api);
+  return check_driver(api, api->cuGraphExecDestroy(static_cast<CUgraphExec>(graph)), "cuGraphExecDestroy");
 }
 
 int bb200_mem_alloc(void** device_ptr_out, size_t bytes) {

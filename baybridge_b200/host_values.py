@@ -20,6 +20,7 @@ from typing import Any
 import numpy as np
 
 from .errors import BackendNotImplementedError
+from .launch_state import recording
 from .portable_ir import Layout, row_major_stride
 from .scalar_types import (
     LOGICAL_NUMPY,
@@ -346,7 +347,7 @@ class TensorHandle:
 
 
 def _export_capsule(value: Any, stream: Any | None) -> Any:
-    if stream is None:
+    if stream is None or recording():  # a recording stream cannot wait for the exporter's pending work
         return value.__dlpack__()
     try:
         return value.__dlpack__(stream=stream)

@@ -646,12 +646,104 @@ class ColumnReduce(_Reduction):
                 "l2": "working set 1.07 GB > 126 MB L2, no flush"}
 
 
-WORKLOADS = {cls.name: cls for cls in (FusedMulAdd, RmsNorm, Gemm, Attention, LayerNorm, RowReduce, ColumnReduce)}
+class IndexedAdd(Workload):
+    """Config 1: 256x256 f32 indexed add.  786 KB of traffic, all of it L2-resident after the first launch: what this
+    measures is launch latency, reported per call and per launch of a recorded launch graph (`launch_latency`)."""
+    name, unit, bound, dtype = "indexed_add", "GB/s", "hbm", "f32"
+    rows = cols = 256
+
+    def shrink(self):
+        pass
+
+    def size_key(self):
+        return self.rows
+
+    def work_per_step(self) -> float:
+        return 3.0 * self.rows * self.cols * 4
+
+    def setup(self, torch, cute, zoo, rank, cache_dir):
+        generator = torch.Generator(device="cuda").manual_seed(1001 + rank)
+        self.a = torch.rand((self.rows, self.cols), device="cuda", dtype=torch.float32, generator=generator).mul_(2).sub_(1)
+        self.b = torch.rand((self.rows, self.cols), device="cuda", dtype=torch.float32, generator=generator).mul_(2).sub_(1)
+        self.c = torch.zeros_like(self.a)
+        from baybridge_b200 import B200Backend
+
+        self.kernel = zoo.make_indexed_add_2d(self.rows, self.cols)
+        self.artifact = cute.compile(self.kernel, self.a, self.b, self.c, backend=B200Backend(synchronize=False), cache_dir=cache_dir)
+        self.blocking = cute.compile(self.kernel, self.a, self.b, self.c, backend="b200", cache_dir=cache_dir)  # upstream-style: sync per launch
+        self.args = tuple(cute.from_dlpack(t) for t in (self.a, self.b, self.c))
+        self.stream = torch.cuda.current_stream().cuda_stream
+        self.host = [self.a.cpu().pin_memory(), self.b.cpu().pin_memory(), self.c.cpu().pin_memory()]
+        self.h2d_bytes = 2 * self.rows * self.cols * 4
+        self.d2h_bytes = self.rows * self.cols * 4
+
+    def step(self):
+        self.artifact(*self.args, stream=self.stream)
+
+    def output(self):
+        return self.c
+
+    def e2e_setup(self, cute, zoo, cache_dir):
+        from baybridge_b200.host_pipeline import HostPipeline
+
+        self.pipeline = HostPipeline(lambda rows: zoo.make_indexed_add_2d(rows, self.cols), self.host, chunks=1, cache_dir=cache_dir)
+
+    def config(self):
+        return {"workload": f"indexed add c[r,c]=a[r,c]+b[r,c] f32 {self.rows}x{self.cols} per GPU (grid {self.rows} x block {self.cols})",
+                "l2": "786 KB working set is L2-resident: launch-latency bound, no roofline claimed"}
+
+    def cpu_sample(self):
+        rng = np.random.default_rng(1001)
+        a = rng.uniform(-1, 1, (self.rows, self.cols)).astype(np.float32).astype(np.float64)
+        b = rng.uniform(-1, 1, (self.rows, self.cols)).astype(np.float32).astype(np.float64)
+        return (lambda: (a + b).astype(np.float32)), self.work_per_step(), "full size, numpy f64 port of the per-thread CPU runtime loop"
+
+    def extras(self, torch) -> dict:
+        """Microseconds per launch three ways: upstream-style (synchronise after every launch), asynchronous launches,
+        and the same launches recorded once into a launch graph and replayed."""
+        from baybridge_b200.launch_graph import LaunchGraph
+
+        calls = 2000
+        torch.cuda.synchronize()
+        started = time.perf_counter()
+        for _ in range(calls):
+            self.blocking(*self.args)
+        blocking_us = (time.perf_counter() - started) / calls * 1e6
+        started = time.perf_counter()
+        for _ in range(calls):
+            self.artifact(*self.args, stream=self.stream)
+        torch.cuda.synchronize()
+        eager_us = (time.perf_counter() - started) / calls * 1e6
+        per_graph, replays = 200, 20
+        graph = LaunchGraph()
+        with graph.record() as recording_stream:
+            for _ in range(per_graph):
+                self.artifact(*self.args, stream=recording_stream)
+        for _ in range(3):
+            graph.replay(stream=self.stream)
+        torch.cuda.synchronize()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        started = time.perf_counter()
+        begin.record()
+        for _ in range(replays):
+            graph.replay(stream=self.stream)
+        end.record()
+        torch.cuda.synchronize()
+        graph_wall_us = (time.perf_counter() - started) / (per_graph * replays) * 1e6
+        graph_us = begin.elapsed_time(end) * 1e3 / (per_graph * replays)
+        graph.close()
+        return {"launch_latency": {"synchronising_call_us": blocking_us, "asynchronous_call_us": eager_us,
+                                   "graph_replay_us_per_launch": graph_us, "graph_replay_wall_us_per_launch": graph_wall_us,
+                                   "launches_per_graph": per_graph, "calls": calls}}
+
+
+WORKLOADS = {cls.name: cls for cls in (FusedMulAdd, RmsNorm, Gemm, Attention, LayerNorm, RowReduce, ColumnReduce, IndexedAdd)}
 METRIC = {
     "fused_mul_add": "elementwise HBM GB/s (fused c=a*b+a, bf16)", "rmsnorm": "RMSNorm HBM GB/s (bf16)",
     "gemm": "BF16 GEMM TFLOP/s", "attention": "causal attention forward TFLOP/s (bf16)",
     "layernorm": "LayerNorm + residual HBM GB/s (bf16)", "reduce_rows": "row reduction HBM GB/s (bf16)",
     "reduce_cols": "column reduction HBM GB/s (bf16)",
+    "indexed_add": "indexed add 256x256 f32: effective GB/s of a launch-latency-bound call",
 }
 
 
@@ -669,7 +761,7 @@ def time_cpu(workload: Workload, budget_s: float = 10.0, min_runs: int = 2) -> d
         durations.append(time.perf_counter() - t0)
     median = sorted(durations)[len(durations) // 2]
     scale = 1e9 if workload.unit == "GB/s" else 1e12
-    threads = 1 if workload.name in ("fused_mul_add", "rmsnorm") else (os.cpu_count() or 1)
+    threads = 1 if workload.name in ("fused_mul_add", "rmsnorm", "indexed_add") else (os.cpu_count() or 1)
     return {"value": work / median / scale, "unit": workload.unit, "cores": threads, "kind": "port",
             "sample": sample, "seconds_per_sample": median, "runs": len(durations)}
 
@@ -688,7 +780,7 @@ def reference_arm(args, workload: Workload) -> None:
     elapsed = time.perf_counter() - started
     scale = 1e9 if workload.unit == "GB/s" else 1e12
     value = work * steps / elapsed / scale
-    threads = 1 if workload.name in ("fused_mul_add", "rmsnorm") else (os.cpu_count() or 1)
+    threads = 1 if workload.name in ("fused_mul_add", "rmsnorm", "indexed_add") else (os.cpu_count() or 1)
     line = {
         "impl": "reference", "metric": METRIC[workload.name], "value": value, "unit": workload.unit,
         "n_gpus": args.gpus, "steps": steps, "warmup": min(args.warmup, 2), "ms_per_step": elapsed / steps * 1e3,
@@ -877,6 +969,8 @@ def main() -> None:
         }
         if allgather is not None:
             line["allgather"] = allgather
+        if hasattr(workload, "extras"):
+            line.update(workload.extras(torch))
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = time_cpu(workload)
         info = native.DeviceInfo()

@@ -134,6 +134,17 @@ int bb200_event_synchronize(void* event);
 int bb200_event_elapsed_ms(void* start, void* stop, float* ms_out);
 int bb200_event_destroy(void* event);
 
+/* Launch graphs.  Between capture_begin and capture_end every launch made on `stream` (a created stream, not the
+ * default one) — bb200_launch, the per-op entry points, copies and memsets — is recorded instead of executed;
+ * capture_end returns an executable graph that bb200_graph_launch replays on any stream with a single driver call,
+ * pointers and sizes as recorded.  Nothing may synchronise `stream` while it records.  For launch-latency-bound
+ * loops of small kernels (config 1 is one).  No upstream counterpart: upstream launches and synchronises one
+ * kernel at a time (src/baybridge/backends/ptx_exec.py:160-171). */
+int bb200_graph_capture_begin(void* stream);
+int bb200_graph_capture_end(void* stream, void** graph_out);
+int bb200_graph_launch(void* graph, void* stream);
+int bb200_graph_destroy(void* graph);
+
 /* Device memory for staging host tensors.
  * Replace CudaDriver.mem_alloc / mem_free / memcpy_htod / memcpy_dtoh
  * (src/baybridge/cuda_driver.py:352-375).  Copies are asynchronous on `stream`; pass pinned
