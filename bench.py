@@ -42,7 +42,7 @@ for entry in (str(ROOT), str(ROOT / "tests")):
         sys.path.insert(0, entry)
 
 L2_FLUSH_BYTES = 256 << 20
-E2E_CHUNKS = 8  # chunks of the host pipeline (copy-in / kernel / copy-out overlap)
+E2E_CHUNKS = int(os.environ.get("BB200_BENCH_E2E_CHUNKS", "16"))  # chunks of the host pipeline (copy-in / kernel / copy-out overlap)
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel at the full-size
 # workload, from one-pass `ncu --metrics dram__bytes_read.sum,dram__bytes_write.sum --clock-control none`
 # captures of this script (commands and figures in profiles/); None for other sizes.
