@@ -51,6 +51,9 @@ MEASURED_DRAM_TRAFFIC = {
     ("rmsnorm", 65536): 1.07e9 + 1.02e9,
     ("gemm", 8192): 1.43e9 + 126.8e6,
     ("attention", 16): 1.61e9 + 523.8e6,
+    ("layernorm", 32768): 1.07e9 + 1.02e9,
+    ("reduce_rows", 65536): 1.07e9 + 2.0e6,
+    ("reduce_cols", 65536): 1.07e9 + 1.8e6,
 }
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
