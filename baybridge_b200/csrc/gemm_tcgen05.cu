@@ -32,16 +32,25 @@ namespace {
 using namespace sm100;
 
 constexpr int BM = 128, BN = 256, BK = 64;
-constexpr int STAGES = 4;
 constexpr int UMMA_K = 16;
 constexpr int A_TILE_BYTES = BM * BK * 2;  // 16 KB
-constexpr int B_TILE_BYTES = BN * BK * 2;  // 32 KB
-constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
-constexpr int ACC_COLUMNS = BN;            // fp32 accumulator: 128 lanes x 256 columns
+constexpr int ACC_COLUMNS = BN;            // fp32 accumulator of a full-width tile: 128 lanes x 256 columns
 constexpr int TMEM_COLUMNS = 2 * ACC_COLUMNS;
 constexpr int THREADS = 192;
 constexpr int DEFAULT_GROUP_M = 16;        // rasterisation: tiles advance down this many M-blocks before moving in N
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */ + 4 * 32 * 144 /* epilogue staging */;
+
+// The single-CTA kernel comes in three tile widths.  256 columns is the fastest per flop (one MMA instruction covers
+// 128x256); 128 and 64 columns exist for problems with too few 128x256 tiles to occupy the SMs — narrower tiles
+// spread the operand streams over more SMs, and their smaller stages buy a deeper ring.
+template <int TN> struct Tile {
+  static_assert(TN == 256 || TN == 128 || TN == 64, "tile widths: 256, 128, 64");
+  static constexpr int STAGES = TN == 256 ? 4 : TN == 128 ? 6 : 8;
+  static constexpr int B_TILE_BYTES = TN * BK * 2;
+  static constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
+  static constexpr int ACC_COLUMNS = TN;          // fp32 accumulator: 128 lanes x TN columns
+  static constexpr int TMEM_COLUMNS = 2 * TN;     // double-buffered; a power of two >= 32
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */ + 4 * 32 * 144 /* epilogue staging */;
+};
 
 enum WaitCode { kWaitEmpty = 101, kWaitFull = 102, kWaitAccEmpty = 103, kWaitAccFull = 104 };
 
@@ -110,13 +119,13 @@ constexpr int STAGE_ROW_BYTES = 144;
 constexpr int STAGING_BYTES_PER_WARP = 32 * STAGE_ROW_BYTES;
 constexpr int STAGING_BYTES = 4 * STAGING_BYTES_PER_WARP;
 
-template <typename OutT>
+template <typename OutT, int COLS>
 __device__ __forceinline__ void store_accumulator_rows(const Destinations& dst, uint32_t taddr, int first_row, int lane, int m, int n,
                                                        int col0, uint8_t* stage) {
   constexpr int PASS_COLS = 128 / (int)sizeof(OutT);  // columns that make 128 bytes of output: 64 (bf16) or 32 (f32)
   const bool rows_aligned = ((size_t)n * sizeof(OutT)) % 16 == 0;
 #pragma unroll 1
-  for (int pass = 0; pass < BN / PASS_COLS; ++pass) {
+  for (int pass = 0; pass < COLS / PASS_COLS; ++pass) {
     uint32_t acc[PASS_COLS];
 #pragma unroll
     for (int q = 0; q < PASS_COLS / 32; ++q)
@@ -176,10 +185,12 @@ __device__ __forceinline__ void store_accumulator_rows(const Destinations& dst, 
 // B_MN = false: B tile is [BN n-rows, 64 k] (K-major).  B_MN = true: B is stored [K, N]; a stage holds
 // BN/64 sub-tiles of [64 k-rows, 64 n] (MN-major), each 8 KB, consecutive in shared memory.  A_MN is the
 // same for A stored [K, M]: BM/64 sub-tiles of [64 k-rows, 64 m].
-template <typename OutT, bool A_MN, bool B_MN>
+template <typename OutT, bool A_MN, bool B_MN, int TN>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_abt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ Destinations dst,
                 int m, int n, int k, int group_m, int* status_word) {
+  using T = Tile<TN>;
+  constexpr int STAGES = T::STAGES, STAGE_BYTES = T::STAGE_BYTES, ACC_COLUMNS = T::ACC_COLUMNS, TMEM_COLUMNS = T::TMEM_COLUMNS;
   extern __shared__ uint8_t smem_raw[];
   // operand tiles need 1024-byte alignment for the 128-byte swizzle pattern
   const uint32_t smem_base = (smem_addr(smem_raw) + 1023u) & ~1023u;
@@ -196,7 +207,7 @@ gemm_abt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int m_blocks = (m + BM - 1) / BM, n_blocks = (n + BN - 1) / BN;
+  const int m_blocks = (m + BM - 1) / BM, n_blocks = (n + TN - 1) / TN;
   const int tiles = m_blocks * n_blocks;
   const int k_blocks = (k + BK - 1) / BK;
 
@@ -244,10 +255,10 @@ gemm_abt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           }
           if constexpr (B_MN) {
 #pragma unroll
-            for (int t = 0; t < BN / 64; ++t)
-              tma_load_2d(b_dst + t * (BK * 128), &map_b, full_bar(stage), coord.n_block * BN + t * 64, kb * BK);
+            for (int t = 0; t < TN / 64; ++t)
+              tma_load_2d(b_dst + t * (BK * 128), &map_b, full_bar(stage), coord.n_block * TN + t * 64, kb * BK);
           } else {
-            tma_load_2d(b_dst, &map_b, full_bar(stage), kb * BK, coord.n_block * BN);
+            tma_load_2d(b_dst, &map_b, full_bar(stage), kb * BK, coord.n_block * TN);
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
@@ -256,7 +267,7 @@ gemm_abt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (elect_one()) {
-      constexpr uint32_t idesc = umma_idesc_bf16_f32(BM, BN, A_MN, B_MN);
+      constexpr uint32_t idesc = umma_idesc_bf16_f32(BM, TN, A_MN, B_MN);
       int stage = 0;
       uint32_t phase = 0;
       int local_tile = 0;
@@ -300,9 +311,9 @@ gemm_abt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld below is warp-collective: leave together or not at all
       if (!ok) break;
       tcgen05_fence_after();
-      const int col0 = coord.n_block * BN;
+      const int col0 = coord.n_block * TN;
       const uint32_t taddr = tmem_base + ((uint32_t)(quadrant * 32) << 16) + (uint32_t)(buffer * ACC_COLUMNS);
-      store_accumulator_rows<OutT>(dst, taddr, coord.m_block * BM + quadrant * 32, lane, m, n, col0,
+      store_accumulator_rows<OutT, TN>(dst, taddr, coord.m_block * BM + quadrant * 32, lane, m, n, col0,
                                    smem_aligned + STAGES * STAGE_BYTES + 256 + (warp - 2) * STAGING_BYTES_PER_WARP);
       tcgen05_fence_before();
       __syncwarp();
@@ -475,7 +486,7 @@ gemm_abt_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       tcgen05_fence_after();
       const int col0 = coord.n_block * BN;
       const uint32_t taddr = tmem_base + ((uint32_t)(quadrant * 32) << 16) + (uint32_t)(buffer * ACC_COLUMNS);
-      store_accumulator_rows<OutT>(dst, taddr, coord.m_block * PAIR_BM + (int)cta_rank * BM + quadrant * 32, lane, m, n, col0,
+      store_accumulator_rows<OutT, BN>(dst, taddr, coord.m_block * PAIR_BM + (int)cta_rank * BM + quadrant * 32, lane, m, n, col0,
                                    smem_aligned + PAIR_STAGES * PAIR_STAGE_BYTES + 256 + (warp - 2) * STAGING_BYTES_PER_WARP);
       tcgen05_fence_before();
       __syncwarp();
@@ -551,8 +562,9 @@ int raster_group_m() {
   return value;
 }
 
-// The pair kernel pays off once both tile dimensions are large enough to fill the pairs; small and
-// ragged problems stay on the single-CTA kernel.  BB200_GEMM_PAIR=0/1 forces the choice for tuning runs.
+// The pair kernel pays off once there are 256x256 tiles for at least half of the CTA pairs (a pair tile streams a third
+// less per flop, so even a half-occupied wave beats single-CTA tiles at full occupancy); smaller and ragged
+// problems stay on the single-CTA kernel.  BB200_GEMM_PAIR=0/1 forces the choice for tuning runs.
 bool use_pair_kernel(int m, int n, int sms) {
   static int forced = -2;
   if (forced == -2) {
@@ -561,7 +573,10 @@ bool use_pair_kernel(int m, int n, int sms) {
   }
   if (forced >= 0) return forced == 1;
   const long tiles = (long)((m + PAIR_BM - 1) / PAIR_BM) * ((n + BN - 1) / BN);
-  return (sms % 2) == 0 && tiles >= sms / 2;
+  // an odd number of 128-row blocks leaves the last pair tile half empty: tolerable from nine blocks on
+  const int m_blocks = (m + BM - 1) / BM;
+  const bool rows_fill_pairs = (m_blocks % 2) == 0 || m_blocks >= 9;
+  return (sms % 2) == 0 && rows_fill_pairs && tiles >= sms / 4;
 }
 
 template <typename OutT, bool A_MN, bool B_MN>
@@ -589,31 +604,61 @@ int launch_pair(const void* a_operand, const void* b, const Destinations& dst, i
 
 // A_MN: A is stored [k, m] (m contiguous) and consumed as an MN-major operand; otherwise [m, k].
 // B_MN: B is stored [k, n] (n contiguous), MN-major; otherwise [n, k].
-template <typename OutT, bool A_MN, bool B_MN>
-int launch_native(const void* a_operand, const void* b, const Destinations& dst, int m, int n, int k, cudaStream_t stream) {
+// Tile width of the single-CTA kernel.  BB200_GEMM_TILE_N = 256 / 128 / 64 forces it for tuning runs.
+int single_cta_tile_n(int m, int n, int sms) {
+  static int forced = -1;
+  if (forced < 0) {
+    const char* text = getenv("BB200_GEMM_TILE_N");
+    const int parsed = text ? atoi(text) : 0;
+    forced = parsed == 256 || parsed == 128 || parsed == 64 ? parsed : 0;
+  }
+  if (forced) return forced;
+  // a wave of full-width tiles that (nearly) fills the SMs stays; otherwise the narrowest width whose tiles still fit one
+  // wave: a lone tile is bound by the latency of its own operand stream, and narrower tiles put more streams in flight
+  const long m_blocks = (m + BM - 1) / BM;
+  if (m_blocks * ((n + 255) / 256) * 10 >= (long)sms * 9) return 256;
+  int chosen = 256;
+  for (int width : {128, 64}) {
+    if (m_blocks * ((n + width - 1) / width) <= (long)sms) chosen = width;
+  }
+  return chosen;
+}
+
+template <typename OutT, bool A_MN, bool B_MN, int TN>
+int launch_single(const void* a_operand, const void* b, const Destinations& dst, int m, int n, int k, int device, int sms, cudaStream_t stream) {
+  using T = Tile<TN>;
   alignas(64) CUtensorMap map_a, map_b;
   if (int status = A_MN ? encode_tensormap_2d(&map_a, BB200_BF16, a_operand, (uint64_t)k, (uint64_t)m, (uint64_t)m * 2, BK, 64, 3)
                         : encode_tensormap_2d(&map_a, BB200_BF16, a_operand, (uint64_t)m, (uint64_t)k, (uint64_t)k * 2, BM, BK, 3))
     return status;
   if (int status = B_MN ? encode_tensormap_2d(&map_b, BB200_BF16, b, (uint64_t)k, (uint64_t)n, (uint64_t)n * 2, BK, 64, 3)
-                        : encode_tensormap_2d(&map_b, BB200_BF16, b, (uint64_t)n, (uint64_t)k, (uint64_t)k * 2, BN, BK, 3))
+                        : encode_tensormap_2d(&map_b, BB200_BF16, b, (uint64_t)n, (uint64_t)k, (uint64_t)k * 2, TN, BK, 3))
     return status;
-  const int device = current_device();
-  if (device < 0) return fail(BB200_E_NO_DRIVER, "gemm: no CUDA device is current");
   static bool configured[kMaxDevices] = {};  // per template instantiation and device
   if (!configured[device]) {
-    if (int status = check_runtime(cudaFuncSetAttribute(gemm_abt_kernel<OutT, A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES),
+    if (int status = check_runtime(cudaFuncSetAttribute(gemm_abt_kernel<OutT, A_MN, B_MN, TN>, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_BYTES),
                                    "cudaFuncSetAttribute(gemm smem)"))
       return status;
     configured[device] = true;
   }
+  const int tiles = ((m + BM - 1) / BM) * ((n + TN - 1) / TN);
+  const int grid = tiles < sms ? tiles : sms;
+  gemm_abt_kernel<OutT, A_MN, B_MN, TN><<<grid, THREADS, T::SMEM_BYTES, stream>>>(map_a, map_b, dst, m, n, k, raster_group_m(), device_status_word());
+  return check_launch("gemm kernel launch");
+}
+
+template <typename OutT, bool A_MN, bool B_MN>
+int launch_native(const void* a_operand, const void* b, const Destinations& dst, int m, int n, int k, cudaStream_t stream) {
+  const int device = current_device();
+  if (device < 0) return fail(BB200_E_NO_DRIVER, "gemm: no CUDA device is current");
   const int sms = cached_sm_count(device);
   if (sms <= 0) return fail(BB200_E_NO_DRIVER, "gemm: could not query the SM count");
   if (use_pair_kernel(m, n, sms)) return launch_pair<OutT, A_MN, B_MN>(a_operand, b, dst, m, n, k, device, sms, stream);
-  const int tiles = ((m + BM - 1) / BM) * ((n + BN - 1) / BN);
-  const int grid = tiles < sms ? tiles : sms;
-  gemm_abt_kernel<OutT, A_MN, B_MN><<<grid, THREADS, SMEM_BYTES, stream>>>(map_a, map_b, dst, m, n, k, raster_group_m(), device_status_word());
-  return check_launch("gemm kernel launch");
+  switch (single_cta_tile_n(m, n, sms)) {
+    case 256: return launch_single<OutT, A_MN, B_MN, 256>(a_operand, b, dst, m, n, k, device, sms, stream);
+    case 128: return launch_single<OutT, A_MN, B_MN, 128>(a_operand, b, dst, m, n, k, device, sms, stream);
+    default: return launch_single<OutT, A_MN, B_MN, 64>(a_operand, b, dst, m, n, k, device, sms, stream);
+  }
 }
 
 int dispatch_native(const void* a_operand, const void* b, const Destinations& dst, int m, int n, int k, bool a_is_km, bool b_is_kn,

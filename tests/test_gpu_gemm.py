@@ -44,6 +44,10 @@ def test_compiled_gemm_matches_upstream_vectors(case, zoo, tmp_path):
 @pytest.mark.parametrize("m,n,k", [
     (128, 256, 64), (256, 512, 128), (128, 256, 1024), (384, 768, 320), (200, 136, 72), (100, 50, 24), (1, 8, 8),
     (129, 257, 8), (1024, 1024, 1024), (4096, 512, 256), (130, 4100, 136),
+    (128, 35840, 64),    # one row block, 140 full-width tiles: the 256-column single-CTA kernel
+    (256, 8192, 512),    # 128 tiles of 128 columns fit one wave: the 128-column kernel
+    (512, 8192, 256),    # 64 pair tiles: the CTA-pair kernel at less than one wave
+    (384, 4096, 128),    # three row blocks (no pairs), 192 tiles of 64 columns would not fit: 128 columns
 ])
 @pytest.mark.parametrize("c_dtype", ["bf16", "f32"])
 def test_c_abi_gemm_abt_shapes(m, n, k, c_dtype):
@@ -67,6 +71,8 @@ def test_c_abi_gemm_abt_shapes(m, n, k, c_dtype):
     (156, 264, 96),      # A stored [k, m] with m % 8 != 0: the transposed-copy path
     (640, 1032, 200),    # several tiles, ragged edges in m, n and k
     (2560, 2048, 136),   # enough 256x256 tiles for the CTA-pair kernel
+    (128, 34816, 72),    # 136 full-width tiles in one row block: the 256-column single-CTA kernel
+    (256, 8192, 72),     # the 128-column single-CTA kernel
 ])
 def test_c_abi_gemm_transpose_variants_agree(m, n, k):
     from baybridge_b200.backend import native
