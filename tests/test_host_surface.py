@@ -312,6 +312,32 @@ def test_launcher_contract_without_a_device(zoo, tmp_path):
     assert 77 in carriers[0].dlpack_streams
 
 
+def test_launch_graph_state_without_a_device():
+    """Recording needs a device (no CPU stand-in); while a graph records, DLPack exporters are not handed the stream."""
+    from baybridge_b200 import launch_state
+    from baybridge_b200.backend import native
+    from baybridge_b200.launch_graph import LaunchGraph
+
+    graph = LaunchGraph()
+    with pytest.raises(RuntimeError, match="nothing has been recorded"):
+        graph.replay()
+    if not native.device_available():
+        with pytest.raises(cute.BackendNotImplementedError, match="CUDA device"):
+            with graph.record():
+                pass
+    assert not native.recording()
+    carrier = FakeCudaTensor((16,), "float32")
+    launch_state.set_recording(True)
+    try:
+        cute.from_dlpack(carrier, stream=55)
+    finally:
+        launch_state.set_recording(False)
+    assert 55 not in carrier.dlpack_streams
+    cute.from_dlpack(carrier, stream=56)
+    assert 56 in carrier.dlpack_streams
+    graph.close()
+
+
 def test_from_dlpack_handle_fields():
     handle = cute.from_dlpack(FakeCudaTensor((4, 8), "torch.float16", ptr=16384, stride=(8, 1)), assumed_align=32)
     assert (handle.shape, handle.dtype, handle.device_type, handle.device_id) == ((4, 8), "f16", 2, 0)
