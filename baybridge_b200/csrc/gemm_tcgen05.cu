@@ -121,7 +121,7 @@ constexpr int STAGING_BYTES = 4 * STAGING_BYTES_PER_WARP;
 
 template <typename OutT, int COLS>
 __device__ __forceinline__ void store_accumulator_rows(const Destinations& dst, uint32_t taddr, int first_row, int lane, int m, int n,
-                                                       int col0, uint8_t* stage) {
+                                                       int col0, uint8_t* stage, int extra_row_offset = 0) {
   constexpr int PASS_COLS = 128 / (int)sizeof(OutT);  // columns that make 128 bytes of output: 64 (bf16) or 32 (f32)
   const bool rows_aligned = ((size_t)n * sizeof(OutT)) % 16 == 0;
 #pragma unroll 1
@@ -160,7 +160,7 @@ __device__ __forceinline__ void store_accumulator_rows(const Destinations& dst, 
         const uint4 value = *reinterpret_cast<const uint4*>(stage + r * STAGE_ROW_BYTES + piece * 16);
         const int row = first_row + r;
         if (row < m) {
-          const size_t byte_offset = ((size_t)(row + dst.row_offset) * n + col) * sizeof(OutT) + (size_t)piece * 16;
+          const size_t byte_offset = ((size_t)(row + dst.row_offset + extra_row_offset) * n + col) * sizeof(OutT) + (size_t)piece * 16;
           for (int d = 0; d < dst.count; ++d) *reinterpret_cast<uint4*>(static_cast<uint8_t*>(dst.p[d]) + byte_offset) = value;
         }
       }
@@ -172,7 +172,7 @@ __device__ __forceinline__ void store_accumulator_rows(const Destinations& dst, 
         for (int q = 0; q < PASS_COLS / 32; ++q) {
           const int c = col + q * 32;
           if (c < n) {
-            const size_t offset = (size_t)(row + dst.row_offset) * n + c;
+            const size_t offset = (size_t)(row + dst.row_offset + extra_row_offset) * n + c;
             for (int d = 0; d < dst.count; ++d)
               store_chunk<OutT>(static_cast<OutT*>(dst.p[d]) + offset, *reinterpret_cast<const uint32_t(*)[32]>(&acc[q * 32]), n - c);
           }
@@ -188,7 +188,7 @@ __device__ __forceinline__ void store_accumulator_rows(const Destinations& dst, 
 template <typename OutT, bool A_MN, bool B_MN, int TN>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_abt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ Destinations dst,
-                int m, int n, int k, int group_m, int* status_word) {
+                int m, int n, int k, int group_m, int splits, int kb_per_split, int* status_word) {
   using T = Tile<TN>;
   constexpr int STAGES = T::STAGES, STAGE_BYTES = T::STAGE_BYTES, ACC_COLUMNS = T::ACC_COLUMNS, TMEM_COLUMNS = T::TMEM_COLUMNS;
   extern __shared__ uint8_t smem_raw[];
@@ -210,6 +210,10 @@ gemm_abt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   const int m_blocks = (m + BM - 1) / BM, n_blocks = (n + TN - 1) / TN;
   const int tiles = m_blocks * n_blocks;
   const int k_blocks = (k + BK - 1) / BK;
+  // split along K: work item w covers k-blocks [split * kb_per_split, +kb_per_split) of tile w % tiles and its
+  // accumulator goes to row block `split` of an fp32 workspace [splits * m, n] that a second kernel folds
+  // (splits == 1: kb_per_split == k_blocks and the tile goes straight to C)
+  const int work_items = tiles * splits;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -238,9 +242,10 @@ gemm_abt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < tiles; tile += gridDim.x) {
-        const TileCoord coord = tile_coord(tile, m_blocks, n_blocks, group_m);
-        for (int kb = 0; kb < k_blocks; ++kb) {
+      for (int work = blockIdx.x; ok && work < work_items; work += gridDim.x) {
+        const TileCoord coord = tile_coord(work % tiles, m_blocks, n_blocks, group_m);
+        const int kb_begin = (work / tiles) * kb_per_split, kb_end = min(k_blocks, kb_begin + kb_per_split);
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
           // a fresh barrier's "previous phase" counts as complete: waiting on parity^1 passes at once
           if (!(ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, status_word, kWaitEmpty))) break;
           const uint32_t a_dst = smem_base + stage * STAGE_BYTES;
@@ -272,13 +277,14 @@ gemm_abt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       uint32_t phase = 0;
       int local_tile = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < tiles; tile += gridDim.x, ++local_tile) {
+      for (int work = blockIdx.x; ok && work < work_items; work += gridDim.x, ++local_tile) {
         const int buffer = local_tile & 1;
         const uint32_t acc_phase = (uint32_t)(local_tile >> 1) & 1u;
         if (!(ok = mbar_wait(acc_empty_bar(buffer), acc_phase ^ 1u, abort_flag, status_word, kWaitAccEmpty))) break;
         tcgen05_fence_after();
         const uint32_t tmem_acc = tmem_base + (uint32_t)(buffer * ACC_COLUMNS);
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        const int kb_begin = (work / tiles) * kb_per_split, kb_end = min(k_blocks, kb_begin + kb_per_split);
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
           if (!(ok = mbar_wait(full_bar(stage), phase, abort_flag, status_word, kWaitFull))) break;
           tcgen05_fence_after();
           const uint32_t a_src = smem_base + stage * STAGE_BYTES;
@@ -291,7 +297,7 @@ gemm_abt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 #pragma unroll
           for (int kk = 0; kk < BK / UMMA_K; ++kk)
             umma_bf16_ss(tmem_acc, umma_desc_advance_k(desc_a, kk * a_step), umma_desc_advance_k(desc_b, kk * b_step),
-                         idesc, (kb | kk) != 0 ? 1u : 0u);
+                         idesc, (kb > kb_begin || kk != 0) ? 1u : 0u);
           umma_commit(empty_bar(stage));  // the stage may be refilled once these MMAs have read it
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
@@ -303,8 +309,8 @@ gemm_abt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const int quadrant = warp & 3;  // TMEM lanes [32*quadrant, 32*quadrant+32) are the ones this warp may read
     int local_tile = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; ok && tile < tiles; tile += gridDim.x, ++local_tile) {
-      const TileCoord coord = tile_coord(tile, m_blocks, n_blocks, group_m);
+    for (int work = blockIdx.x; ok && work < work_items; work += gridDim.x, ++local_tile) {
+      const TileCoord coord = tile_coord(work % tiles, m_blocks, n_blocks, group_m);
       const int buffer = local_tile & 1;
       const uint32_t acc_phase = (uint32_t)(local_tile >> 1) & 1u;
       ok = mbar_wait(acc_full_bar(buffer), acc_phase, abort_flag, status_word, kWaitAccFull);
@@ -314,7 +320,8 @@ gemm_abt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       const int col0 = coord.n_block * TN;
       const uint32_t taddr = tmem_base + ((uint32_t)(quadrant * 32) << 16) + (uint32_t)(buffer * ACC_COLUMNS);
       store_accumulator_rows<OutT, TN>(dst, taddr, coord.m_block * BM + quadrant * 32, lane, m, n, col0,
-                                   smem_aligned + STAGES * STAGE_BYTES + 256 + (warp - 2) * STAGING_BYTES_PER_WARP);
+                                   smem_aligned + STAGES * STAGE_BYTES + 256 + (warp - 2) * STAGING_BYTES_PER_WARP,
+                                   (work / tiles) * m);
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(acc_empty_bar(buffer));
@@ -335,6 +342,50 @@ gemm_abt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     __syncwarp();
     tcgen05_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLUMNS);
+  }
+}
+
+// Folds the fp32 partial products of a K-split GEMM — `partial` is [splits * m, n], one row block per split —
+// into C (every destination of the gather form), rounding once.
+template <typename OutT>
+__global__ void __launch_bounds__(256) split_k_fold_kernel(const float* __restrict__ partial, const __grid_constant__ Destinations dst,
+                                                           int m, int n, int splits) {
+  const size_t total = (size_t)m * n;
+  const size_t slice = total;  // elements per split
+  if ((n & 3) == 0) {
+    const size_t index = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (index >= total) return;
+    float4 sum = *reinterpret_cast<const float4*>(partial + index);
+    for (int s = 1; s < splits; ++s) {
+      const float4 part = *reinterpret_cast<const float4*>(partial + (size_t)s * slice + index);
+      sum.x += part.x; sum.y += part.y; sum.z += part.z; sum.w += part.w;
+    }
+    const size_t out_index = index + (size_t)dst.row_offset * n;
+    for (int d = 0; d < dst.count; ++d) {
+      OutT* out = static_cast<OutT*>(dst.p[d]) + out_index;
+      if constexpr (sizeof(OutT) == 2) {
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(sum.x, sum.y), hi = __floats2bfloat162_rn(sum.z, sum.w);
+        if ((reinterpret_cast<uintptr_t>(out) & 7u) == 0) {
+          *reinterpret_cast<uint2*>(out) = make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+        } else {
+          out[0] = lo.x; out[1] = lo.y; out[2] = hi.x; out[3] = hi.y;
+        }
+      } else {
+        if ((reinterpret_cast<uintptr_t>(out) & 15u) == 0) *reinterpret_cast<float4*>(out) = sum;
+        else { out[0] = sum.x; out[1] = sum.y; out[2] = sum.z; out[3] = sum.w; }
+      }
+    }
+  } else {
+    for (size_t index = (size_t)blockIdx.x * blockDim.x * 4 + threadIdx.x; index < total && index < ((size_t)blockIdx.x + 1) * blockDim.x * 4;
+         index += blockDim.x) {
+      float sum = partial[index];
+      for (int s = 1; s < splits; ++s) sum += partial[(size_t)s * slice + index];
+      const size_t out_index = index + (size_t)dst.row_offset * n;
+      for (int d = 0; d < dst.count; ++d) {
+        if constexpr (sizeof(OutT) == 2) static_cast<__nv_bfloat16*>(dst.p[d])[out_index] = __float2bfloat16_rn(sum);
+        else static_cast<float*>(dst.p[d])[out_index] = sum;
+      }
+    }
   }
 }
 
@@ -624,8 +675,33 @@ int single_cta_tile_n(int m, int n, int sms) {
   return chosen;
 }
 
+Destinations single_destination(void* c) {
+  Destinations dst = {};
+  dst.p[0] = c;
+  dst.count = 1;
+  dst.row_offset = 0;
+  return dst;
+}
+
+// K-splits of the single-CTA kernel: when even the narrowest tiles leave most SMs idle and K is deep, each tile's K
+// range is cut into `splits` work items whose fp32 partial products a second kernel folds.  Needs a workspace, so the
+// allocation-free entry point never splits.  BB200_GEMM_SPLIT_K forces a count (1 = never) for tuning runs.
+int split_k_count(int tiles, int k_blocks, int sms) {
+  static int forced = -1;
+  if (forced < 0) {
+    const char* text = getenv("BB200_GEMM_SPLIT_K");
+    const int parsed = text ? atoi(text) : 0;
+    forced = parsed >= 1 && parsed <= 64 ? parsed : 0;
+  }
+  int splits = forced ? forced : (tiles * 2 <= sms ? sms / tiles : 1);
+  if (splits > 16 && !forced) splits = 16;
+  if (splits > k_blocks / 8) splits = k_blocks / 8;  // at least eight 64-wide k-blocks per work item
+  return splits < 2 ? 1 : splits;
+}
+
 template <typename OutT, bool A_MN, bool B_MN, int TN>
-int launch_single(const void* a_operand, const void* b, const Destinations& dst, int m, int n, int k, int device, int sms, cudaStream_t stream) {
+int launch_single(const void* a_operand, const void* b, const Destinations& dst, int m, int n, int k, int device, int sms, bool may_split,
+                  cudaStream_t stream) {
   using T = Tile<TN>;
   alignas(64) CUtensorMap map_a, map_b;
   if (int status = A_MN ? encode_tensormap_2d(&map_a, BB200_BF16, a_operand, (uint64_t)k, (uint64_t)m, (uint64_t)m * 2, BK, 64, 3)
@@ -639,32 +715,58 @@ int launch_single(const void* a_operand, const void* b, const Destinations& dst,
     if (int status = check_runtime(cudaFuncSetAttribute(gemm_abt_kernel<OutT, A_MN, B_MN, TN>, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_BYTES),
                                    "cudaFuncSetAttribute(gemm smem)"))
       return status;
+    if (int status = check_runtime(cudaFuncSetAttribute(gemm_abt_kernel<float, A_MN, B_MN, TN>, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_BYTES),
+                                   "cudaFuncSetAttribute(gemm smem)"))
+      return status;
     configured[device] = true;
   }
   const int tiles = ((m + BM - 1) / BM) * ((n + TN - 1) / TN);
+  const int k_blocks = (k + BK - 1) / BK;
+  const int splits = may_split ? split_k_count(tiles, k_blocks, sms) : 1;
+  if (splits > 1) {
+    const int kb_per_split = (k_blocks + splits - 1) / splits;
+    const int used_splits = (k_blocks + kb_per_split - 1) / kb_per_split;  // no empty K ranges
+    float* partial = nullptr;
+    if (int status = check_runtime(cudaMallocAsync(reinterpret_cast<void**>(&partial), (size_t)used_splits * m * n * sizeof(float), stream),
+                                   "cudaMallocAsync(gemm split-K workspace)"))
+      return status;
+    const Destinations workspace = single_destination(partial);
+    const int work_items = tiles * used_splits;
+    gemm_abt_kernel<float, A_MN, B_MN, TN><<<work_items < sms ? work_items : sms, THREADS, T::SMEM_BYTES, stream>>>(
+        map_a, map_b, workspace, m, n, k, raster_group_m(), used_splits, kb_per_split, device_status_word());
+    int status = check_launch("gemm split-K kernel launch");
+    if (!status) {
+      const size_t quads = ((size_t)m * n + 3) / 4;
+      split_k_fold_kernel<OutT><<<(unsigned)((quads + 255) / 256), 256, 0, stream>>>(partial, dst, m, n, used_splits);
+      status = check_launch("gemm split-K fold launch");
+    }
+    const int freed = check_runtime(cudaFreeAsync(partial, stream), "cudaFreeAsync(gemm split-K workspace)");
+    return status ? status : freed;
+  }
   const int grid = tiles < sms ? tiles : sms;
-  gemm_abt_kernel<OutT, A_MN, B_MN, TN><<<grid, THREADS, T::SMEM_BYTES, stream>>>(map_a, map_b, dst, m, n, k, raster_group_m(), device_status_word());
+  gemm_abt_kernel<OutT, A_MN, B_MN, TN><<<grid, THREADS, T::SMEM_BYTES, stream>>>(map_a, map_b, dst, m, n, k, raster_group_m(), 1, k_blocks,
+                                                                              device_status_word());
   return check_launch("gemm kernel launch");
 }
 
 template <typename OutT, bool A_MN, bool B_MN>
-int launch_native(const void* a_operand, const void* b, const Destinations& dst, int m, int n, int k, cudaStream_t stream) {
+int launch_native(const void* a_operand, const void* b, const Destinations& dst, int m, int n, int k, bool may_split, cudaStream_t stream) {
   const int device = current_device();
   if (device < 0) return fail(BB200_E_NO_DRIVER, "gemm: no CUDA device is current");
   const int sms = cached_sm_count(device);
   if (sms <= 0) return fail(BB200_E_NO_DRIVER, "gemm: could not query the SM count");
   if (use_pair_kernel(m, n, sms)) return launch_pair<OutT, A_MN, B_MN>(a_operand, b, dst, m, n, k, device, sms, stream);
   switch (single_cta_tile_n(m, n, sms)) {
-    case 256: return launch_single<OutT, A_MN, B_MN, 256>(a_operand, b, dst, m, n, k, device, sms, stream);
-    case 128: return launch_single<OutT, A_MN, B_MN, 128>(a_operand, b, dst, m, n, k, device, sms, stream);
-    default: return launch_single<OutT, A_MN, B_MN, 64>(a_operand, b, dst, m, n, k, device, sms, stream);
+    case 256: return launch_single<OutT, A_MN, B_MN, 256>(a_operand, b, dst, m, n, k, device, sms, may_split, stream);
+    case 128: return launch_single<OutT, A_MN, B_MN, 128>(a_operand, b, dst, m, n, k, device, sms, may_split, stream);
+    default: return launch_single<OutT, A_MN, B_MN, 64>(a_operand, b, dst, m, n, k, device, sms, may_split, stream);
   }
 }
 
 int dispatch_native(const void* a_operand, const void* b, const Destinations& dst, int m, int n, int k, bool a_is_km, bool b_is_kn,
-                    bb200_dtype c_dtype, cudaStream_t s) {
+                    bb200_dtype c_dtype, bool may_split, cudaStream_t s) {
 #define BB200_GEMM_CASE(OUT, A_MN, B_MN) \
-  if (a_is_km == A_MN && b_is_kn == B_MN) return launch_native<OUT, A_MN, B_MN>(a_operand, b, dst, m, n, k, s)
+  if (a_is_km == A_MN && b_is_kn == B_MN) return launch_native<OUT, A_MN, B_MN>(a_operand, b, dst, m, n, k, may_split, s)
   if (c_dtype == BB200_BF16) {
     BB200_GEMM_CASE(__nv_bfloat16, false, false);
     BB200_GEMM_CASE(__nv_bfloat16, false, true);
@@ -678,14 +780,6 @@ int dispatch_native(const void* a_operand, const void* b, const Destinations& ds
   }
 #undef BB200_GEMM_CASE
   return fail(BB200_E_INVALID_ARGUMENT, "gemm: unreachable operand layout");
-}
-
-Destinations single_destination(void* c) {
-  Destinations dst = {};
-  dst.p[0] = c;
-  dst.count = 1;
-  dst.row_offset = 0;
-  return dst;
 }
 
 }  // namespace
@@ -717,7 +811,7 @@ static int gemm_bf16_into(const void* a, const void* b, const Destinations& dest
     }
     a_operand = workspace;
   }
-  int status = dispatch_native(a_operand, b, destinations, m, n, k, a_in_place, b_is_kn, c_dtype, s);
+  int status = dispatch_native(a_operand, b, destinations, m, n, k, a_in_place, b_is_kn, c_dtype, /*may_split=*/true, s);
   if (workspace) {
     const int freed = check_runtime(cudaFreeAsync(workspace, s), "cudaFreeAsync(gemm workspace)");
     if (!status) status = freed;
@@ -810,5 +904,5 @@ extern "C" int bb200_gemm_bf16_noalloc(const void* a, const void* b, void* c, in
     if (int status = launch_transpose(a, scratch, k, m, s)) return status;
     a_operand = scratch;
   }
-  return dispatch_native(a_operand, b, single_destination(c), m, n, k, a_in_place, b_is_kn, c_dtype, s);
+  return dispatch_native(a_operand, b, single_destination(c), m, n, k, a_in_place, b_is_kn, c_dtype, /*may_split=*/false, s);
 }

@@ -215,7 +215,8 @@ int bb200_layernorm(bb200_dtype dtype, const void* x, const void* residual, cons
  * A, B bf16 row-major as stored ([m,k] or [k,m]; [k,n] or [n,k]); C row-major [m, n] of
  * c_dtype bf16 or f32; fp32 accumulation on tcgen05 tensor cores; C is overwritten.  Every layout is
  * read in place except A stored [k, m] with m not a multiple of 8, which is first transposed into a
- * stream-ordered workspace taken from the driver.
+ * stream-ordered workspace taken from the driver.  Problems with few output tiles and a deep k are split along k
+ * into fp32 partial products (a second stream-ordered workspace of at most 16 * m * n floats) that a second kernel folds.
  * Replaces launch_<kernel> of the GEMM template (src/baybridge/backends/hipkittens_exec.py:
  * 994-1044; semantics src/baybridge/frontend.py:3684-3716). */
 int bb200_gemm_bf16(const void* a, const void* b, void* c, int m, int n, int k, int transpose_a, int transpose_b,
@@ -227,7 +228,8 @@ int bb200_gemm_bf16(const void* a, const void* b, void* c, int m, int n, int k, 
  * allocation stalling or failing late.  bb200_gemm_bf16 takes a stream-ordered workspace from the
  * driver when A is stored [k, m] with m not a multiple of 8; this entry point puts that transposed
  * copy of A into a 32 MiB buffer built into the library instead, and performs no cudaMalloc /
- * cudaFree / pool operation of any kind.  Limits and rules:
+ * cudaFree / pool operation of any kind; it also never splits a problem along k (that needs a workspace), so small
+ * outputs with a deep k run as one work item per tile.  Limits and rules:
  *   - with transpose_a != 0 and m % 8 != 0, m*k must not exceed 16,777,216 elements (32 MiB of bf16);
  *     larger requests return BB200_E_TOO_LARGE.  In every other case the buffer is not used and any
  *     size is accepted.

@@ -59,7 +59,8 @@ def test_fan_out_refuses_in_place_and_non_flat_kernels(zoo):
                     destinations={2: [t.data_ptr()]}, shard_index=0)
 
 
-@pytest.mark.parametrize("m,n,k,c_dtype", [(256, 512, 128, "bf16"), (200, 136, 72, "f32"), (2560, 2048, 136, "bf16")])
+@pytest.mark.parametrize("m,n,k,c_dtype", [(256, 512, 128, "bf16"), (200, 136, 72, "f32"), (2560, 2048, 136, "bf16"),
+                                          (128, 256, 2048, "bf16")])  # the last one is split along K and folded into both copies
 def test_gemm_epilogue_stores_its_row_block_into_every_destination(m, n, k, c_dtype, zoo):
     """bb200_gemm_bf16_gather with two local destination buffers standing in for two GPUs' copies of C."""
     import torch

@@ -48,6 +48,9 @@ def test_compiled_gemm_matches_upstream_vectors(case, zoo, tmp_path):
     (256, 8192, 512),    # 128 tiles of 128 columns fit one wave: the 128-column kernel
     (512, 8192, 256),    # 64 pair tiles: the CTA-pair kernel at less than one wave
     (384, 4096, 128),    # three row blocks (no pairs), 192 tiles of 64 columns would not fit: 128 columns
+    (512, 512, 4096),    # 32 narrow tiles, deep K: four K-splits folded by the second kernel
+    (200, 136, 2048),    # K-split with ragged tiles
+    (100, 50, 1024),     # K-split whose rows are not 16-byte multiples (element-wise fold)
 ])
 @pytest.mark.parametrize("c_dtype", ["bf16", "f32"])
 def test_c_abi_gemm_abt_shapes(m, n, k, c_dtype):
@@ -73,6 +76,7 @@ def test_c_abi_gemm_abt_shapes(m, n, k, c_dtype):
     (2560, 2048, 136),   # enough 256x256 tiles for the CTA-pair kernel
     (128, 34816, 72),    # 136 full-width tiles in one row block: the 256-column single-CTA kernel
     (256, 8192, 72),     # the 128-column single-CTA kernel
+    (160, 264, 1096),    # two K-splits, the last k-block ragged
 ])
 def test_c_abi_gemm_transpose_variants_agree(m, n, k):
     from baybridge_b200.backend import native
