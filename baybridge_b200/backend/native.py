@@ -146,6 +146,7 @@ PROTOTYPES: dict[str, list[Any]] = {
     "bb200_elementwise_mul_add": [I, P, P, P, Z, P],
     "bb200_rmsnorm": [I, P, P, P, Z, Z, I, ctypes.c_float, P],
     "bb200_layernorm": [I, P, P, P, P, P, P, Z, Z, I, I, ctypes.c_float, P],
+    "bb200_layernorm_gather": [I, P, P, P, P, ctypes.POINTER(P), ctypes.POINTER(P), I, Z, Z, Z, I, I, ctypes.c_float, P],
     "bb200_gemm_bf16": [P, P, P, I, I, I, I, I, I, P],
     "bb200_gemm_bf16_noalloc": [P, P, P, I, I, I, I, I, I, P],
     "bb200_rmsnorm_gather": [I, P, P, ctypes.POINTER(P), I, Z, Z, Z, I, ctypes.c_float, P],

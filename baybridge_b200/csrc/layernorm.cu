@@ -28,16 +28,31 @@ template <int THREADS> __device__ __forceinline__ float block_sum(float v, float
   return warp_sum(total);
 }
 
-template <typename T, int THREADS, int VPT>
+// Where the two outputs go.  Ordinarily one pair of tensors.  In the gather form this GPU's rows are the block starting at
+// `row_offset` of taller tensors of which every GPU of the box holds a copy: each output vector is stored into all
+// `count` copies (its own and, through peer-mapped pointers, the others').
+constexpr int kMaxDestinations = 8;
+struct LayerNormDestinations {
+  void* out[kMaxDestinations];
+  void* out_resid[kMaxDestinations];
+  int count;
+  size_t row_offset;
+};
+
+// GATHER = false keeps one unconditional store per output vector (a loop over destinations there costs bandwidth).
+template <typename T, int THREADS, int VPT, bool GATHER>
 __global__ void __launch_bounds__(THREADS)
 layernorm_rows(const T* __restrict__ x, const T* __restrict__ residual, const T* __restrict__ weight, const T* __restrict__ bias,
-               T* __restrict__ out, T* __restrict__ out_resid, size_t rows, int hidden, size_t weight_row_stride,
+               const __grid_constant__ LayerNormDestinations dst, size_t rows, int hidden, size_t weight_row_stride,
                size_t bias_row_stride, float epsilon) {
   constexpr int VEC = 16 / sizeof(T);
+  T* __restrict__ out = static_cast<T*>(dst.out[0]);
+  T* __restrict__ out_resid = static_cast<T*>(dst.out_resid[0]);
   __shared__ float scratch[32];
   const size_t row = blockIdx.x;
   if (row >= rows) return;
   const size_t offset = row * (size_t)hidden;
+  const size_t out_offset = (row + dst.row_offset) * (size_t)hidden;
   const int nvec = hidden / VEC;
   float mixed[VPT][VEC];
   float sum = 0.0f;
@@ -63,7 +78,11 @@ layernorm_rows(const T* __restrict__ x, const T* __restrict__ residual, const T*
           sum += mixed[j][e];
           r.v[e] = Conv<float, T>::narrow(mixed[j][e]);
         }
-        store_stream<T, VEC>(out_resid + offset + (size_t)v * VEC, r);
+        if constexpr (GATHER) {
+          for (int d = 0; d < dst.count; ++d) store_stream<T, VEC>(static_cast<T*>(dst.out_resid[d]) + out_offset + (size_t)v * VEC, r);
+        } else {
+          store_stream<T, VEC>(out_resid + out_offset + (size_t)v * VEC, r);
+        }
       }
     }
   }
@@ -93,30 +112,39 @@ layernorm_rows(const T* __restrict__ x, const T* __restrict__ residual, const T*
 #pragma unroll
       for (int e = 0; e < VEC; ++e)
         o.v[e] = Conv<float, T>::narrow((mixed[j][e] - mean) * inv_std * Conv<float, T>::widen(w.v[e]) + Conv<float, T>::widen(b.v[e]));
-      store_stream<T, VEC>(out + offset + (size_t)v * VEC, o);
+      if constexpr (GATHER) {
+        for (int d = 0; d < dst.count; ++d) store_stream<T, VEC>(static_cast<T*>(dst.out[d]) + out_offset + (size_t)v * VEC, o);
+      } else {
+        store_stream<T, VEC>(out + out_offset + (size_t)v * VEC, o);
+      }
     }
   }
 }
 
 template <typename T, int THREADS, int VPT>
-int launch(const void* x, const void* residual, const void* weight, const void* bias, void* out, void* out_resid, size_t rows,
+int launch(const void* x, const void* residual, const void* weight, const void* bias, const LayerNormDestinations& dst, size_t rows,
            size_t hidden, int weight_is_full, int bias_is_full, float epsilon, cudaStream_t stream) {
-  layernorm_rows<T, THREADS, VPT><<<(unsigned)rows, THREADS, 0, stream>>>(
-      static_cast<const T*>(x), static_cast<const T*>(residual), static_cast<const T*>(weight), static_cast<const T*>(bias),
-      static_cast<T*>(out), static_cast<T*>(out_resid), rows, (int)hidden, weight_is_full ? hidden : 0, bias_is_full ? hidden : 0,
-      epsilon);
+  if (dst.count == 1 && dst.row_offset == 0) {
+    layernorm_rows<T, THREADS, VPT, false><<<(unsigned)rows, THREADS, 0, stream>>>(
+        static_cast<const T*>(x), static_cast<const T*>(residual), static_cast<const T*>(weight), static_cast<const T*>(bias), dst,
+        rows, (int)hidden, weight_is_full ? hidden : 0, bias_is_full ? hidden : 0, epsilon);
+  } else {
+    layernorm_rows<T, THREADS, VPT, true><<<(unsigned)rows, THREADS, 0, stream>>>(
+        static_cast<const T*>(x), static_cast<const T*>(residual), static_cast<const T*>(weight), static_cast<const T*>(bias), dst,
+        rows, (int)hidden, weight_is_full ? hidden : 0, bias_is_full ? hidden : 0, epsilon);
+  }
   return check_launch("layernorm kernel launch");
 }
 
 template <typename T>
-int dispatch(const void* x, const void* residual, const void* weight, const void* bias, void* out, void* out_resid, size_t rows,
+int dispatch(const void* x, const void* residual, const void* weight, const void* bias, const LayerNormDestinations& dst, size_t rows,
              size_t hidden, int weight_is_full, int bias_is_full, float epsilon, cudaStream_t stream) {
   constexpr size_t VEC = 16 / sizeof(T);
   if (hidden % VEC) return fail(BB200_E_UNSUPPORTED_SHAPE, "layernorm: hidden=%zu must be a multiple of %zu", hidden, VEC);
   const size_t nvec = hidden / VEC;
 #define BB200_LN(THREADS, VPT) \
   if (nvec <= (size_t)(THREADS) * (VPT)) \
-    return launch<T, THREADS, VPT>(x, residual, weight, bias, out, out_resid, rows, hidden, weight_is_full, bias_is_full, epsilon, stream)
+    return launch<T, THREADS, VPT>(x, residual, weight, bias, dst, rows, hidden, weight_is_full, bias_is_full, epsilon, stream)
   BB200_LN(32, 1);
   BB200_LN(64, 1);
   BB200_LN(128, 1);
@@ -135,19 +163,51 @@ int dispatch(const void* x, const void* residual, const void* weight, const void
 
 using namespace bb200;
 
+static int layernorm_into(bb200_dtype dtype, const void* x, const void* residual, const void* weight, const void* bias,
+                          const LayerNormDestinations& dst, size_t rows, size_t hidden, int weight_is_full, int bias_is_full,
+                          float epsilon, void* stream) {
+  if (!x || !residual || !weight || !bias) return fail(BB200_E_INVALID_ARGUMENT, "layernorm: null tensor pointer");
+  if (rows == 0 || hidden == 0) return fail(BB200_E_INVALID_ARGUMENT, "layernorm: rows and hidden must be > 0");
+  if (rows > 0x7fffffffu || hidden > 0x7fffffffu) return fail(BB200_E_UNSUPPORTED_SHAPE, "layernorm: extent exceeds 2^31-1");
+  for (const void* p : {x, residual, weight, bias})
+    if (!aligned16(p)) return fail(BB200_E_MISALIGNED, "layernorm: all tensors must be 16-byte aligned");
+  for (int d = 0; d < dst.count; ++d) {
+    if (!dst.out[d] || !dst.out_resid[d]) return fail(BB200_E_INVALID_ARGUMENT, "layernorm: null tensor pointer");
+    if (!aligned16(dst.out[d]) || !aligned16(dst.out_resid[d])) return fail(BB200_E_MISALIGNED, "layernorm: all tensors must be 16-byte aligned");
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case BB200_BF16: return dispatch<__nv_bfloat16>(x, residual, weight, bias, dst, rows, hidden, weight_is_full, bias_is_full, epsilon, s);
+    case BB200_F16: return dispatch<__half>(x, residual, weight, bias, dst, rows, hidden, weight_is_full, bias_is_full, epsilon, s);
+    case BB200_F32: return dispatch<float>(x, residual, weight, bias, dst, rows, hidden, weight_is_full, bias_is_full, epsilon, s);
+    default: return fail(BB200_E_INVALID_ARGUMENT, "layernorm: dtype %d is not bf16/f16/f32", (int)dtype);
+  }
+}
+
 extern "C" int bb200_layernorm(bb200_dtype dtype, const void* x, const void* residual, const void* weight, const void* bias,
                                void* out, void* out_resid, size_t rows, size_t hidden, int weight_is_full, int bias_is_full,
                                float epsilon, void* stream) {
-  if (!x || !residual || !weight || !bias || !out || !out_resid) return fail(BB200_E_INVALID_ARGUMENT, "layernorm: null tensor pointer");
-  if (rows == 0 || hidden == 0) return fail(BB200_E_INVALID_ARGUMENT, "layernorm: rows and hidden must be > 0");
-  if (rows > 0x7fffffffu || hidden > 0x7fffffffu) return fail(BB200_E_UNSUPPORTED_SHAPE, "layernorm: extent exceeds 2^31-1");
-  for (const void* p : {x, residual, weight, bias, (const void*)out, (const void*)out_resid})
-    if (!aligned16(p)) return fail(BB200_E_MISALIGNED, "layernorm: all tensors must be 16-byte aligned");
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  switch (dtype) {
-    case BB200_BF16: return dispatch<__nv_bfloat16>(x, residual, weight, bias, out, out_resid, rows, hidden, weight_is_full, bias_is_full, epsilon, s);
-    case BB200_F16: return dispatch<__half>(x, residual, weight, bias, out, out_resid, rows, hidden, weight_is_full, bias_is_full, epsilon, s);
-    case BB200_F32: return dispatch<float>(x, residual, weight, bias, out, out_resid, rows, hidden, weight_is_full, bias_is_full, epsilon, s);
-    default: return fail(BB200_E_INVALID_ARGUMENT, "layernorm: dtype %d is not bf16/f16/f32", (int)dtype);
+  LayerNormDestinations single = {};
+  single.out[0] = out;
+  single.out_resid[0] = out_resid;
+  single.count = 1;
+  single.row_offset = 0;
+  return layernorm_into(dtype, x, residual, weight, bias, single, rows, hidden, weight_is_full, bias_is_full, epsilon, stream);
+}
+
+extern "C" int bb200_layernorm_gather(bb200_dtype dtype, const void* x, const void* residual, const void* weight, const void* bias,
+                                      void* const* out_destinations, void* const* out_resid_destinations, int destination_count,
+                                      size_t row_offset, size_t rows, size_t hidden, int weight_is_full, int bias_is_full,
+                                      float epsilon, void* stream) {
+  if (!out_destinations || !out_resid_destinations || destination_count < 1 || destination_count > kMaxDestinations)
+    return fail(BB200_E_INVALID_ARGUMENT, "layernorm (gather): 1..%d destination buffers are needed (got %d)", kMaxDestinations,
+                destination_count);
+  LayerNormDestinations all = {};
+  for (int d = 0; d < destination_count; ++d) {
+    all.out[d] = out_destinations[d];
+    all.out_resid[d] = out_resid_destinations[d];
   }
+  all.count = destination_count;
+  all.row_offset = row_offset;
+  return layernorm_into(dtype, x, residual, weight, bias, all, rows, hidden, weight_is_full, bias_is_full, epsilon, stream);
 }

@@ -137,6 +137,66 @@ class FusedGatherRmsNorm:
                     self.row_offset, plan.rows, plan.hidden, 1 if plan.gamma_is_full else 0, plan.epsilon, native.stream_handle(stream))
 
 
+class FusedGatherLayerNorm:
+    """LayerNorm (with its fused residual add) whose two outputs are all-gathered by the kernel itself
+    (``bb200_layernorm_gather``).  ``over_group`` returns ``(fused, (out_full, out_resid_full))``."""
+
+    def __init__(self, kernel: Any, sample_args: Sequence[Any], *, out_destinations: Sequence[int],
+                 out_resid_destinations: Sequence[int], shard_index: int):
+        definition = _normalize_kernel(kernel)
+        self.ir = trace(definition, tuple(normalize_runtime_argument(arg) for arg in sample_args))
+        plan = match(self.ir)
+        if plan.kind != "layernorm":
+            raise BackendNotImplementedError("FusedGatherLayerNorm needs a kernel that lowers to LayerNorm")
+        if not 1 <= len(out_destinations) <= MAX_FANOUT or len(out_destinations) != len(out_resid_destinations):
+            raise ValueError("1..8 destination buffers are needed, as many for out_resid as for out")
+        self.plan = plan
+        self.row_offset = int(shard_index) * plan.rows
+        self._out_table = (ctypes.c_void_p * len(out_destinations))(*[int(pointer) for pointer in out_destinations])
+        self._resid_table = (ctypes.c_void_p * len(out_resid_destinations))(*[int(pointer) for pointer in out_resid_destinations])
+        self._count = len(out_destinations)
+
+    @classmethod
+    def over_group(cls, kernel: Any, sample_args: Sequence[Any], *, group=None):
+        import torch
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symmetric
+
+        group = group or dist.group.WORLD
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        if world > MAX_FANOUT:
+            raise BackendNotImplementedError(f"FusedGatherLayerNorm fans out to at most {MAX_FANOUT} ranks")
+        plan = cls(kernel, sample_args, out_destinations=[1], out_resid_destinations=[1], shard_index=0).plan  # trace + match only
+        dtype = {"bf16": torch.bfloat16, "f16": torch.float16, "f32": torch.float32}[plan.dtype]
+        device = torch.device("cuda", torch.cuda.current_device())
+        out_full = symmetric.empty((world * plan.rows, plan.hidden), dtype=dtype, device=device)
+        resid_full = symmetric.empty((world * plan.rows, plan.hidden), dtype=dtype, device=device)
+        out_handle = symmetric.rendezvous(out_full, group)
+        resid_handle = symmetric.rendezvous(resid_full, group)
+        fused = cls(kernel, sample_args, out_destinations=[int(pointer) for pointer in out_handle.buffer_ptrs],
+                    out_resid_destinations=[int(pointer) for pointer in resid_handle.buffer_ptrs], shard_index=rank)
+        fused._handle = out_handle
+        fused._resid_handle = resid_handle
+        return fused, (out_full, resid_full)
+
+    def barrier(self) -> None:
+        handle = getattr(self, "_handle", None)
+        if handle is not None:
+            handle.barrier()  # follows every store of the launch on the stream, so it orders both tensors
+
+    def run(self, x: Any, residual: Any, weight: Any, bias: Any, *, stream: Any = None) -> None:
+        plan = self.plan
+        native.require_device()
+        pointers = []
+        for value in (x, residual, weight, bias):
+            if not hasattr(value, "data_ptr"):
+                value = normalize_runtime_argument(value)
+            pointers.append(ctypes.c_void_p(int(value.data_ptr() or getattr(value, "raw_address", 0))))
+        native.call("bb200_layernorm_gather", native.DTYPE_CODES[plan.dtype], *pointers, self._out_table, self._resid_table, self._count,
+                    self.row_offset, plan.rows, plan.hidden, 1 if plan.weight_is_full else 0, 1 if plan.bias_is_full else 0,
+                    plan.epsilon, native.stream_handle(stream))
+
+
 class FusedGatherAttention:
     """Attention forward with the all-gather of ``out`` and ``lse`` fused into the kernel's epilogue
     (``bb200_attention_fwd_gather``): every rank attends over its own sequences and stores each finished output

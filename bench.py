@@ -563,6 +563,34 @@ class LayerNorm(Workload):
 
         self.pipeline = HostPipeline(lambda rows: zoo.layernorm_kernel, self.host, chunks=E2E_CHUNKS, cache_dir=cache_dir)
 
+    def fused_gather_ms(self, torch, dist, cute, zoo, barrier) -> float | None:
+        """LayerNorm with the all-gather of out and out_resid fused into the kernel (peer stores of every vector), then one
+        barrier.  The separate NCCL figure next to it gathers `out` alone."""
+        from baybridge_b200.fused_gather import FusedGatherLayerNorm
+
+        fused, (out_full, resid_full) = FusedGatherLayerNorm.over_group(
+            zoo.layernorm_kernel, [self.x, self.residual, self.out, self.out_resid, self.w, self.b])
+        stream = torch.cuda.current_stream().cuda_stream
+        for _ in range(3):
+            fused.run(self.x, self.residual, self.w, self.b, stream=stream)
+            fused.barrier()
+        barrier()
+        reference, reference_resid = torch.empty_like(out_full), torch.empty_like(resid_full)
+        dist.all_gather_into_tensor(reference, self.out)
+        dist.all_gather_into_tensor(reference_resid, self.out_resid)
+        if not (torch.equal(out_full, reference) and torch.equal(resid_full, reference_resid)):
+            raise RuntimeError("fused LayerNorm + gather differs from LayerNorm followed by the NCCL all-gather")
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 10
+        barrier()
+        begin.record()
+        for _ in range(reps):
+            fused.run(self.x, self.residual, self.w, self.b, stream=stream)
+            fused.barrier()
+        end.record()
+        barrier()
+        return begin.elapsed_time(end) / reps
+
     def config(self):
         return {"workload": f"layernorm with residual add, bf16 [{self.rows}, {self.hidden}] per GPU, weight/bias [{self.hidden}], eps 1e-5",
                 "l2": "working set 2.1 GB > 126 MB L2, no flush"}

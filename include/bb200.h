@@ -211,6 +211,17 @@ int bb200_layernorm(bb200_dtype dtype, const void* x, const void* residual, cons
                     void* out_resid, size_t rows, size_t hidden, int weight_is_full, int bias_is_full, float epsilon,
                     void* stream);
 
+/* bb200_layernorm fused with the all-gather of both outputs across the GPUs of one box: this GPU's rows are the block
+ * starting at `row_offset` of taller out / out_resid tensors of which every GPU holds a copy, and every output vector
+ * is stored into all `destination_count` (1..8) copies (own buffers or peer-mapped pointers; ordinary 16-byte stores
+ * over NVLink).  The caller still needs a barrier across the GPUs before the gathered tensors are read.  Other
+ * arguments as bb200_layernorm.  No upstream counterpart (upstream is single-device:
+ * src/baybridge/backends/cuda_driver.py:292-300). */
+int bb200_layernorm_gather(bb200_dtype dtype, const void* x, const void* residual, const void* weight, const void* bias,
+                           void* const* out_destinations, void* const* out_resid_destinations, int destination_count,
+                           size_t row_offset, size_t rows, size_t hidden, int weight_is_full, int bias_is_full,
+                           float epsilon, void* stream);
+
 /* C[m, n] = sum_k A'[m, k] * B'[k, n]; A' = A or A^T, B' = B or B^T per the transpose flags;
  * A, B bf16 row-major as stored ([m,k] or [k,m]; [k,n] or [n,k]); C row-major [m, n] of
  * c_dtype bf16 or f32; fp32 accumulation on tcgen05 tensor cores; C is overwritten.  Every layout is

@@ -148,3 +148,35 @@ def test_attention_stores_its_sequences_into_every_destination(batch, seq, heads
     artifact = cute.compile(kernel, d_q, d_k, d_v, sample_out, sample_lse, backend="b200")
     artifact(d_q, d_k, d_v, sample_out, sample_lse)
     assert torch.equal(outs[0][mine_rows], sample_out) and torch.equal(lses[0][mine_rows], sample_lse)
+
+
+@pytest.mark.parametrize("dtype,rows,hidden", [("bf16", 16, 8192), ("f32", 6, 1020), ("f16", 33, 2048)])
+def test_layernorm_stores_both_outputs_into_every_destination(dtype, rows, hidden, zoo):
+    import torch
+
+    from baybridge_b200.fused_gather import FusedGatherLayerNorm
+
+    rng = np.random.default_rng(rows * 7 + hidden)
+    x = oracle.round_to_dtype(rng.standard_normal((rows, hidden)), dtype)
+    r = oracle.round_to_dtype(rng.standard_normal((rows, hidden)), dtype)
+    w = oracle.round_to_dtype(1 + 0.1 * rng.standard_normal(hidden), dtype)
+    b = oracle.round_to_dtype(0.1 * rng.standard_normal(hidden), dtype)
+    d_x, d_r, d_w, d_b = (to_device(t, dtype) for t in (x, r, w, b))
+    torch_dtype = {"bf16": torch.bfloat16, "f16": torch.float16, "f32": torch.float32}[dtype]
+    blocks, mine = 3, 1
+    outs = [torch.full((blocks * rows, hidden), -3.0, device="cuda", dtype=torch_dtype) for _ in range(2)]
+    resids = [torch.full((blocks * rows, hidden), -3.0, device="cuda", dtype=torch_dtype) for _ in range(2)]
+    sample = torch.zeros((rows, hidden), device="cuda", dtype=torch_dtype)
+    fused = FusedGatherLayerNorm(zoo.layernorm_kernel, [d_x, d_r, sample, sample.clone(), d_w, d_b],
+                                 out_destinations=[t.data_ptr() for t in outs], out_resid_destinations=[t.data_ptr() for t in resids],
+                                 shard_index=mine)
+    fused.run(d_x, d_r, d_w, d_b)
+    torch.cuda.synchronize()
+    ref_out, ref_mixed = oracle.layernorm(x, r, w, b, 1e-5)
+    block = slice(mine * rows, (mine + 1) * rows)
+    for out, resid in zip(outs, resids):
+        host_out, host_resid = to_host(out), to_host(resid)
+        assert oracle.rel_l2(host_out[block], ref_out) <= (2e-3 if dtype != "f32" else 2e-6)
+        assert np.array_equal(host_resid[block], oracle.round_to_dtype(ref_mixed, dtype))
+        assert np.all(np.delete(host_out, block, axis=0) == -3.0) and np.all(np.delete(host_resid, block, axis=0) == -3.0)
+    assert torch.equal(outs[0], outs[1]) and torch.equal(resids[0], resids[1])
