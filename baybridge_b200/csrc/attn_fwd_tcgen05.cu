@@ -6,11 +6,13 @@
 // rows are `heads*head_dim` elements apart; TMA reads it through a 3-D map (head_dim*heads, seq,
 // batch) and zero-fills rows past `seq`.
 //
-// One CTA handles TWO 128-query tiles of one (batch, head) and walks the key/value blocks of 128
-// keys once for both (only blocks at or below the diagonal when causal).  384 threads in three
+// A work item is TWO 128-query tiles of one (batch, head), for which the key/value blocks of 128 keys
+// are walked once (only blocks at or below the diagonal when causal).  The kernel is persistent: one CTA
+// per SM draws items from a counter in global memory until none is left.  384 threads in three
 // warpgroups; warpgroup 0 gives registers back (setmaxnreg) so the softmax warpgroups can hold a
 // full 128-column score row per thread:
-//   warp 0       TMA producer: both Q tiles once, then K and V blocks into a 2-stage ring.
+//   warp 0       work distributor and TMA producer: fetches the next item, hands it to the other warps
+//                through a two-slot ring, loads both Q tiles, then K and V blocks into a 2-stage ring.
 //   warp 1       MMA issuer (one elected thread).  Per tile t and block j:  S_t = Q_t·K_j^T  into TMEM
 //                (both operands K-major in shared memory), later  O_t += P_t·V_j  with P_t read from
 //                TMEM and V_j consumed in place as an MN-major shared-memory operand.  The issue order
@@ -26,6 +28,8 @@
 // Head dims other than 64/128 use a plain SIMT kernel below.
 #include <cuda_bf16.h>
 #include <math.h>
+
+#include <atomic>
 
 #include "bb200_internal.h"
 #include "bb200_sm100.cuh"
@@ -43,7 +47,7 @@ constexpr int SUBTILE_BYTES = 128 * 128;   // [128 rows, 64 bf16] with 128-byte 
 constexpr float RESCALE_THRESHOLD = 8.0f;  // in log2 units: p stays below 2^8 between rescales
 
 enum WaitCode { kWaitQ = 201, kWaitKvEmpty = 202, kWaitK = 203, kWaitV = 204, kWaitSReady = 205, kWaitPReady = 206,
-                kWaitODone = 207 };
+                kWaitODone = 207, kWaitItem = 208, kWaitOFree = 209 };
 
 template <int D> struct Smem {
   static constexpr int DCH = D / 64;                       // 64-column sub-tiles per row block
@@ -84,45 +88,69 @@ struct OutputDestinations {
 // GATHER = true: rows are staged in the (by then unused) shared memory of the tile's Q and leave as whole
 // contiguous rows, sixteen (or eight) lanes per row, into every destination — 16-byte pieces of 32 different rows
 // per store instruction would waste most of an NVLink packet.
+//
+// The kernel is persistent: one CTA per SM takes work items — a pair of query tiles of one (batch, head) — from a
+// counter in global memory until it runs dry, so the loads and the first Q·K^T of the next item overlap the last
+// softmax, the epilogue and the stores of the current one, and TMEM, barriers and the register hand-over are set up
+// once per SM.  Items are numbered (batch, head)-major with the longest causal pair first inside each (batch, head), so
+// the CTAs that run together mostly share one head's keys and values in L2.  The producer warp fetches an item index
+// and hands it to the other warps through a two-slot ring; every barrier parity follows running counters.
 template <int D, bool CAUSAL, bool GATHER>
 __global__ void __launch_bounds__(THREADS, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                 const __grid_constant__ CUtensorMap map_v, const __grid_constant__ OutputDestinations dst,
-                int seq, int heads, int kv_heads, float scale_log2e, int* status_word) {
+                int seq, int heads, int kv_heads, int batches, float scale_log2e, int* work_counter, int* status_word) {
   using L = Smem<D>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_addr(smem_raw) + 1023u) & ~1023u;
   uint8_t* aligned = smem_raw + (base - smem_addr(smem_raw));
   const uint32_t bar_base = base + L::BAR_OFF;
-  // barriers: q_full, k_full[2], v_full[2], kv_empty[2], s_ready[2], p_ready[2 tiles][2 halves], o_done[2]
-  const uint32_t q_full = bar_base;
-  auto k_full = [&](int s) { return bar_base + 8u * (1 + s); };
-  auto v_full = [&](int s) { return bar_base + 8u * (3 + s); };
-  auto kv_empty = [&](int s) { return bar_base + 8u * (5 + s); };
-  auto s_ready = [&](int t) { return bar_base + 8u * (7 + t); };
-  auto p_ready = [&](int t, int half) { return bar_base + 8u * (9 + 2 * t + half); };
-  auto o_done = [&](int t) { return bar_base + 8u * (13 + t); };
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(aligned + L::BAR_OFF + 8 * 15);
+  // barriers: q_full, q_free, k_full[2], v_full[2], kv_empty[2], s_ready[2], p_ready[2 tiles][2 halves], o_done[2],
+  // o_free[2], item_full[2], item_empty[2]
+  const uint32_t q_full = bar_base, q_free = bar_base + 8u;
+  auto k_full = [&](int s) { return bar_base + 8u * (2 + s); };
+  auto v_full = [&](int s) { return bar_base + 8u * (4 + s); };
+  auto kv_empty = [&](int s) { return bar_base + 8u * (6 + s); };
+  auto s_ready = [&](int t) { return bar_base + 8u * (8 + t); };
+  auto p_ready = [&](int t, int half) { return bar_base + 8u * (10 + 2 * t + half); };
+  auto o_done = [&](int t) { return bar_base + 8u * (14 + t); };
+  auto o_free = [&](int t) { return bar_base + 8u * (16 + t); };
+  auto item_full = [&](int s) { return bar_base + 8u * (18 + s); };
+  auto item_empty = [&](int s) { return bar_base + 8u * (20 + s); };
+  constexpr int BARRIERS = 22;
+  volatile int* item_slot = reinterpret_cast<volatile int*>(aligned + L::BAR_OFF + 8 * BARRIERS);  // two entries
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(aligned + L::BAR_OFF + 8 * BARRIERS + 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int q_blocks = (seq + BLOCK_M - 1) / BLOCK_M;
   const int pairs = (q_blocks + Q_TILES - 1) / Q_TILES;
-  const int pair = pairs - 1 - (int)blockIdx.x;  // longest causal rows first
-  const int head = blockIdx.y, batch = blockIdx.z;
-  const int kv_head = head / (heads / kv_heads);
   const int kv_blocks_all = (seq + BLOCK_N - 1) / BLOCK_N;
-  // key/value blocks each query tile needs (0 for a tile that starts past the end of the sequence)
-  int blocks_of[Q_TILES];
+  const int total_items = pairs * heads * batches;
+  const int kv_group = heads / kv_heads;
+
+  // a work item: which pair of query tiles of which (batch, head), and how many key/value blocks each tile needs
+  struct Item {
+    int pair, head, batch, blocks_of[Q_TILES], kv_blocks;
+  };
+  auto decode = [&](int index) {
+    Item item;
+    item.pair = pairs - 1 - index % pairs;  // longest causal rows first
+    const int slice = index / pairs;
+    item.head = slice % heads;
+    item.batch = slice / heads;
 #pragma unroll
-  for (int t = 0; t < Q_TILES; ++t) {
-    const int q_block = pair * Q_TILES + t;
-    blocks_of[t] = q_block >= q_blocks ? 0 : (CAUSAL ? min(q_block + 1, kv_blocks_all) : kv_blocks_all);
-  }
-  const int kv_blocks = max(blocks_of[0], blocks_of[1]);
+    for (int t = 0; t < Q_TILES; ++t) {
+      const int q_block = item.pair * Q_TILES + t;
+      item.blocks_of[t] = q_block >= q_blocks ? 0 : (CAUSAL ? min(q_block + 1, kv_blocks_all) : kv_blocks_all);
+    }
+    item.kv_blocks = max(item.blocks_of[0], item.blocks_of[1]);
+    return item;
+  };
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
+    mbar_init(q_free, GATHER ? 1 + 2 * 4 : 1);  // the MMA issuer's commit, plus every softmax warp when Q doubles as staging
     for (int s = 0; s < KV_STAGES; ++s) {
       mbar_init(k_full(s), 1);
       mbar_init(v_full(s), 1);
@@ -133,6 +161,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       mbar_init(p_ready(t, 0), 4);  // one arrival per softmax warp
       mbar_init(p_ready(t, 1), 4);
       mbar_init(o_done(t), 1);
+      mbar_init(o_free(t), 4);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(item_full(s), 1);
+      mbar_init(item_empty(s), 1 + 2 * 4);  // the MMA issuer and every softmax warp
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -145,36 +178,52 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp < 4) {
-    // warpgroup 0 (TMA, MMA and two idle warps) hands registers to the softmax warpgroups
+    // warpgroup 0 (TMA, MMA and two idle warps) hands registers to the softmax warpgroups.  64 + 216 leaves 2048
+    // registers of the SM's file unclaimed; 80 + 216 claims all of it and the softmax warps' `inc` then never returns.
     asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
   if (warp == 0) {
-    // ---------------- TMA producer ----------------
+    // ---------------- TMA producer and work distributor ----------------
     if (elect_one()) {
       prefetch_tensormap(&map_q);
       prefetch_tensormap(&map_k);
       prefetch_tensormap(&map_v);
-      mbar_arrive_expect_tx(q_full, Q_TILES * L::Q_BYTES);
-#pragma unroll
-      for (int t = 0; t < Q_TILES; ++t)
-#pragma unroll
-        for (int c = 0; c < L::DCH; ++c)
-          tma_load_3d(base + L::Q_OFF + t * L::Q_BYTES + c * SUBTILE_BYTES, &map_q, q_full, head * D + c * 64,
-                      (pair * Q_TILES + t) * BLOCK_M, batch);
       bool ok = true;
-      for (int j = 0; ok && j < kv_blocks; ++j) {
-        const int stage = j & 1;
-        const uint32_t use_parity = (uint32_t)(j >> 1) & 1u;
-        if (!(ok = mbar_wait(kv_empty(stage), use_parity ^ 1u, abort_flag, status_word, kWaitKvEmpty))) break;
-        const uint32_t k_dst = base + L::KV_OFF + stage * (L::K_BYTES + L::V_BYTES);
-        const uint32_t v_dst = k_dst + L::K_BYTES;
-        mbar_arrive_expect_tx(k_full(stage), L::K_BYTES);
+      int kv_count = 0;  // key/value blocks loaded so far: ring stage and parity follow it across items
+      for (int n = 0; ok; ++n) {
+        const int slot = n & 1;
+        // the ring slot is free once the issuer and the softmax warps have finished the item before last
+        if (!(ok = mbar_wait(item_empty(slot), ((uint32_t)(n >> 1) & 1u) ^ 1u, abort_flag, status_word, kWaitItem))) break;
+        int index = atomicAdd(work_counter, 1);
+        if (index >= total_items) index = -1;
+        item_slot[slot] = index;
+        mbar_arrive(item_full(slot));  // release: the slot is written before the arrival is seen
+        if (index < 0) break;
+        const Item item = decode(index);
+        const int kv_head = item.head / kv_group;
+        // Q may be overwritten once the previous item's last Q·K^T (and, in the gather form, its staged rows) are done
+        if (!(ok = mbar_wait(q_free, ((uint32_t)n & 1u) ^ 1u, abort_flag, status_word, kWaitQ))) break;
+        mbar_arrive_expect_tx(q_full, Q_TILES * L::Q_BYTES);
 #pragma unroll
-        for (int c = 0; c < L::DCH; ++c)
-          tma_load_3d(k_dst + c * SUBTILE_BYTES, &map_k, k_full(stage), kv_head * D + c * 64, j * BLOCK_N, batch);
-        mbar_arrive_expect_tx(v_full(stage), L::V_BYTES);
+        for (int t = 0; t < Q_TILES; ++t)
 #pragma unroll
-        for (int c = 0; c < L::DCH; ++c)
-          tma_load_3d(v_dst + c * SUBTILE_BYTES, &map_v, v_full(stage), kv_head * D + c * 64, j * BLOCK_N, batch);
+          for (int c = 0; c < L::DCH; ++c)
+            tma_load_3d(base + L::Q_OFF + t * L::Q_BYTES + c * SUBTILE_BYTES, &map_q, q_full, item.head * D + c * 64,
+                        (item.pair * Q_TILES + t) * BLOCK_M, item.batch);
+        for (int j = 0; ok && j < item.kv_blocks; ++j, ++kv_count) {
+          const int stage = kv_count & 1;
+          const uint32_t use_parity = (uint32_t)(kv_count >> 1) & 1u;
+          if (!(ok = mbar_wait(kv_empty(stage), use_parity ^ 1u, abort_flag, status_word, kWaitKvEmpty))) break;
+          const uint32_t k_dst = base + L::KV_OFF + stage * (L::K_BYTES + L::V_BYTES);
+          const uint32_t v_dst = k_dst + L::K_BYTES;
+          mbar_arrive_expect_tx(k_full(stage), L::K_BYTES);
+#pragma unroll
+          for (int c = 0; c < L::DCH; ++c)
+            tma_load_3d(k_dst + c * SUBTILE_BYTES, &map_k, k_full(stage), kv_head * D + c * 64, j * BLOCK_N, item.batch);
+          mbar_arrive_expect_tx(v_full(stage), L::V_BYTES);
+#pragma unroll
+          for (int c = 0; c < L::DCH; ++c)
+            tma_load_3d(v_dst + c * SUBTILE_BYTES, &map_v, v_full(stage), kv_head * D + c * 64, j * BLOCK_N, item.batch);
+        }
       }
     }
   } else if (warp == 1) {
@@ -182,8 +231,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     if (elect_one()) {
       constexpr uint32_t idesc_qk = umma_idesc_bf16_f32(BLOCK_M, BLOCK_N);
       constexpr uint32_t idesc_pv = umma_idesc_bf16_f32(BLOCK_M, D, false, true);  // V is MN-major
-      auto issue_qk = [&](int t, int j) {  // S_t = Q_t · K_j^T
-        const uint32_t k_src = base + L::KV_OFF + (j & 1) * (L::K_BYTES + L::V_BYTES);
+      auto issue_qk = [&](int t, int stage) {  // S_t = Q_t · K^T with K in ring stage `stage`
+        const uint32_t k_src = base + L::KV_OFF + stage * (L::K_BYTES + L::V_BYTES);
         const uint32_t acc = tmem_base + (uint32_t)(t * BLOCK_N);
 #pragma unroll
         for (int c = 0; c < L::DCH; ++c) {
@@ -196,51 +245,72 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         }
         umma_commit(s_ready(t));
       };
-      // O_t (+)= P_t · V_j over keys [64*half, 64*half+64); P_t is packed bf16 in the first 64 columns of S_t
-      auto issue_pv = [&](int t, int j, int half) {
-        const uint32_t v_src = base + L::KV_OFF + (j & 1) * (L::K_BYTES + L::V_BYTES) + L::K_BYTES;
+      // O_t (+)= P_t · V over keys [64*half, 64*half+64) of the block in ring stage `stage`; P_t is packed bf16 in the
+      // first 64 columns of S_t; `first` = first block of the item (O_t is overwritten, not accumulated)
+      auto issue_pv = [&](int t, int stage, int half, bool first) {
+        const uint32_t v_src = base + L::KV_OFF + stage * (L::K_BYTES + L::V_BYTES) + L::K_BYTES;
         const uint64_t desc_v = umma_desc_mn_major_sw128(v_src, SUBTILE_BYTES);
         const uint32_t p_addr = tmem_base + (uint32_t)(t * BLOCK_N);
         const uint32_t o_addr = tmem_base + 256u + (uint32_t)(t * 128);
 #pragma unroll
         for (int kk = half * 4; kk < half * 4 + 4; ++kk)
           umma_bf16_ts(o_addr, p_addr + (uint32_t)(kk * 8), umma_desc_advance_k(desc_v, kk * 2048), idesc_pv,
-                       (j | kk) != 0 ? 1u : 0u);
+                       (!first || kk != 0) ? 1u : 0u);
         if (half == 1) umma_commit(o_done(t));
       };
-      bool ok = mbar_wait(q_full, 0, abort_flag, status_word, kWaitQ);
-      if (ok && kv_blocks > 0) ok = mbar_wait(k_full(0), 0, abort_flag, status_word, kWaitK);
-      if (ok) {
+      bool ok = true;
+      int kv_count = 0;               // key/value blocks consumed so far (ring stage and parity)
+      int blocks_done[Q_TILES] = {};  // score blocks issued so far per tile (parity of s_ready / p_ready / o_done)
+      for (int n = 0; ok; ++n) {
+        const int slot = n & 1;
+        if (!(ok = mbar_wait(item_full(slot), (uint32_t)(n >> 1) & 1u, abort_flag, status_word, kWaitItem))) break;
+        const int index = item_slot[slot];
+        if (index < 0) break;
+        const Item item = decode(index);
+        if (!(ok = mbar_wait(q_full, (uint32_t)n & 1u, abort_flag, status_word, kWaitQ))) break;
+        if (!(ok = mbar_wait(k_full(kv_count & 1), (uint32_t)(kv_count >> 1) & 1u, abort_flag, status_word, kWaitK))) break;
         tcgen05_fence_after();
 #pragma unroll
         for (int t = 0; t < Q_TILES; ++t)
-          if (0 < blocks_of[t]) issue_qk(t, 0);
-      }
-      for (int j = 0; ok && j < kv_blocks; ++j) {
-        const int stage = j & 1, next = j + 1;
-        if (!(ok = mbar_wait(v_full(stage), (uint32_t)(j >> 1) & 1u, abort_flag, status_word, kWaitV))) break;
-        bool next_k_ready = false;
+          if (0 < item.blocks_of[t]) issue_qk(t, kv_count & 1);
+        for (int j = 0; ok && j < item.kv_blocks; ++j) {
+          const int current = kv_count + j, next = current + 1;
+          const int stage = current & 1;
+          // every Q·K^T of the item has been issued once its last block is reached: Q may be refilled when they complete
+          if (j == item.kv_blocks - 1) umma_commit(q_free);
+          if (!(ok = mbar_wait(v_full(stage), (uint32_t)(current >> 1) & 1u, abort_flag, status_word, kWaitV))) break;
+          bool next_k_ready = false;
 #pragma unroll
-        for (int t = 0; t < Q_TILES; ++t) {
-          if (j < blocks_of[t]) {
-            // the first 64 keys of P arrive while the softmax warps still work on the last 64
-            if (!(ok = mbar_wait(p_ready(t, 0), (uint32_t)j & 1u, abort_flag, status_word, kWaitPReady))) break;
-            tcgen05_fence_after();
-            issue_pv(t, j, 0);
-            if (!(ok = mbar_wait(p_ready(t, 1), (uint32_t)j & 1u, abort_flag, status_word, kWaitPReady))) break;
-            tcgen05_fence_after();
-            issue_pv(t, j, 1);
-          }
-          if (next < blocks_of[t]) {
-            if (!next_k_ready) {
-              if (!(ok = mbar_wait(k_full(next & 1), (uint32_t)(next >> 1) & 1u, abort_flag, status_word, kWaitK))) break;
+          for (int t = 0; t < Q_TILES; ++t) {
+            if (j < item.blocks_of[t]) {
+              const uint32_t parity = (uint32_t)(blocks_done[t] + j) & 1u;
+              if (j == 0 && n > 0) {
+                // O_t is about to be overwritten: the previous item's epilogue must have read it
+                if (!(ok = mbar_wait(o_free(t), (uint32_t)(n - 1) & 1u, abort_flag, status_word, kWaitOFree))) break;
+              }
+              // the first 64 keys of P arrive while the softmax warps still work on the last 64
+              if (!(ok = mbar_wait(p_ready(t, 0), parity, abort_flag, status_word, kWaitPReady))) break;
               tcgen05_fence_after();
-              next_k_ready = true;
+              issue_pv(t, stage, 0, j == 0);
+              if (!(ok = mbar_wait(p_ready(t, 1), parity, abort_flag, status_word, kWaitPReady))) break;
+              tcgen05_fence_after();
+              issue_pv(t, stage, 1, j == 0);
             }
-            issue_qk(t, next);  // overwrites S_t/P_t: ordered after PV_t(j) on the tensor pipe
+            if (j + 1 < item.blocks_of[t]) {
+              if (!next_k_ready) {
+                if (!(ok = mbar_wait(k_full(next & 1), (uint32_t)(next >> 1) & 1u, abort_flag, status_word, kWaitK))) break;
+                tcgen05_fence_after();
+                next_k_ready = true;
+              }
+              issue_qk(t, next & 1);  // overwrites S_t/P_t: ordered after PV_t(j) on the tensor pipe
+            }
           }
+          if (ok) umma_commit(kv_empty(stage));
         }
-        if (ok) umma_commit(kv_empty(stage));
+        kv_count += item.kv_blocks;
+#pragma unroll
+        for (int t = 0; t < Q_TILES; ++t) blocks_done[t] += item.blocks_of[t];
+        if (ok) mbar_arrive(item_empty(slot));
       }
     }
   }
@@ -250,17 +320,27 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     const int tile = (warp - 4) >> 2;
     const int quadrant = warp & 3;          // TMEM lanes [32*quadrant, +32) are the ones this warp may touch
     const int row = quadrant * 32 + lane;   // row of the query tile == TMEM lane
-    const int q0 = (pair * Q_TILES + tile) * BLOCK_M;
-    const int query = q0 + row;
-    const int my_blocks = tile == 0 ? blocks_of[0] : blocks_of[1];
     const uint32_t lane_base = (uint32_t)(quadrant * 32) << 16;
     const uint32_t s_addr = tmem_base + lane_base + (uint32_t)(tile * BLOCK_N);
     const uint32_t o_addr = tmem_base + lane_base + 256u + (uint32_t)(tile * 128);
+    bool ok = true;
+    int blocks_done = 0;  // score blocks of this tile consumed so far, over all items (barrier parities)
+    for (int n = 0; ok; ++n) {
+    const int slot = n & 1;
+    ok = mbar_wait(item_full(slot), (uint32_t)(n >> 1) & 1u, abort_flag, status_word, kWaitItem);
+    ok = __all_sync(0xffffffffu, ok);
+    if (!ok) break;
+    const int index = item_slot[slot];
+    if (index < 0) break;
+    const Item item = decode(index);
+    const int pair = item.pair, head = item.head, batch = item.batch;
+    const int q0 = (pair * Q_TILES + tile) * BLOCK_M;
+    const int query = q0 + row;
+    const int my_blocks = tile == 0 ? item.blocks_of[0] : item.blocks_of[1];
     float used_max = -INFINITY;             // running maximum (scaled, log2 units) the exponentials refer to
     float row_sum = 0.0f;
-    bool ok = true;
     for (int j = 0; j < my_blocks; ++j) {
-      ok = mbar_wait(s_ready(tile), (uint32_t)j & 1u, abort_flag, status_word, kWaitSReady);
+      ok = mbar_wait(s_ready(tile), (uint32_t)(blocks_done + j) & 1u, abort_flag, status_word, kWaitSReady);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tcgen05_fence_after();
@@ -296,7 +376,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         used_max = candidate;
         if (j > 0) {
           // P·V of the previous block must have landed in O before it is rescaled
-          ok = mbar_wait(o_done(tile), (uint32_t)(j - 1) & 1u, abort_flag, status_word, kWaitODone);
+          ok = mbar_wait(o_done(tile), (uint32_t)(blocks_done + j - 1) & 1u, abort_flag, status_word, kWaitODone);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           tcgen05_fence_after();
@@ -340,7 +420,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       row_sum += (sum0 + sum1) + (sum2 + sum3);
     }
     if (ok && my_blocks > 0) {
-      ok = mbar_wait(o_done(tile), (uint32_t)(my_blocks - 1) & 1u, abort_flag, status_word, kWaitODone);
+      ok = mbar_wait(o_done(tile), (uint32_t)(blocks_done + my_blocks - 1) & 1u, abort_flag, status_word, kWaitODone);
       ok = __all_sync(0xffffffffu, ok);
     }
     if (ok && my_blocks > 0) {
@@ -417,6 +497,19 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         }
       }
     }
+    if (!ok) break;
+    // this item is finished for the warp: O_t may be overwritten, the ring slot (and, in the gather form, the
+    // staging rows in Q) reused
+    tcgen05_fence_before();
+    if constexpr (GATHER) fence_proxy_async();  // the staged rows were read through the generic proxy; TMA refills them
+    __syncwarp();
+    if (lane == 0) {
+      mbar_arrive(o_free(tile));
+      if constexpr (GATHER) mbar_arrive(q_free);
+      mbar_arrive(item_empty(slot));
+    }
+    blocks_done += my_blocks;
+    }  // items
   }
 
   // ---------------- teardown ----------------
@@ -489,6 +582,18 @@ __global__ void attn_fwd_generic_kernel(const __nv_bfloat16* __restrict__ q, con
 
 constexpr int kMaxDevices = 64;
 
+// Work counters of the persistent kernel: a small pool handed out round-robin, so launches in flight at the same
+// time (different streams, recorded graphs) do not share one unless more than kWorkCounters of them overlap.
+constexpr int kWorkCounters = 256;
+__device__ int g_attention_work_counters[kWorkCounters];
+
+int* next_work_counter() {
+  static std::atomic<unsigned> next{0};
+  int* base = nullptr;
+  if (cudaGetSymbolAddress(reinterpret_cast<void**>(&base), g_attention_work_counters) != cudaSuccess || !base) return nullptr;
+  return base + (next.fetch_add(1) % kWorkCounters);
+}
+
 template <int D, bool CAUSAL, bool GATHER>
 int launch_tensor_to(const void* q, const void* k, const void* v, const OutputDestinations& dst, int batch, int seq, int heads,
                      int kv_heads, cudaStream_t stream) {
@@ -515,9 +620,20 @@ int launch_tensor_to(const void* q, const void* k, const void* v, const OutputDe
   }
   const float scale_log2e = (1.0f / sqrtf((float)D)) * 1.4426950408889634f;
   const int q_blocks = (seq + BLOCK_M - 1) / BLOCK_M;
-  dim3 grid((q_blocks + Q_TILES - 1) / Q_TILES, heads, batch);
+  const long long items = (long long)((q_blocks + Q_TILES - 1) / Q_TILES) * heads * batch;
+  if (items > 0x7fffffff - 4096) return fail(BB200_E_UNSUPPORTED_SHAPE, "attention: too many query tiles");
+  static int sm_counts[kMaxDevices] = {};
+  if (sm_counts[device] == 0 && cudaDeviceGetAttribute(&sm_counts[device], cudaDevAttrMultiProcessorCount, device) != cudaSuccess)
+    sm_counts[device] = 0;
+  if (sm_counts[device] <= 0) return fail(BB200_E_NO_DRIVER, "attention: could not query the SM count");
+  // the CTAs draw their work items from a counter that this launch zeroes first (on the same stream); launches that
+  // may overlap on the GPU get different counters
+  int* counter = next_work_counter();
+  if (!counter) return fail(BB200_E_NO_DRIVER, "attention: the work counters have no device address");
+  if (int status = check_runtime(cudaMemsetAsync(counter, 0, sizeof(int), stream), "cudaMemsetAsync(attention work counter)")) return status;
+  const int grid = (int)(items < sm_counts[device] ? items : sm_counts[device]);
   attn_fwd_kernel<D, CAUSAL, GATHER><<<grid, THREADS, Smem<D>::TOTAL, stream>>>(
-      map_q, map_k, map_v, dst, seq, heads, kv_heads, scale_log2e, device_status_word());
+      map_q, map_k, map_v, dst, seq, heads, kv_heads, batch, scale_log2e, counter, device_status_word());
   return check_launch("attention kernel launch");
 }
 
