@@ -44,6 +44,7 @@ constexpr int Q_TILES = 2;                 // query tiles per CTA
 constexpr int KV_STAGES = 2;
 constexpr int THREADS = 128 * (1 + Q_TILES);  // warpgroup 0: TMA + MMA warps; warpgroups 1..2: softmax of tile 0 / 1
 constexpr int SUBTILE_BYTES = 128 * 128;   // [128 rows, 64 bf16] with 128-byte rows
+constexpr int DEFER_KEYS = 32;              // exponentials of the second half computed before the first half's store is awaited
 constexpr float RESCALE_THRESHOLD = 8.0f;  // in log2 units: p stays below 2^8 between rescales
 
 enum WaitCode { kWaitQ = 201, kWaitKvEmpty = 202, kWaitK = 203, kWaitV = 204, kWaitSReady = 205, kWaitPReady = 206,
@@ -410,12 +411,21 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           const __nv_bfloat162 hi = __floats2bfloat162_rn(p2, p3);
           s[i >> 1] = *reinterpret_cast<const uint32_t*>(&lo);
           s[(i >> 1) + 1] = *reinterpret_cast<const uint32_t*>(&hi);
+          if (half == 1 && i == 64 + DEFER_KEYS - 4) {
+            // the first half's store has had DEFER_KEYS exponentials of time to land: publish it now
+            tmem_st_wait();
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(p_ready(tile, 0));
+          }
         }
         tmem_st_32x32b_x32(s_addr + (uint32_t)(half * 32), *reinterpret_cast<uint32_t(*)[32]>(&s[half * 32]));
-        tmem_st_wait();
-        tcgen05_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(p_ready(tile, half));
+        if (half == 1) {
+          tmem_st_wait();
+          tcgen05_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(p_ready(tile, 1));
+        }
       }
       row_sum += (sum0 + sum1) + (sum2 + sum3);
     }
