@@ -268,7 +268,9 @@ int bb200_gemm_bf16_gather(const void* a, const void* b, void* const* c_destinat
 /* Softmax attention forward.  q/out: [batch, seq, heads, head_dim]; k/v: [batch, seq, kv_heads,
  * head_dim] (heads % kv_heads == 0), all bf16 row-major; lse: fp32 [batch, heads, seq]
  * (identical memory layout to [batch, heads, 1, seq]), natural log.  Scale is fixed at
- * 1/sqrt(head_dim).  causal != 0 masks key > query.
+ * 1/sqrt(head_dim).  causal != 0 masks key > query.  For head_dim 64 and 128 the kernel is persistent and draws its
+ * work from a 4-byte counter inside the library that the call zeroes on `stream` first (one of 256, taken in turn, so
+ * calls whose GPU work overlaps do not share one unless more than 256 are in flight); no device memory is allocated.
  * Replaces launch_<kernel> of the attention templates (src/baybridge/backends/hipkittens_exec.py:
  * 1178-1335; semantics src/baybridge/frontend.py:3877-3937). */
 int bb200_attention_fwd(const void* q, const void* k, const void* v, void* out, float* lse, int batch, int seq,
