@@ -1,8 +1,9 @@
-"""Kernel zoo shared by the golden-vector generator and the parity tests.
+"""Sample kernels of the hot path, shared by the benchmark, the build step, the golden-vector
+generator and the parity tests.
 
 Every kernel here is written once against a DSL module handle ``cute`` so that
 the *same Python body* can be traced by the upstream package (when the golden
-vectors are generated) and by ``baybridge_b200`` (when the tests run).  The
+vectors are generated) and by ``baybridge_b200`` (everywhere else).  The
 bodies follow the upstream samples: the indexed forms use the canonical
 ``block_idx * block_dim + thread_idx`` prefix of
 ``tools/backend_benchmark_kernels.py:691-697`` and the explicit-op kernels are

@@ -53,6 +53,6 @@ def gemm_zoo_kernel(case: str, ir: dict, zoo):
 @pytest.fixture(scope="session")
 def zoo():
     import baybridge_b200 as cute
-    from kernel_zoo import build_zoo
+    from baybridge_b200.samples import build_zoo
 
     return build_zoo(cute)

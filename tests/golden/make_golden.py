@@ -57,7 +57,7 @@ def main() -> None:
     import baybridge as bb  # noqa: E402  (upstream)
     from baybridge.compiler import _cache_key, _trace_cache_payload  # noqa: E402
 
-    from kernel_zoo import build_zoo
+    from baybridge_b200.samples import build_zoo
 
     zoo = build_zoo(bb)
     target = bb.NvidiaTarget(sm="sm_100a", ptx_version="8.8")
