@@ -148,6 +148,7 @@ class B200Backend:
         expected = [(tuple(a.spec.shape), a.spec.dtype, row_major_stride(a.spec.shape)) if a.kind == "tensor" else None for a in arguments]
         tensor_positions = [position for position, a in enumerate(arguments) if a.kind == "tensor"]
         all_tensors = len(tensor_positions) == len(arguments)
+        waits_on_device = plan.kind in ("gemm", "attention")  # the kernels with mbarrier pipelines (bounded waits)
 
         def launcher(*args: Any, **kwargs: Any) -> None:
             stream = kwargs.pop("stream", None)
@@ -195,6 +196,13 @@ class B200Backend:
                 LAUNCH_COUNTER["launches"] += 1
                 if staged or synchronize:
                     native.call("bb200_stream_synchronize", stream_handle)
+                    if waits_on_device:
+                        # a bounded in-kernel wait that gave up leaves partial output: surface it like a native launch
+                        # that returned non-zero (upstream hipcc_exec.py:181-182)
+                        status = native.take_device_status(stream_handle)
+                        if status:
+                            raise RuntimeError(f"launch_{ir.name} returned device status {status}: a bounded device-side wait "
+                                               f"gave up ({native.ERROR_NAMES[-6]}); the output is incomplete")
                 for tensor, slot, foreign in staged:
                     image = np.empty(tensor.numel, dtype=DEVICE_NUMPY[tensor.dtype])
                     native.call("bb200_memcpy_d2h", image.ctypes.data_as(ctypes.c_void_p), slot.pointer, slot.nbytes, stream_handle)
@@ -208,7 +216,19 @@ class B200Backend:
                 state["slots"] = {}
                 raise
 
+        def release() -> None:
+            """Free the staged device copies and unload the modules this launcher holds (it reloads them on the next call)."""
+            holders = [state] + [value for key, value in state.items() if key.startswith("part") and isinstance(value, dict)]
+            for holder in holders:
+                for slot in holder.get("slots", {}).values():
+                    slot.release()
+                holder["slots"] = {}
+                for module in holder.pop("modules", {}).values():
+                    native.library().bb200_module_unload(module)
+                holder.get("functions", {}).clear()
+
         launcher.plan = plan  # type: ignore[attr-defined]
+        launcher.release = release  # type: ignore[attr-defined]
         return launcher
 
     # -- argument marshalling ------------------------------------------------------------------------
@@ -260,11 +280,12 @@ class B200Backend:
                 state["warned_staging"] = True
             image = value.device_image()
             signature = (value.shape, value.dtype)
-            slot = state["slots"].get(position)
+            slot_key = (position, getattr(_thread_state, "device", self.device))  # device memory belongs to one device
+            slot = state["slots"].get(slot_key)
             if slot is None or slot.signature != signature:
                 if slot is not None:
                     slot.release()
-                slot = state["slots"][position] = _StagedSlot(image.nbytes, signature)
+                slot = state["slots"][slot_key] = _StagedSlot(image.nbytes, signature)
             native.call("bb200_memcpy_h2d", slot.pointer, image.ctypes.data_as(ctypes.c_void_p), image.nbytes, stream_handle)
             native.call("bb200_stream_synchronize", stream_handle)  # `image` is pageable and about to go out of scope
             staged.append((value, slot, foreign))
@@ -303,14 +324,17 @@ class B200Backend:
         entry = record["entry"].encode()
 
         def run(pointers: dict[int, int], scalars: dict[int, Any], stream_handle) -> None:
-            function = state.get("function")
+            # a module belongs to the context it was loaded in: one per device this launcher has run on
+            device_id = getattr(_thread_state, "device", self.device)
+            function = functions.get(device_id)
             if function is None:
                 image = cubin_path.read_bytes()
                 module = ctypes.c_void_p()
                 native.call("bb200_module_load", image, len(image), ctypes.byref(module))
                 function = ctypes.c_void_p()
                 native.call("bb200_get_function", module, entry, ctypes.byref(function))
-                state["module"], state["function"] = module, function
+                state.setdefault("modules", {})[device_id] = module
+                functions[device_id] = function
             for slot, position in zip(tensor_slots, tensor_order):
                 slot.value = pointers[position]
             for slot, position in zip(scalar_slots, scalar_order):
@@ -322,6 +346,7 @@ class B200Backend:
                 vector_flag.value = 0 if misaligned & 15 else 1
             native.call("bb200_launch", function, grid, block, cluster, 0, stream_handle, params)
 
+        functions: dict[int, Any] = state.setdefault("functions", {})
         # the parameter block is built once; a call only rewrites the values (launchers are not thread-safe, like upstream's)
         tensor_slots = [ctypes.c_void_p() for _ in tensor_order]
         scalar_slots = [ctype() for ctype in scalar_ctypes]
@@ -372,17 +397,20 @@ class B200Backend:
             scratch_bytes = 0
 
         def function(name: str):
+            # modules and functions are per context, hence per device; so is the scratch buffer below
+            device_id = getattr(_thread_state, "device", self.device)
             functions = state.setdefault("functions", {})
-            if name not in functions:
-                if "module" not in state:
+            if (device_id, name) not in functions:
+                modules = state.setdefault("modules", {})
+                if device_id not in modules:
                     image = cubin_path.read_bytes()
                     module = ctypes.c_void_p()
                     native.call("bb200_module_load", image, len(image), ctypes.byref(module))
-                    state["module"] = module
+                    modules[device_id] = module
                 handle = ctypes.c_void_p()
-                native.call("bb200_get_function", state["module"], name.encode(), ctypes.byref(handle))
-                functions[name] = handle
-            return functions[name]
+                native.call("bb200_get_function", modules[device_id], name.encode(), ctypes.byref(handle))
+                functions[(device_id, name)] = handle
+            return functions[(device_id, name)]
 
         def launch(name: str, grid, block, values: list[Any], stream_handle) -> None:
             params = (ctypes.c_void_p * len(values))(*[ctypes.cast(ctypes.byref(v), ctypes.c_void_p) for v in values])
@@ -396,11 +424,12 @@ class B200Backend:
             aligned = ctypes.c_int(1 if all(pointers[position] % 16 == 0 for position in tensor_order) else 0)
             scratch = None
             if scratch_bytes:
-                slot = state.get("scratch")
+                scratch_key = ("scratch", getattr(_thread_state, "device", self.device))
+                slot = state["slots"].get(scratch_key)
                 if slot is None or slot.nbytes < scratch_bytes:
                     if slot is not None:
                         slot.release()
-                    slot = state["scratch"] = _StagedSlot(scratch_bytes, ("scratch",))
+                    slot = state["slots"][scratch_key] = _StagedSlot(scratch_bytes, ("scratch",))
                 scratch = ctypes.c_void_p(slot.pointer.value)
             block = native.U3(threads, 1, 1)
             if plan.form == "rows":

@@ -646,6 +646,10 @@ class _Elementwise:
         if any(access["kind"] == "uniform" and access["tensor"] in written for access in self.accesses):
             self.not_flat("a fixed-position load from a tensor the kernel also writes")
         indexed = [access for access in self.accesses if access["kind"] != "uniform"]
+        # the flat form runs `i < bound` only, which is the kernel's behaviour only when every store carries that guard:
+        # a masked load feeding an unguarded store writes `f(fallback)` to the elements at and past the bound
+        if self.bound is not None and any(access["kind"] == "store" and access["predicate"] is None for access in indexed):
+            self.not_flat("a guarded load feeding a store that is not guarded by the same bound")
         identity = self.flat_ok and self.one_d and all(
             access["offset"] is not None and access["offset"].equals_linear_id(threads) for access in indexed)
         if identity:

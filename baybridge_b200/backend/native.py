@@ -154,6 +154,7 @@ PROTOTYPES: dict[str, list[Any]] = {
     "bb200_attention_fwd": [P, P, P, P, P, I, I, I, I, I, I, P],
     "bb200_attention_fwd_gather": [P, P, P, ctypes.POINTER(P), ctypes.POINTER(P), I, I, I, I, I, I, I, I, P],
     "bb200_take_device_status": [P, ctypes.POINTER(I)],
+    "bb200_selftest_bounded_wait": [ctypes.c_uint, P],
     "bb200_graph_capture_begin": [P],
     "bb200_graph_capture_end": [P, ctypes.POINTER(P)],
     "bb200_graph_launch": [P, P],
@@ -192,6 +193,13 @@ def call(name: str, *args: Any) -> None:
     if status != 0:
         message = (lib.bb200_last_error() or b"").decode("utf-8", "replace")
         raise CudaDriverError(name, status, ERROR_NAMES.get(status, "CUDA_ERROR" if status > 0 else "BB200_ERROR"), message)
+
+
+def take_device_status(stream: ctypes.c_void_p) -> int:
+    """Synchronise ``stream``, then read and clear the device status word (0 = no bounded wait gave up)."""
+    status = ctypes.c_int(0)
+    call("bb200_take_device_status", stream, ctypes.byref(status))
+    return int(status.value)
 
 
 def stream_handle(stream: Any) -> ctypes.c_void_p:

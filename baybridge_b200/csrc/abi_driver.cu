@@ -15,6 +15,7 @@
 #include <string>
 
 #include "bb200_internal.h"
+#include "bb200_sm100.cuh"
 
 namespace bb200 {
 
@@ -197,6 +198,22 @@ int* device_status_word() {
   int* address = nullptr;
   if (cudaGetSymbolAddress(reinterpret_cast<void**>(&address), g_device_status) != cudaSuccess) return nullptr;
   return address;
+}
+
+// One CTA, one mbarrier that expects an arrival nobody makes: the wait must give up after `limit_ns`, record its code
+// in the status word and let the kernel return normally.
+__global__ void bounded_wait_selftest_kernel(unsigned long long limit_ns, int* status_word, int* returned) {
+  __shared__ __align__(8) uint64_t barrier;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    sm100::mbar_init(sm100::smem_addr(&barrier), 1);
+    sm100::fence_barrier_init();
+  }
+  __syncthreads();
+  const bool completed = sm100::mbar_wait_limited(sm100::smem_addr(&barrier), 0, &abort_flag, status_word, BB200_WAIT_SELFTEST, limit_ns);
+  __syncthreads();
+  if (threadIdx.x == 0) *returned = completed ? 2 : 1;
 }
 
 int encode_tensormap_2d(void* map_out, bb200_dtype dtype, const void* base, uint64_t rows, uint64_t cols,
@@ -553,6 +570,29 @@ int bb200_take_device_status(void* stream, int* status_out) {
     return status;
   if (int status = check_runtime(cudaStreamSynchronize(s), "cudaStreamSynchronize")) return status;
   if (*status_out != 0) return check_runtime(cudaMemsetAsync(word, 0, sizeof(int), s), "clear status");
+  return BB200_OK;
+}
+
+int bb200_selftest_bounded_wait(unsigned limit_us, void* stream) {
+  if (limit_us == 0 || limit_us > 10000) return fail(BB200_E_INVALID_ARGUMENT, "bb200_selftest_bounded_wait: limit must be 1..10000 us");
+  int* word = device_status_word();
+  if (!word) return fail(BB200_E_NO_DRIVER, "device status word is not addressable (no CUDA device?)");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int* returned = nullptr;
+  if (int status = check_runtime(cudaMallocAsync(reinterpret_cast<void**>(&returned), sizeof(int), s), "cudaMallocAsync")) return status;
+  int status = check_runtime(cudaMemsetAsync(returned, 0, sizeof(int), s), "cudaMemsetAsync");
+  if (!status) {
+    bounded_wait_selftest_kernel<<<1, 32, 0, s>>>((unsigned long long)limit_us * 1000ull, word, returned);
+    status = check_launch("bounded_wait_selftest_kernel");
+  }
+  int host_returned = 0;
+  if (!status) status = check_runtime(cudaMemcpyAsync(&host_returned, returned, sizeof(int), cudaMemcpyDeviceToHost, s), "read back");
+  if (!status) status = check_runtime(cudaStreamSynchronize(s), "cudaStreamSynchronize");
+  cudaFreeAsync(returned, s);
+  if (status) return status;
+  if (host_returned != 1)
+    return fail(BB200_E_DEVICE_TIMEOUT, "bounded-wait self-test: the kernel %s", host_returned == 2 ? "saw a barrier phase complete that nobody arrived on"
+                                                                                                : "did not reach its end");
   return BB200_OK;
 }
 

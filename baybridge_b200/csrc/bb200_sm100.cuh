@@ -62,21 +62,25 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 
 // Wait for the phase with the given parity to complete.  Returns false when the wait was abandoned
-// (limit exceeded here, or another thread of the CTA already raised `*abort_flag`).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status_word, int code) {
+// (`limit_ns` of %globaltimer exceeded here, or another thread of the CTA already raised `*abort_flag`).
+__device__ __forceinline__ bool mbar_wait_limited(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status_word, int code,
+                                                  unsigned long long limit_ns) {
   if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long started = global_timer_ns();
   for (uint32_t spin = 1;; ++spin) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((spin & 31u) == 0) {
       if (*abort_flag != 0) return false;
-      if (global_timer_ns() - started > kWaitLimitNs) {
+      if (global_timer_ns() - started > limit_ns) {
         *abort_flag = code;
         atomicExch(status_word, code);
         return false;
       }
     }
   }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status_word, int code) {
+  return mbar_wait_limited(bar, parity, abort_flag, status_word, code, kWaitLimitNs);
 }
 
 // ---- TMA (tile mode, no multicast) ------------------------------------------------------------------

@@ -50,17 +50,21 @@ class HostPipeline:
         probe_definition = _definition(kernel_for(self.host_args[tensor_positions[0]].shape[0]))
         ir = trace(probe_definition, tuple(_normalize(c) for c in carriers))
         self.spec: ShardSpec = shard_spec(match(ir), ir)
-        if any(axis != 0 for _, axis in self.spec.sharded):
-            chunks = 1  # a non-leading shard axis is not contiguous in host memory: run unchunked
         full_rows = self.spec.extent
         self.rows = full_rows
-        self.chunks = max(1, min(int(chunks), full_rows))
-        self.sharded = {position for position, _ in self.spec.sharded}
         self.outputs = set(self.spec.outputs)
+        self.reads = set(self.spec.reads)
+        if any(axis != 0 for _, axis in self.spec.sharded):
+            # a shard axis that is not the leading one (A of a GEMM stored [k, m]) is not contiguous in host memory:
+            # one pass over whole tensors, every argument held at its full shape
+            self.chunks, self.sharded = 1, set()
+        else:
+            self.chunks = max(1, min(int(chunks), full_rows))
+            self.sharded = {position for position, _ in self.spec.sharded}
         self.bounds = [shard_bounds(full_rows, self.chunks, index) for index in range(self.chunks)]
         longest = max(stop - start for start, stop in self.bounds)
         backend = B200Backend(device=self.device.index or 0, synchronize=False)
-        # device storage: two slots per sharded argument, one full copy per replicated argument
+        # device storage: two slots per sharded argument, one full copy per other argument
         self.slots: list[dict[int, Any]] = [{}, {}]
         self.replicated: dict[int, Any] = {}
         for position in tensor_positions:
@@ -80,7 +84,7 @@ class HostPipeline:
                 self.artifacts[rows] = _compile(kernel_for(rows), *sample, backend=backend, cache_dir=cache_dir)
         self.copy_in, self.compute, self.copy_out = (torch.cuda.Stream(device=self.device) for _ in range(3))
         self.h2d_bytes = sum(self.host_args[p].numel() * self.host_args[p].element_size()
-                             for p in tensor_positions if p not in self.outputs)
+                             for p in tensor_positions if p in self.reads)
         self.d2h_bytes = sum(self.host_args[p].numel() * self.host_args[p].element_size() for p in self.outputs)
 
     def _device_view(self, slot: int, position: int, rows: int):
@@ -96,7 +100,7 @@ class HostPipeline:
             stream.wait_stream(caller)
         with torch.cuda.stream(self.copy_in):
             for position, buffer in self.replicated.items():
-                if position not in self.outputs:
+                if position in self.reads:
                     buffer.copy_(self.host_args[position], non_blocking=True)
         kernel_done: list[Any] = []
         drained: list[Any] = []
@@ -105,7 +109,7 @@ class HostPipeline:
             with torch.cuda.stream(self.copy_in):
                 if index >= 2:
                     self.copy_in.wait_event(kernel_done[index - 2])  # the slot's inputs are free again
-                for position in self.sharded - self.outputs:
+                for position in self.sharded & self.reads:
                     self.slots[slot][position][:rows].copy_(self.host_args[position][start:stop], non_blocking=True)
                 loaded = torch.cuda.Event()
                 loaded.record(self.copy_in)

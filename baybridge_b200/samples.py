@@ -148,6 +148,35 @@ def build_zoo(cute) -> SimpleNamespace:
 
     zoo.make_indexed_masked_add = make_indexed_masked_add
 
+    # zero padding: the load is guarded, the store is not, so elements past `valid` receive f(else_value)
+    def make_indexed_padded_increment(n: int, valid: int, block: int = 128):
+        @cute.kernel(launch=cute.LaunchConfig(grid=((n + block - 1) // block, 1, 1), block=(block, 1, 1)))
+        def indexed_padded_increment_kernel(src: cute.Tensor, dst: cute.Tensor):
+            tidx, _, _ = cute.arch.thread_idx()
+            bidx, _, _ = cute.arch.block_idx()
+            bdim, _, _ = cute.arch.block_dim()
+            idx = bidx * bdim + tidx
+            value = cute.load(src, idx, predicate=idx < valid, else_value=0.0)
+            dst[idx] = value + 1.0
+
+        return indexed_padded_increment_kernel
+
+    zoo.make_indexed_padded_increment = make_indexed_padded_increment
+
+    # read-modify-write of one tensor: dst[i] = dst[i] + src[i]
+    def make_indexed_accumulate(n: int, block: int = 128):
+        @cute.kernel(launch=cute.LaunchConfig(grid=((n + block - 1) // block, 1, 1), block=(block, 1, 1)))
+        def indexed_accumulate_kernel(src: cute.Tensor, dst: cute.Tensor):
+            tidx, _, _ = cute.arch.thread_idx()
+            bidx, _, _ = cute.arch.block_idx()
+            bdim, _, _ = cute.arch.block_dim()
+            idx = bidx * bdim + tidx
+            dst[idx] = dst[idx] + src[idx]
+
+        return indexed_accumulate_kernel
+
+    zoo.make_indexed_accumulate = make_indexed_accumulate
+
     # tensor-SSA pointwise forms
     @cute.kernel
     def ssa_add(a: cute.Tensor, b: cute.Tensor, c: cute.Tensor):

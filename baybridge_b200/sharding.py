@@ -33,6 +33,9 @@ class ShardSpec:
     sharded: tuple[tuple[int, int], ...]   # (argument position, axis)
     replicated: tuple[int, ...]
     outputs: tuple[int, ...]          # argument positions that are all-gathered afterwards
+    # argument positions whose contents the kernel needs on the device before it runs: every tensor it reads, and
+    # every output it only partly overwrites (a guarded or short store leaves the other elements as they were)
+    reads: tuple[int, ...] = ()
 
 
 def shard_spec(plan: Any, ir: Any) -> ShardSpec:
@@ -41,6 +44,8 @@ def shard_spec(plan: Any, ir: Any) -> ShardSpec:
     the leading axis → rows (others do not shard)."""
     kind = plan.kind
     if kind == "elementwise":
+        if plan.mode != "flat":
+            raise ValueError("a body whose accesses are not one shared element-to-element map does not split along axis 0")
         tensors = tuple(dict.fromkeys(tuple(plan.inputs) + tuple(store[0] for store in plan.stores)))
         shapes = {ir.arguments[p].spec.shape for p in tensors}
         if len(shapes) != 1:
@@ -52,20 +57,26 @@ def shard_spec(plan: Any, ir: Any) -> ShardSpec:
         for node in plan.nodes:
             if node.op == "broadcast_input" and node.attrs["source_shape"][0] != 1:
                 raise ValueError("an operand broadcast along the columns varies along the shard axis; this kernel does not shard")
-        return ShardSpec(kind, shape[0], tuple((p, 0) for p in tensors), gathers, tuple(store[0] for store in plan.stores))
+        stored = tuple(store[0] for store in plan.stores)
+        numel = 1
+        for length in shape:
+            numel *= length
+        partly = stored if plan.extent < numel else ()
+        return ShardSpec(kind, shape[0], tuple((p, 0) for p in tensors), gathers, stored,
+                         reads=tuple(dict.fromkeys(tuple(plan.inputs) + gathers + partly)))
     if kind == "rmsnorm":
         full = (plan.gamma,) if plan.gamma_is_full else ()
         shape = ir.arguments[plan.x].spec.shape
         if len(shape) < 2:
             raise ValueError("a rank-1 rmsnorm has a single row and does not shard")
         return ShardSpec(kind, shape[0], tuple((p, 0) for p in (plan.x, plan.out) + full),
-                         () if plan.gamma_is_full else (plan.gamma,), (plan.out,))
+                         () if plan.gamma_is_full else (plan.gamma,), (plan.out,), reads=(plan.x, plan.gamma))
     if kind == "gemm":
         a_axis = 1 if plan.transpose_a else 0  # A is [m,k] or, transposed, [k,m]
-        return ShardSpec(kind, plan.m, ((plan.a, a_axis), (plan.c, 0)), (plan.b,), (plan.c,))
+        return ShardSpec(kind, plan.m, ((plan.a, a_axis), (plan.c, 0)), (plan.b,), (plan.c,), reads=(plan.a, plan.b))
     if kind == "attention":
         return ShardSpec(kind, plan.batch, tuple((p, 0) for p in (plan.q, plan.k, plan.v, plan.out, plan.lse)), (),
-                         (plan.out, plan.lse))
+                         (plan.out, plan.lse), reads=(plan.q, plan.k, plan.v))
     if kind == "layernorm":
         shape = ir.arguments[plan.x].spec.shape
         if len(shape) < 2:
@@ -73,15 +84,18 @@ def shard_spec(plan: Any, ir: Any) -> ShardSpec:
         per_row = (plan.x, plan.residual, plan.out, plan.out_resid)
         full = tuple(p for p, is_full in ((plan.weight, plan.weight_is_full), (plan.bias, plan.bias_is_full)) if is_full)
         shared = tuple(p for p, is_full in ((plan.weight, plan.weight_is_full), (plan.bias, plan.bias_is_full)) if not is_full)
-        return ShardSpec(kind, shape[0], tuple((p, 0) for p in per_row + full), shared, (plan.out, plan.out_resid))
+        return ShardSpec(kind, shape[0], tuple((p, 0) for p in per_row + full), shared, (plan.out, plan.out_resid),
+                         reads=(plan.x, plan.residual, plan.weight, plan.bias))
     if kind == "reduction_bundle":
         raise ValueError("a bundle of reductions folds over different axes of one tensor; it does not shard")
     if kind == "reduction":
         # only a fold that keeps the leading axis splits without an exchange step (each rank folds its own rows);
         # folds over the leading axis run whole on one GPU
         if plan.form == "rows" and len(plan.source_shape) >= 2 and ir.arguments[plan.dst].spec.shape[:1] == plan.source_shape[:1]:
-            return ShardSpec(kind, plan.source_shape[0], tuple((p, 0) for p in tuple(plan.inputs) + (plan.dst,)), (), (plan.dst,))
-        return ShardSpec(kind, 1, (), tuple(plan.inputs) + (plan.dst,), (plan.dst,))
+            return ShardSpec(kind, plan.source_shape[0], tuple((p, 0) for p in tuple(plan.inputs) + (plan.dst,)), (), (plan.dst,),
+                             reads=tuple(plan.inputs))
+        # a scalar result lands at one offset of dst: the rest of dst keeps its contents
+        return ShardSpec(kind, 1, (), tuple(plan.inputs) + (plan.dst,), (plan.dst,), reads=tuple(plan.inputs) + (plan.dst,))
     raise ValueError(f"unknown plan kind '{kind}'")
 
 

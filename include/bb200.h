@@ -293,6 +293,17 @@ int bb200_attention_fwd_gather(const void* q, const void* k, const void* v, void
  * `stream` first.  No upstream counterpart (its generated kernels never wait on one another). */
 int bb200_take_device_status(void* stream, int* status_out);
 
+/* Status-word code written by the self-test below (kernels use codes 100 and up). */
+#define BB200_WAIT_SELFTEST 99
+
+/* Diagnostic: launches one CTA that waits, through the same bounded wait every kernel of this library uses, on a
+ * barrier nobody arrives on, with a limit of `limit_us` microseconds (1..10000) instead of the kernels' 1 s.  The
+ * wait gives up, the kernel returns normally and the device status word holds BB200_WAIT_SELFTEST until
+ * bb200_take_device_status reads it; the context stays usable.  Returns BB200_OK when exactly that happened.
+ * Synchronises `stream`.  It exercises the path by which a launcher learns of an abandoned wait — the analogue of a
+ * native launch returning non-zero upstream (src/baybridge/backends/hipcc_exec.py:181-182) — without faulting. */
+int bb200_selftest_bounded_wait(unsigned limit_us, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -55,3 +55,46 @@ def test_pipeline_rmsnorm_and_attention(zoo, tmp_path):
     ref_out, ref_lse = oracle.attention(q.double().numpy(), k.double().numpy(), v.double().numpy(), causal=True)
     assert oracle.rel_l2(o.double().numpy(), ref_out) <= 1e-2
     assert float(np.abs(lse.double().numpy() - ref_lse).max()) <= 1e-2
+
+
+def test_pipeline_copies_in_what_the_kernel_reads(zoo, tmp_path):
+    """A tensor that is read and written (dst += src) must reach the device before the kernel runs, and an output the
+    kernel only partly overwrites must come back with its other elements unchanged."""
+    import torch
+
+    from baybridge_b200.host_pipeline import HostPipeline
+
+    n = 40_000
+    rng = np.random.default_rng(5)
+    src = torch.from_numpy(rng.uniform(-1, 1, n).astype(np.float32)).pin_memory()
+    start = rng.uniform(-1, 1, n).astype(np.float32)
+    for chunks in (1, 3):
+        dst = torch.from_numpy(start.copy()).pin_memory()
+        pipeline = HostPipeline(lambda rows: zoo.make_indexed_accumulate(rows), [src, dst], chunks=chunks, cache_dir=tmp_path)
+        pipeline.run()
+        assert np.array_equal(dst.numpy(), (start.astype(np.float64) + src.numpy().astype(np.float64)).astype(np.float32))
+        assert pipeline.h2d_bytes == 2 * n * 4 and pipeline.d2h_bytes == n * 4
+
+    # masked add over 1000 of 1024 elements: the last 24 elements of dst are not the kernel's to write
+    a, b = (torch.from_numpy(rng.uniform(-1, 1, 1024).astype(np.float32)).pin_memory() for _ in range(2))
+    kept = torch.full((1024,), 7.0).pin_memory()
+    HostPipeline(lambda rows: zoo.make_indexed_masked_add(1000), [a, b, kept], chunks=1, cache_dir=tmp_path).run()
+    assert np.array_equal(kept.numpy()[:1000], (a.numpy().astype(np.float64) + b.numpy()).astype(np.float32)[:1000])
+    assert np.array_equal(kept.numpy()[1000:], np.full(24, 7.0, dtype=np.float32))
+
+
+def test_pipeline_gemm_with_a_stored_k_by_m(zoo, tmp_path):
+    """A stored [k, m] is sharded along its second axis: the pipeline runs whole tensors, with k != m."""
+    import torch
+
+    from baybridge_b200.host_pipeline import HostPipeline
+
+    m, n, k = 384, 256, 640
+    rng = np.random.default_rng(6)
+    a = torch.from_numpy(oracle.bf16_round((rng.standard_normal((k, m)) / 16).astype(np.float32))).to(torch.bfloat16).pin_memory()
+    b = torch.from_numpy(oracle.bf16_round((rng.standard_normal((k, n)) / 16).astype(np.float32))).to(torch.bfloat16).pin_memory()
+    c = torch.zeros((m, n), dtype=torch.float32).pin_memory()
+    pipeline = HostPipeline(lambda rows: zoo.gemm_atb, [a, b, c], chunks=4, cache_dir=tmp_path)
+    assert pipeline.chunks == 1
+    pipeline.run()
+    assert oracle.rel_l2(c.double().numpy(), oracle.gemm(a.double().numpy(), b.double().numpy(), transpose_a=True)) <= 1e-5
