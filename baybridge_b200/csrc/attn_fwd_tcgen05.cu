@@ -620,7 +620,7 @@ int launch_tensor_to(const void* q, const void* k, const void* v, const OutputDe
   int device = 0;
   if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices)
     return fail(BB200_E_NO_DRIVER, "attention: no CUDA device is current");
-  static bool configured[kMaxDevices] = {};
+  static std::atomic<bool> configured[kMaxDevices];  // setting the attribute twice from two threads is harmless
   if (!configured[device]) {
     if (int status = check_runtime(cudaFuncSetAttribute(attn_fwd_kernel<D, CAUSAL, GATHER>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                         Smem<D>::TOTAL),
@@ -632,16 +632,19 @@ int launch_tensor_to(const void* q, const void* k, const void* v, const OutputDe
   const int q_blocks = (seq + BLOCK_M - 1) / BLOCK_M;
   const long long items = (long long)((q_blocks + Q_TILES - 1) / Q_TILES) * heads * batch;
   if (items > 0x7fffffff - 4096) return fail(BB200_E_UNSUPPORTED_SHAPE, "attention: too many query tiles");
-  static int sm_counts[kMaxDevices] = {};
-  if (sm_counts[device] == 0 && cudaDeviceGetAttribute(&sm_counts[device], cudaDevAttrMultiProcessorCount, device) != cudaSuccess)
-    sm_counts[device] = 0;
-  if (sm_counts[device] <= 0) return fail(BB200_E_NO_DRIVER, "attention: could not query the SM count");
+  static std::atomic<int> sm_counts[kMaxDevices];
+  int sm_count = sm_counts[device].load(std::memory_order_relaxed);
+  if (sm_count == 0) {
+    if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) sm_count = 0;
+    sm_counts[device].store(sm_count, std::memory_order_relaxed);
+  }
+  if (sm_count <= 0) return fail(BB200_E_NO_DRIVER, "attention: could not query the SM count");
   // the CTAs draw their work items from a counter that this launch zeroes first (on the same stream); launches that
   // may overlap on the GPU get different counters
   int* counter = next_work_counter();
   if (!counter) return fail(BB200_E_NO_DRIVER, "attention: the work counters have no device address");
   if (int status = check_runtime(cudaMemsetAsync(counter, 0, sizeof(int), stream), "cudaMemsetAsync(attention work counter)")) return status;
-  const int grid = (int)(items < sm_counts[device] ? items : sm_counts[device]);
+  const int grid = (int)(items < sm_count ? items : sm_count);
   attn_fwd_kernel<D, CAUSAL, GATHER><<<grid, THREADS, Smem<D>::TOTAL, stream>>>(
       map_q, map_k, map_v, dst, seq, heads, kv_heads, batch, scale_log2e, counter, device_status_word());
   return check_launch("attention kernel launch");

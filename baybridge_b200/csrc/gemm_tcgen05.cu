@@ -21,6 +21,7 @@
 
 #include <stdlib.h>
 
+#include <atomic>
 #include <mutex>
 
 #include "bb200_internal.h"
@@ -567,7 +568,9 @@ gemm_abt_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
 // ---- tiled transpose (brings other operand layouts to the native K-contiguous form) ------------------
 __global__ void transpose_bf16_kernel(const __nv_bfloat16* __restrict__ src, __nv_bfloat16* __restrict__ dst, int rows, int cols) {
   __shared__ __nv_bfloat16 tile[32][33];
-  const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+  // tiles are numbered along grid.x alone (2^31 - 1 blocks): a long, narrow matrix must not run into the 65535 limit of grid.y
+  const unsigned tiles_across = (unsigned)(cols + 31) / 32;
+  const int c0 = (int)(blockIdx.x % tiles_across) * 32, r0 = (int)(blockIdx.x / tiles_across) * 32;
   for (int j = threadIdx.y; j < 32; j += blockDim.y) {
     const int r = r0 + j, c = c0 + threadIdx.x;
     if (r < rows && c < cols) tile[j][threadIdx.x] = src[(size_t)r * cols + c];
@@ -580,7 +583,9 @@ __global__ void transpose_bf16_kernel(const __nv_bfloat16* __restrict__ src, __n
 }
 
 int launch_transpose(const void* src, void* dst, int rows, int cols, cudaStream_t stream) {
-  dim3 grid((cols + 31) / 32, (rows + 31) / 32), block(32, 8);
+  const unsigned long long tiles = (unsigned long long)((cols + 31) / 32) * (unsigned long long)((rows + 31) / 32);
+  if (tiles > 0x7fffffffull) return fail(BB200_E_UNSUPPORTED_SHAPE, "transpose: %d x %d needs more than 2^31 - 1 tiles", rows, cols);
+  dim3 grid((unsigned)tiles), block(32, 8);
   transpose_bf16_kernel<<<grid, block, 0, stream>>>(static_cast<const __nv_bfloat16*>(src), static_cast<__nv_bfloat16*>(dst), rows, cols);
   return check_launch("transpose kernel launch");
 }
@@ -592,24 +597,26 @@ int current_device() {
   return cudaGetDevice(&device) == cudaSuccess && device >= 0 && device < kMaxDevices ? device : -1;
 }
 
+// Host-side caches below are atomics or initialised-once statics: entry points may be called from several threads.
 int cached_sm_count(int device) {
-  static int counts[kMaxDevices] = {};
-  if (counts[device] == 0 &&
-      cudaDeviceGetAttribute(&counts[device], cudaDevAttrMultiProcessorCount, device) != cudaSuccess)
-    counts[device] = 0;
-  return counts[device];
+  static std::atomic<int> counts[kMaxDevices];
+  int count = counts[device].load(std::memory_order_relaxed);
+  if (count == 0) {
+    if (cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) count = 0;
+    counts[device].store(count, std::memory_order_relaxed);
+  }
+  return count;
 }
 
 // Tiles that run concurrently (148 consecutive tile ids) cover group_m M-blocks x 148/group_m N-blocks;
 // 16 keeps that footprint (A rows + B rows of one wave) inside the 126 MB L2 for K up to 8192.
 // BB200_GEMM_GROUP_M overrides it for tuning runs.
 int raster_group_m() {
-  static int value = 0;
-  if (value == 0) {
+  static const int value = [] {
     const char* text = getenv("BB200_GEMM_GROUP_M");
     const int parsed = text ? atoi(text) : 0;
-    value = parsed > 0 && parsed <= 1024 ? parsed : DEFAULT_GROUP_M;
-  }
+    return parsed > 0 && parsed <= 1024 ? parsed : DEFAULT_GROUP_M;
+  }();
   return value;
 }
 
@@ -617,11 +624,10 @@ int raster_group_m() {
 // less per flop, so even a half-occupied wave beats single-CTA tiles at full occupancy); smaller and ragged
 // problems stay on the single-CTA kernel.  BB200_GEMM_PAIR=0/1 forces the choice for tuning runs.
 bool use_pair_kernel(int m, int n, int sms) {
-  static int forced = -2;
-  if (forced == -2) {
+  static const int forced = [] {
     const char* text = getenv("BB200_GEMM_PAIR");
-    forced = text ? (atoi(text) != 0 ? 1 : 0) : -1;
-  }
+    return text ? (atoi(text) != 0 ? 1 : 0) : -1;
+  }();
   if (forced >= 0) return forced == 1;
   const long tiles = (long)((m + PAIR_BM - 1) / PAIR_BM) * ((n + BN - 1) / BN);
   // an odd number of 128-row blocks leaves the last pair tile half empty: tolerable from nine blocks on
@@ -639,7 +645,7 @@ int launch_pair(const void* a_operand, const void* b, const Destinations& dst, i
   if (int status = B_MN ? encode_tensormap_2d(&map_b, BB200_BF16, b, (uint64_t)k, (uint64_t)n, (uint64_t)n * 2, BK, 64, 3)
                         : encode_tensormap_2d(&map_b, BB200_BF16, b, (uint64_t)n, (uint64_t)k, (uint64_t)k * 2, PAIR_B_ROWS, BK, 3))
     return status;
-  static bool configured[kMaxDevices] = {};
+  static std::atomic<bool> configured[kMaxDevices];
   if (!configured[device]) {
     if (int status = check_runtime(cudaFuncSetAttribute(gemm_abt_pair_kernel<OutT, A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM_BYTES),
                                    "cudaFuncSetAttribute(gemm pair smem)"))
@@ -657,12 +663,11 @@ int launch_pair(const void* a_operand, const void* b, const Destinations& dst, i
 // B_MN: B is stored [k, n] (n contiguous), MN-major; otherwise [n, k].
 // Tile width of the single-CTA kernel.  BB200_GEMM_TILE_N = 256 / 128 / 64 forces it for tuning runs.
 int single_cta_tile_n(int m, int n, int sms) {
-  static int forced = -1;
-  if (forced < 0) {
+  static const int forced = [] {
     const char* text = getenv("BB200_GEMM_TILE_N");
     const int parsed = text ? atoi(text) : 0;
-    forced = parsed == 256 || parsed == 128 || parsed == 64 ? parsed : 0;
-  }
+    return parsed == 256 || parsed == 128 || parsed == 64 ? parsed : 0;
+  }();
   if (forced) return forced;
   // a wave of full-width tiles that (nearly) fills the SMs stays; otherwise the narrowest width whose tiles still fit one
   // wave: a lone tile is bound by the latency of its own operand stream, and narrower tiles put more streams in flight
@@ -687,12 +692,11 @@ Destinations single_destination(void* c) {
 // range is cut into `splits` work items whose fp32 partial products a second kernel folds.  Needs a workspace, so the
 // allocation-free entry point never splits.  BB200_GEMM_SPLIT_K forces a count (1 = never) for tuning runs.
 int split_k_count(int tiles, int k_blocks, int sms) {
-  static int forced = -1;
-  if (forced < 0) {
+  static const int forced = [] {
     const char* text = getenv("BB200_GEMM_SPLIT_K");
     const int parsed = text ? atoi(text) : 0;
-    forced = parsed >= 1 && parsed <= 64 ? parsed : 0;
-  }
+    return parsed >= 1 && parsed <= 64 ? parsed : 0;
+  }();
   int splits = forced ? forced : (tiles * 2 <= sms ? sms / tiles : 1);
   if (splits > 16 && !forced) splits = 16;
   if (splits > k_blocks / 8) splits = k_blocks / 8;  // at least eight 64-wide k-blocks per work item
@@ -710,7 +714,7 @@ int launch_single(const void* a_operand, const void* b, const Destinations& dst,
   if (int status = B_MN ? encode_tensormap_2d(&map_b, BB200_BF16, b, (uint64_t)k, (uint64_t)n, (uint64_t)n * 2, BK, 64, 3)
                         : encode_tensormap_2d(&map_b, BB200_BF16, b, (uint64_t)n, (uint64_t)k, (uint64_t)k * 2, TN, BK, 3))
     return status;
-  static bool configured[kMaxDevices] = {};  // per template instantiation and device
+  static std::atomic<bool> configured[kMaxDevices];  // per template instantiation and device
   if (!configured[device]) {
     if (int status = check_runtime(cudaFuncSetAttribute(gemm_abt_kernel<OutT, A_MN, B_MN, TN>, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_BYTES),
                                    "cudaFuncSetAttribute(gemm smem)"))

@@ -23,6 +23,7 @@ from typing import Any, Callable
 from .errors import BackendNotImplementedError, CompilationError
 from .host_values import RuntimeScalar, RuntimeTensor, normalize_runtime_argument
 from .portable_ir import AddressSpace, LaunchConfig, ScalarSpec, TensorSpec
+from .scalar_types import byte_width
 from .trace import ScalarValue, TensorValue, active_builder, broadcast_shapes, coerce_scalar, require_builder
 
 
@@ -223,11 +224,73 @@ def store(value: ScalarValue, tensor: TensorValue, index: Any, *, predicate: Sca
         builder.emit_void("masked_store", value, tensor, *operands, guard, attrs={"rank": len(operands)})
 
 
-def copy(src: TensorValue, dst: TensorValue, *, vector_bytes: int | None = None) -> None:
-    """Whole-tensor copy op; ``vector_bytes`` is recorded as an attribute exactly as upstream does."""
+class ReductionOp:
+    """Reduction kinds of a reducing copy (upstream ``frontend.py:76-84``); the IR carries the lower-case string."""
+    ADD, INC, DEC, MIN, MAX, AND, OR, XOR = "add", "inc", "dec", "min", "max", "and", "or", "xor"
+
+
+class CtaGroup:
+    """Upstream ``nvgpu.tcgen05.CtaGroup``: recorded on copy ops as the strings ``"one"`` / ``"two"``."""
+    ONE, TWO = "one", "two"
+
+
+@dataclass(frozen=True)
+class CopyReduceBulkTensorTileS2GOp:
+    """``dst = dst (op) src`` element by element (upstream ``frontend.py:115-121``): the traced op is ``copy_reduce``."""
+    reduction_kind: Any = ReductionOp.ADD
+    cta_group: Any = None
+
+    def __post_init__(self) -> None:
+        kind = str(getattr(self.reduction_kind, "value", self.reduction_kind)).lower()
+        if kind not in ("add", "inc", "dec", "min", "max", "and", "or", "xor"):
+            raise ValueError(f"unsupported cpasync reduction op '{self.reduction_kind}'")
+        object.__setattr__(self, "reduction_kind", kind)
+
+
+@dataclass(frozen=True)
+class CopyAtom:
+    """A copy op bound to an element type (upstream ``make_copy_atom``, ``frontend.py:3123-3127``)."""
+    op: Any
+    value_type: str
+    num_bits_per_copy: int
+
+    @property
+    def vector_bytes(self) -> int:
+        return self.num_bits_per_copy // 8
+
+
+def make_copy_atom(op: Any, value_type: Any, *, num_bits_per_copy: int | None = None) -> CopyAtom:
+    from .scalar_types import resolve_element_type_name
+
+    resolved = resolve_element_type_name(value_type)
+    if num_bits_per_copy is None:
+        num_bits_per_copy = 8 * byte_width(resolved)
+    return CopyAtom(op=op, value_type=resolved, num_bits_per_copy=int(num_bits_per_copy))
+
+
+def copy(*args: Any, vector_bytes: int | None = None) -> None:
+    """Whole-tensor copy op, ``copy(src, dst)`` or ``copy(copy_atom, src, dst)`` (upstream ``frontend.py:3358-3414``).
+    ``vector_bytes`` and the atom's attributes are recorded exactly as upstream records them; an atom built on
+    ``CopyReduceBulkTensorTileS2GOp`` traces the read-modify-write op ``copy_reduce``."""
+    atom = None
+    if len(args) == 2:
+        src, dst = args
+    elif len(args) == 3 and isinstance(args[0], CopyAtom):
+        atom, src, dst = args
+    else:
+        raise TypeError("copy expects (src, dst) or (copy_atom, src, dst)")
     if not (isinstance(src, TensorValue) and isinstance(dst, TensorValue)):
         raise BackendNotImplementedError("copy on host tensors would execute on the host; baybridge_b200 has no CPU runtime")
-    require_builder().emit_void("copy", src, dst, attrs={"vector_bytes": vector_bytes})
+    if atom is not None and vector_bytes is None:
+        vector_bytes = atom.vector_bytes
+    attrs: dict[str, Any] = {"vector_bytes": vector_bytes}
+    if atom is None:
+        require_builder().emit_void("copy", src, dst, attrs=attrs)
+        return
+    if not isinstance(atom.op, CopyReduceBulkTensorTileS2GOp):
+        raise BackendNotImplementedError(f"copy atoms over {type(atom.op).__name__} are outside the b200 hot path")
+    attrs.update(copy_variant="cpasync_tma_s2g_reduce", cta_group=atom.op.cta_group, reduction=atom.op.reduction_kind)
+    require_builder().emit_void("copy_reduce", src, dst, attrs=attrs)
 
 
 def make_tensor(name: str, shape: tuple[int, ...] | None = None, dtype: str | None = None, *,

@@ -27,8 +27,11 @@ timed, each as the max over ranks of CUDA-event time on the launching stream:
     value_with_gather   kernel, then the NCCL all-gather of the output shards
     value_fused         the kernel that stores its shard into every rank's gathered buffer + one barrier
 
-and sampled rows of the GATHERED output are compared with the CPU oracle (``"parity"``).  Inputs smaller
-than 1 GiB per rank are timed with a 256 MB L2 flush before every step (outside the event pairs).
+and sampled rows of the GATHERED output are compared with the CPU oracle (``"parity"``).  L2 between timed
+steps: a working set of 1 GiB or more per rank is simply larger than the 126 MB L2; a smaller one is timed over
+several copies of its tensors used in rotation, so that at least 1 GiB of other data passes through L2 before a
+copy is touched again; the GEMM and every step form that contains a collective instead get a 256 MB L2 flush
+write before each step, outside that step's event pair.
 
 ``--impl reference`` times upstream's own CPU reference runtime (``oracle/ref_runtime.py`` over the copy in
 ``oracle/_ref``; the numpy port in ``oracle/cpu_runtime.py`` when that copy is absent) on a bounded sample
@@ -54,7 +57,7 @@ if str(ROOT) not in sys.path:
     sys.path.insert(0, str(ROOT))
 
 L2_FLUSH_BYTES = 256 << 20
-FLUSH_BELOW_BYTES = 1 << 30  # working sets below this are timed with an L2 flush before every step
+ROTATE_BELOW_BYTES = 1 << 30  # smaller working sets are timed over rotating copies that add up to at least this much
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 CONFIGS = ("fused_mul_add", "gemm", "rmsnorm", "attention", "indexed_add")
 
@@ -258,7 +261,8 @@ class Workload:
     dtype, bound, seed = "bf16", "hbm", 0
     extent = 0            # length of the sharded outer axis at the configuration's size
     axis_name = "rows"
-    always_flush = False
+    always_flush = False   # time every step behind an L2 flush write (event pair per step)
+    l2_resident = False    # the configuration is smaller than L2 by design and is reported as such
     input_names: tuple[str, ...] = ()
     output_names: tuple[str, ...] = ()
     order: tuple[str, ...] = ()   # kernel argument order over inputs, replicated operands and outputs
@@ -331,12 +335,21 @@ class Workload:
         self.artifact = ctx.cute.compile(self.kernel_object, *self.tensors, backend=B200Backend(synchronize=False),
                                          cache_dir=ctx.cache_dir)
         self.handles = tuple(ctx.cute.from_dlpack(t) for t in self.tensors)
-        self.flush = self.always_flush or self.bytes_resident(self.local) < FLUSH_BELOW_BYTES
+        resident = self.bytes_resident(self.local)
+        self.flush = self.always_flush
+        # kernel-only timing of a small working set: rotate over copies of every tensor so no step finds its data in L2
+        copies = 1 if (self.flush or self.l2_resident or resident >= ROTATE_BELOW_BYTES) else min(16, -(-ROTATE_BELOW_BYTES // int(resident)) + 1)
+        self.rotation_keep = [[tensor.clone() for tensor in self.tensors] for _ in range(copies - 1)]
+        self.rotation = [self.handles] + [tuple(ctx.cute.from_dlpack(t) for t in clones) for clones in self.rotation_keep]
         self.launches = 0
 
     def step(self) -> None:
-        self.artifact(*self.handles, stream=self.ctx.stream)
+        """The timed step: the compiled artifact on the next copy of the tensors (copy 0 is the one that is gathered and checked)."""
+        self.artifact(*self.rotation[self.launches % len(self.rotation)], stream=self.ctx.stream)
         self.launches += 1
+
+    def step_in_place(self) -> None:
+        self.artifact(*self.handles, stream=self.ctx.stream)
 
     # ---- parity against the CPU oracle on sampled units of the global problem -----------------------------
     def choose_samples(self, world: int) -> list[tuple]:
@@ -692,6 +705,7 @@ class IndexedAdd(Workload):
     extent, cols = 256, 256
     input_names, output_names, order = ("a", "b"), ("c",), ("a", "b", "c")
     e2e_chunks = 1
+    l2_resident = True
     tolerance = 0.0
     reference_size = reference_arm_size = 256
 
@@ -1131,8 +1145,16 @@ def measure(ctx: Context, workload: Workload, *, steps: int, warmup: int, headli
     per_rank = workload.work(workload.local) / (kernel_ms * 1e-3) / scale
     record: dict = {"metric": workload.metric, "value": per_rank * world, "unit": workload.unit, "ms_per_step": kernel_ms,
                     "steps": steps, "warmup": warmup, "dtype": workload.dtype, "gpu_launches": launches}
-    l2 = ("256 MB L2 flush write before every timed step, outside the event pairs" if workload.flush
-          else f"working set {workload.bytes_resident(workload.local) / 1e9:.2f} GB per GPU > 126 MB L2, no flush")
+    resident_gb = workload.bytes_resident(workload.local) / 1e9
+    if workload.flush:
+        l2 = "256 MB L2 flush write before every timed step, outside the event pairs"
+    elif workload.l2_resident:
+        l2 = f"working set {resident_gb * 1e3:.2f} MB is L2-resident by design (launch-latency bound); no flush"
+    elif len(workload.rotation) > 1:
+        l2 = (f"working set {resident_gb:.2f} GB per GPU: steps rotate over {len(workload.rotation)} copies of every tensor "
+              f"({resident_gb * len(workload.rotation):.2f} GB touched between two uses of a copy), no flush")
+    else:
+        l2 = f"working set {resident_gb:.2f} GB per GPU > 126 MB L2, no flush"
     record["config"] = {"workload": workload.describe(workload.local), "l2": l2}
     if world > 1:
         record["config"].update(shard=f"{workload.local} of {workload.total} {workload.axis_name} per rank",
@@ -1160,6 +1182,7 @@ def measure(ctx: Context, workload: Workload, *, steps: int, warmup: int, headli
 
     # ---- parity of the (gathered) output, and the two gather forms -------------------------------------------
     gather_steps = max(1, min(steps, 10))
+    workload.step_in_place()  # the copy that is gathered and checked holds this run's result
     if world == 1:
         torch.cuda.synchronize()
         record["parity"] = workload.check(workload.outputs)
@@ -1173,13 +1196,15 @@ def measure(ctx: Context, workload: Workload, *, steps: int, warmup: int, headli
                 dist.all_gather_into_tensor(full[name], workload.outputs[name])
 
         def kernel_then_gather() -> None:
-            workload.step()
+            workload.step_in_place()
             gather()
+
+        flush_collective = not workload.l2_resident  # steps with a collective: an L2 flush write before each
 
         for _ in range(2):
             kernel_then_gather()
-        with_gather_ms = ctx.time_ms(kernel_then_gather, gather_steps, workload.flush)
-        gather_ms = ctx.time_ms(gather, gather_steps, workload.flush)
+        with_gather_ms = ctx.time_ms(kernel_then_gather, gather_steps, flush_collective)
+        gather_ms = ctx.time_ms(gather, gather_steps, flush_collective)
         output_bytes = sum(t.numel() * t.element_size() for t in full.values())
         parity = workload.check(full) if ctx.rank == 0 else None
         record["value_with_gather"] = total_work / (with_gather_ms * 1e-3) / scale
@@ -1201,7 +1226,7 @@ def measure(ctx: Context, workload: Workload, *, steps: int, warmup: int, headli
             fused_error = f"{type(error).__name__}: {error}"[:200]
         if ctx.everyone(fused_error is None):
             ctx.barrier()
-            fused_ms = ctx.time_ms(fused_step, gather_steps, workload.flush)
+            fused_ms = ctx.time_ms(fused_step, gather_steps, flush_collective)
             same = all(torch.equal(fused_full[name], full[name]) for name in workload.output_names)
             record["value_fused"] = total_work / (fused_ms * 1e-3) / scale
             record["allgather"].update(fused_kernel_and_gather_ms=fused_ms,
@@ -1242,7 +1267,7 @@ def measure(ctx: Context, workload: Workload, *, steps: int, warmup: int, headli
 
 
 def release(ctx: Context, workload: Workload) -> None:
-    for field in ("inputs", "rep", "outputs", "tensors", "handles", "host", "artifact", "sample_inputs", "_b_host"):
+    for field in ("inputs", "rep", "outputs", "tensors", "handles", "host", "artifact", "sample_inputs", "_b_host", "rotation", "rotation_keep"):
         if hasattr(workload, field):
             delattr(workload, field)
     ctx.torch.cuda.empty_cache()

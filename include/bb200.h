@@ -271,6 +271,11 @@ int bb200_gemm_bf16_gather(const void* a, const void* b, void* const* c_destinat
  * 1/sqrt(head_dim).  causal != 0 masks key > query.  For head_dim 64 and 128 the kernel is persistent and draws its
  * work from a 4-byte counter inside the library that the call zeroes on `stream` first (one of 256, taken in turn, so
  * calls whose GPU work overlaps do not share one unless more than 256 are in flight); no device memory is allocated.
+ * Limits that follow from the counter pool: (1) more than 256 attention launches in flight at once on one GPU (for
+ * example on many streams) may share a counter, and two launches sharing one skip or repeat work items — keep at
+ * most 256 unfinished calls per GPU; (2) a call recorded into a launch graph keeps the counter it drew when it was
+ * recorded, so do not replay one recorded graph concurrently with itself, and do not let a replay overlap with more
+ * than 255 newer live calls.
  * Replaces launch_<kernel> of the attention templates (src/baybridge/backends/hipkittens_exec.py:
  * 1178-1335; semantics src/baybridge/frontend.py:3877-3937). */
 int bb200_attention_fwd(const void* q, const void* k, const void* v, void* out, float* lse, int batch, int seq,
