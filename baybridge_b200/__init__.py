@@ -52,9 +52,10 @@ from .dsl import (
     KernelDefinition,
     KernelLaunch,
     acos, arch, asin, empty_like, full, full_like, ones_like, zeros_like, atan, atan2, attention, block_dim, block_idx, ceil, copy, cos, dim, erf, exp, exp2, floor,
-    gemm, grid_dim, jit, kernel, lane_id, layernorm, load, log, log10, log2, make_tensor, math, maximum, minimum, mma,
+    gemm, grid_dim, jit, kernel, lane_id, layernorm, load, log, log10, log2, make_copy_atom, make_tensor, math, maximum, minimum, mma,
     partition, partition_program, partition_thread, barrier, program_id, rmsnorm, round, rsqrt, sin, sqrt, store, thread_idx, trunc, where,
 )
+from . import nvgpu
 from .targets import AMDTarget, NvidiaTarget
 from .driver import (
     CompiledKernel,

@@ -44,7 +44,7 @@ BINARY_OPS = {
 TENSOR_OP_ALIASES = {
     "tensor_add": "add", "tensor_sub": "sub", "tensor_mul": "mul", "tensor_div": "div", "tensor_max": "max",
     "tensor_min": "min", "tensor_neg": "neg", "tensor_abs": "abs", "tensor_bitand": "bitand", "tensor_bitor": "bitor",
-    "tensor_bitxor": "bitxor", "tensor_bitnot": "bitnot",
+    "tensor_bitxor": "bitxor", "tensor_bitnot": "bitnot", "tensor_select": "select",
 }
 TOPOLOGY_OPS = {"thread_idx", "block_idx", "program_id", "block_dim", "grid_dim"}
 
@@ -923,6 +923,38 @@ def _match_ssa_elementwise(ir) -> ElementwisePlan:
                     raise _unsupported(f"copy into unknown tensor '{destination}'")
             else:
                 raise _unsupported(f"copy from unknown value '{source}'")
+        elif op.op == "copy_reduce":
+            # dst = dst (op) src over whole global tensors (upstream frontend.py:1957-1979); the launch only distributes the
+            # elements, each is combined once (the executable upstream backend's reading, ptx_bridge.py:1391-1428, 2028-2070)
+            source, destination = op.inputs
+            for name in (source, destination):
+                if name not in positions or ir.arguments[positions[name]].kind != "tensor":
+                    raise _unsupported("copy_reduce operands must be kernel tensor arguments")
+            source_spec, destination_spec = global_tensor(source), global_tensor(destination)
+            if source_spec.shape != destination_spec.shape or source_spec.dtype != destination_spec.dtype:
+                raise _unsupported(f"copy_reduce requires matching shapes and dtypes, got {source_spec.shape}/{source_spec.dtype} "
+                                   f"and {destination_spec.shape}/{destination_spec.dtype}")
+            combine = {"add": "add", "max": "max", "min": "min", "and": "bitand", "or": "bitor", "xor": "bitxor"}.get(
+                str(op.attrs.get("reduction", "")).lower())
+            if combine is None:
+                raise _unsupported(f"copy_reduce reduction '{op.attrs.get('reduction')}' is not lowered (add/max/min/and/or/xor are)")
+            if combine.startswith("bit") and destination_spec.dtype not in ("i32", "i64", "i8", "i1"):
+                raise _unsupported(f"bitwise copy_reduce on {destination_spec.dtype} tensors")
+            element_shape(destination_spec.shape)
+            current = []
+            for name, spec in ((destination, destination_spec), (source, source_spec)):
+                position = positions[name]
+                if position in stores:
+                    current.append(stores[position])  # the value an earlier whole-tensor store left there
+                    continue
+                node = f"{name}__elem"
+                if position not in inputs:
+                    inputs.append(position)
+                    nodes.append(Node(node, "input", spec.dtype, attrs={"tensor": position}))
+                current.append(node)
+            combined = f"{destination}__reduced_{len(nodes)}"
+            nodes.append(Node(combined, combine, destination_spec.dtype, tuple(current)))
+            stores[positions[destination]] = combined
         elif op.op == "fill":
             buffer, value = op.inputs
             if buffer not in register_buffers or value not in known:
@@ -1079,7 +1111,7 @@ def match(ir):
     names = {op.op for op in operations}
     if any(name.startswith("reduce_") for name in names):
         return _match_ssa_elementwise(ir)
-    if names & {"copy", "make_tensor", "fill"}:  # whole-tensor form (scalar loads at fixed positions are allowed inside it)
+    if names & {"copy", "copy_reduce", "make_tensor", "fill"}:  # whole-tensor form (scalar loads at fixed positions are allowed inside it)
         return _match_ssa_elementwise(ir)
     if names & {"load", "store", "masked_load", "masked_store"}:
         return _match_scalar_elementwise(ir)

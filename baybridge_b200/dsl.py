@@ -440,22 +440,33 @@ def where(predicate: Any, true_value: Any, false_value: Any, *, loc: Any = None,
     if isinstance(predicate, TensorValue):
         if predicate.spec.dtype != "i1":
             raise ValueError("where requires an i1 predicate tensor")
-        required = next((v.spec.dtype for v in (true_value, false_value) if isinstance(v, (TensorValue, ScalarValue))), None)
+        # the branch dtype follows the tensor branch (the true one first), scalars and literals adapt to it
+        # (upstream frontend.py:2571-2625)
+        required = next((v.spec.dtype for v in (true_value, false_value) if isinstance(v, TensorValue)), None)
 
-        def branch(value: Any) -> Any:
+        def branch(value: Any, wanted: str | None) -> Any:
             if isinstance(value, TensorValue):
-                value = value.broadcast_to(predicate.spec.shape)
-            elif not isinstance(value, ScalarValue):
-                value = builder.constant(value, dtype=required)
-            if required is not None and value.spec.dtype != required:
-                raise ValueError(f"where branch dtype must match {required}, got {value.spec.dtype}")
+                if value.spec.shape != predicate.spec.shape:
+                    value = value.broadcast_to(predicate.spec.shape)
+                if wanted is not None and value.spec.dtype != wanted:
+                    raise ValueError(f"where tensor branch dtype must match {wanted}, got {value.spec.dtype}")
+                return value
+            if not isinstance(value, ScalarValue):
+                value = builder.constant(value) if wanted is None else builder.constant(value, dtype=wanted)
+            if wanted is not None and value.spec.dtype != wanted:
+                raise ValueError(f"where scalar branch dtype must match {wanted}, got {value.spec.dtype}")
             return value
 
-        chosen, other = branch(true_value), branch(false_value)
+        chosen = branch(true_value, required)
+        other = branch(false_value, chosen.spec.dtype)
+        if chosen.spec.dtype != other.spec.dtype:
+            raise ValueError("where requires the true and false branches to have the same dtype")
+        if not isinstance(chosen, TensorValue) and not isinstance(other, TensorValue):
+            raise TypeError("where with a traced tensor predicate requires at least one tensor branch")
         return builder.emit_tensor(
-            "select", predicate, chosen, other,
+            "tensor_select", predicate, chosen, other,
             spec=TensorSpec(predicate.spec.shape, chosen.spec.dtype, address_space=AddressSpace.REGISTER),
-            name_hint="select",
+            name_hint="tensor_select",
         )
     raise BackendNotImplementedError("where on host values would execute on the host; baybridge_b200 has no CPU runtime")
 

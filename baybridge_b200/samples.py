@@ -66,6 +66,140 @@ def build_zoo(cute) -> SimpleNamespace:
 
     zoo.fused_mul_add_ssa = fused_mul_add_ssa
 
+    # ---- reducing copy: dst = dst (op) src over whole tensors (upstream tests/test_backend_ptx_exec.py:227-302, 534-560) ----
+    def make_copy_reduce(reduction: str, grid: int = 1, block: int = 1):
+        import importlib
+
+        nvgpu = importlib.import_module(cute.__name__ + ".nvgpu")
+        kind = getattr(nvgpu.cpasync.ReductionOp, reduction.upper())
+
+        @cute.kernel(launch=cute.LaunchConfig(grid=(grid, 1, 1), block=(block, 1, 1)))
+        def copy_reduce_kernel(src: cute.Tensor, dst: cute.Tensor):
+            atom = cute.make_copy_atom(nvgpu.cpasync.CopyReduceBulkTensorTileS2GOp(kind, nvgpu.tcgen05.CtaGroup.ONE), src.element_type)
+            cute.copy(atom, src, dst)
+
+        return copy_reduce_kernel
+
+    zoo.make_copy_reduce = make_copy_reduce
+
+    # ---- whole-tensor (tensor-SSA) families under the three launch shapes upstream's conformance kernels use ---------
+    # (tests/test_backend_ptx_exec.py:430-1560: serial = one thread, parallel = one block, multiblock = a 2-D grid)
+    launches = {"serial": ((1, 1, 1), (1, 1, 1)), "parallel": ((1, 1, 1), (64, 1, 1)), "multiblock": ((2, 2, 1), (2, 1, 1))}
+    binary_ops = {
+        "add": lambda a, b: a + b, "sub": lambda a, b: a - b, "mul": lambda a, b: a * b, "div": lambda a, b: a / b,
+        "max": lambda a, b: cute.maximum(a, b), "min": lambda a, b: cute.minimum(a, b), "atan2": lambda a, b: cute.math.atan2(a, b),
+        "bitand": lambda a, b: a & b, "bitor": lambda a, b: a | b, "bitxor": lambda a, b: a ^ b,
+        "cmp_lt": lambda a, b: a < b, "cmp_eq": lambda a, b: a == b,
+    }
+    unary_ops = {
+        "sqrt": cute.sqrt, "rsqrt": cute.rsqrt, "sin": cute.sin, "cos": cute.cos, "exp2": cute.exp2, "exp": cute.exp,
+        "log2": cute.log2, "log": cute.log, "log10": cute.log10, "round": cute.round, "floor": cute.floor, "ceil": cute.ceil,
+        "trunc": cute.trunc, "atan": cute.atan, "asin": cute.asin, "acos": cute.acos, "erf": cute.erf,
+        "neg": lambda a: -a, "abs": lambda a: abs(a), "bitnot": lambda a: ~a,
+    }
+    zoo.launch_shapes = launches
+
+    def _launch(shape: str):
+        grid, block = launches[shape]
+        return cute.LaunchConfig(grid=grid, block=block)
+
+    def make_dense_binary(op: str, shape: str = "serial"):
+        """``dst = lhs (op) rhs`` over whole tensors; operands of different shapes broadcast as upstream's tracer does."""
+        body = binary_ops[op]
+
+        @cute.kernel(launch=_launch(shape))
+        def dense_binary_kernel(lhs: cute.Tensor, rhs: cute.Tensor, dst: cute.Tensor):
+            dst.store(body(lhs.load(), rhs.load()))
+
+        return dense_binary_kernel
+
+    zoo.make_dense_binary = make_dense_binary
+
+    def make_dense_unary(op: str, shape: str = "serial"):
+        body = unary_ops[op]
+
+        @cute.kernel(launch=_launch(shape))
+        def dense_unary_kernel(src: cute.Tensor, dst: cute.Tensor):
+            dst.store(body(src.load()))
+
+        return dense_unary_kernel
+
+    zoo.make_dense_unary = make_dense_unary
+
+    def make_dense_scalar_binary(op: str, scalar: str = "f32", shape: str = "serial"):
+        """``dst = src (op) alpha`` with ``alpha`` a kernel scalar parameter."""
+        body = binary_ops[op]
+        if scalar == "f32":
+            @cute.kernel(launch=_launch(shape))
+            def dense_scalar_binary_kernel(src: cute.Tensor, alpha: cute.Float32, dst: cute.Tensor):
+                dst.store(body(src.load(), alpha))
+        else:
+            @cute.kernel(launch=_launch(shape))
+            def dense_scalar_binary_kernel(src: cute.Tensor, alpha: cute.Int32, dst: cute.Tensor):
+                dst.store(body(src.load(), alpha))
+
+        return dense_scalar_binary_kernel
+
+    zoo.make_dense_scalar_binary = make_dense_scalar_binary
+
+    def make_dense_tensor_scalar_binary(op: str, shape: str = "serial"):
+        """``dst = src (op) alpha[0]`` with ``alpha`` a one-element tensor."""
+        body = binary_ops[op]
+
+        @cute.kernel(launch=_launch(shape))
+        def dense_tensor_scalar_binary_kernel(src: cute.Tensor, alpha: cute.Tensor, dst: cute.Tensor):
+            dst.store(body(src.load(), alpha[0]))
+
+        return dense_tensor_scalar_binary_kernel
+
+    zoo.make_dense_tensor_scalar_binary = make_dense_tensor_scalar_binary
+
+    def make_dense_select(form: str = "tensor", shape: str = "serial"):
+        """``where`` over whole tensors: both branches tensors, or one branch a scalar parameter / a one-element tensor."""
+        if form == "tensor":
+            @cute.kernel(launch=_launch(shape))
+            def dense_select_kernel(pred: cute.Tensor, lhs: cute.Tensor, rhs: cute.Tensor, dst: cute.Tensor):
+                dst.store(cute.where(pred.load(), lhs.load(), rhs.load()))
+        elif form == "scalar":
+            @cute.kernel(launch=_launch(shape))
+            def dense_select_kernel(pred: cute.Tensor, src: cute.Tensor, alpha: cute.Float32, dst: cute.Tensor):
+                dst.store(cute.where(pred.load(), src.load(), alpha))
+        else:
+            @cute.kernel(launch=_launch(shape))
+            def dense_select_kernel(pred: cute.Tensor, src: cute.Tensor, alpha: cute.Tensor, dst: cute.Tensor):
+                dst.store(cute.where(pred.load(), alpha[0], src.load()))
+
+        return dense_select_kernel
+
+    zoo.make_dense_select = make_dense_select
+
+    def make_dense_copy(shape: str = "serial"):
+        @cute.kernel(launch=_launch(shape))
+        def dense_copy_kernel(src: cute.Tensor, dst: cute.Tensor):
+            cute.copy(src, dst)
+
+        return dense_copy_kernel
+
+    zoo.make_dense_copy = make_dense_copy
+
+    def make_reduce(op: str, init, axis: str = "all", shape: str = "serial"):
+        """``Tensor.reduce`` to a scalar (``dst[0]``), per row or per column (upstream tests/test_backend_ptx_exec.py:1949-2200)."""
+        kind = getattr(cute.ReductionOp, op.upper())
+        if axis == "all":
+            @cute.kernel(launch=_launch(shape))
+            def reduce_kernel(src: cute.Tensor, dst: cute.Tensor):
+                dst[0] = src.reduce(kind, init, reduction_profile=0)
+        else:
+            profile = (None, 1) if axis == "rows" else (1, None)
+
+            @cute.kernel(launch=_launch(shape))
+            def reduce_kernel(src: cute.Tensor, dst: cute.Tensor):
+                dst.store(src.load().reduce(kind, init, reduction_profile=profile))
+
+        return reduce_kernel
+
+    zoo.make_reduce = make_reduce
+
     # ---- rank-1 indexed binary family (upstream PTX conformance shape) --------------------------
     def make_indexed_binary(op: str, n: int, block: int = 128):
         def body(lhs, rhs):

@@ -140,9 +140,28 @@ def run_kernel_ir(ir: dict[str, Any], arguments: dict[str, Any]) -> None:
     def lane(value: Any) -> np.ndarray:
         return np.broadcast_to(np.asarray(value).reshape(-1) if np.ndim(value) else np.asarray(value), (threads,))
 
+    # Whole-tensor values (tensor-SSA form) by name.  Every emulated thread runs the same whole-tensor statement, so a
+    # per-thread scalar that meets a whole tensor (``src.load() + alpha[0]``) must be the same for all threads and is
+    # used as that one value.
+    whole_values: set[str] = set(tensors)
+
+    def operand(name: str, whole: bool) -> Any:
+        value = env[name]
+        if whole and threads > 1 and name not in whole_values and np.ndim(value) == 1 and np.shape(value)[0] == threads:
+            array = np.asarray(value)
+            if not np.all(array == array[0]):
+                raise NotImplementedError("oracle: a whole-tensor op consumes a scalar that differs between threads")
+            return array[0]
+        return value
+
     for operation in ir["operations"]:
         op, ins, outs, attrs = operation["op"], operation["inputs"], operation["outputs"], operation["attrs"]
         result: Any = None
+        whole = op not in ("load", "store", "masked_load", "masked_store") and any(name in whole_values for name in ins)
+
+        def arg(position: int) -> Any:
+            return operand(ins[position], whole)
+
         if op in ("block_idx", "program_id", "thread_idx"):
             result = topo[(op, attrs["axis"])]
         elif op == "block_dim":
@@ -154,24 +173,26 @@ def run_kernel_ir(ir: dict[str, Any], arguments: dict[str, Any]) -> None:
         elif op == "tensor_dim":
             result = np.int64(attrs["value"])
         elif op == "cast":
-            source = env[ins[0]]
+            source = arg(0)
             target = attrs["target_dtype"]
             result = np.asarray(source).astype(F64) if target.startswith(("f", "bf")) else _as_index(source)
         elif op in ("floordiv", "mod"):
-            lhs, rhs = _as_index(env[ins[0]]), _as_index(env[ins[1]])
+            lhs, rhs = _as_index(arg(0)), _as_index(arg(1))
             result = lhs // rhs if op == "floordiv" else lhs % rhs
         elif op == "div":
-            result = np.asarray(env[ins[0]], dtype=F64) / np.asarray(env[ins[1]], dtype=F64)
+            result = np.asarray(arg(0), dtype=F64) / np.asarray(arg(1), dtype=F64)
         elif op in ("bitand", "bitor", "bitxor"):  # Python int semantics (two's complement, unbounded)
-            result = _SCALAR_BINARY[op](_as_index(env[ins[0]]), _as_index(env[ins[1]]))
+            result = _SCALAR_BINARY[op](_as_index(arg(0)), _as_index(arg(1)))
         elif op == "bitnot":
-            result = np.invert(_as_index(env[ins[0]]))
+            result = np.invert(_as_index(arg(0)))
         elif op in _SCALAR_BINARY:
-            result = _SCALAR_BINARY[op](np.asarray(env[ins[0]]), np.asarray(env[ins[1]]))
+            result = _SCALAR_BINARY[op](np.asarray(arg(0)), np.asarray(arg(1)))
         elif op in _UNARY:
-            result = _UNARY[op](np.asarray(env[ins[0]]))
+            result = _UNARY[op](np.asarray(arg(0)))
         elif op == "select":
-            result = np.where(np.asarray(env[ins[0]]).astype(bool), env[ins[1]], env[ins[2]])
+            result = np.where(np.asarray(arg(0)).astype(bool), arg(1), arg(2))
+        elif op == "tensor_select":  # frontend.py:2626-2640: element-wise choice, scalar branches broadcast
+            result = np.where(np.asarray(arg(0)).astype(bool), arg(1), arg(2))
         elif op == "load":
             result = tensors[ins[0]].reshape(-1)[flat_offset(ins[0], [env[n] for n in ins[1:]])]
         elif op == "masked_load":
@@ -194,6 +215,21 @@ def run_kernel_ir(ir: dict[str, Any], arguments: dict[str, Any]) -> None:
         # ---- tensor-SSA ------------------------------------------------------------------------
         elif op == "make_tensor":
             env[outs[0]] = np.zeros(attrs["shape"], dtype=F64)
+            whole_values.add(outs[0])
+            continue
+        elif op == "copy_reduce":
+            # frontend.py:1957-1979: dst[i] = dst[i] (op) src[i]; the statement runs once per emulated thread, so kinds
+            # that are not idempotent (add, xor) are applied `threads` times, exactly as the sequential launch loop does
+            kind = str(attrs["reduction"]).lower()
+            source, target = tensors[ins[0]], tensors[ins[1]]
+            combine = {"add": np.add, "max": np.maximum, "min": np.minimum,
+                       "and": np.bitwise_and, "or": np.bitwise_or, "xor": np.bitwise_xor}[kind]
+            integer = kind in ("and", "or", "xor")
+            for _ in range(threads if kind in ("add", "xor") else 1):
+                if integer:
+                    target[...] = combine(_as_index(target), _as_index(source))
+                else:
+                    target[...] = combine(target, source)
             continue
         elif op == "copy":
             source = env[ins[0]]
@@ -201,6 +237,7 @@ def run_kernel_ir(ir: dict[str, Any], arguments: dict[str, Any]) -> None:
                 tensors[ins[1]][...] = source
             else:
                 env[ins[1]] = np.array(source, dtype=F64)
+                whole_values.add(ins[1])
             continue
         elif op == "fill":
             env[ins[0]] = np.full(np.shape(env[ins[0]]), env[ins[1]], dtype=F64)
@@ -223,10 +260,12 @@ def run_kernel_ir(ir: dict[str, Any], arguments: dict[str, Any]) -> None:
             result = ufunc(init, ufunc.reduce(data, axis=-1))
         elif op in _TENSOR_ALIAS:
             base = _TENSOR_ALIAS[op]
-            operands = [np.asarray(env[n]) for n in ins]
+            operands = [np.asarray(arg(i)) for i in range(len(ins))]
             if base in ("bitand", "bitor", "bitxor", "bitnot"):
                 operands = [_as_index(v) for v in operands]
-            if base == "div":
+            if base == "bitnot" and attrs.get("result", {}).get("dtype") == "i1":
+                result = np.logical_not(operands[0].astype(bool))  # runtime.py:615-625: `not value` on i1 tensors, `~int` otherwise
+            elif base == "div":
                 result = operands[0] / operands[1]
             elif base in _UNARY:
                 result = _UNARY[base](operands[0])
@@ -236,6 +275,8 @@ def run_kernel_ir(ir: dict[str, Any], arguments: dict[str, Any]) -> None:
             raise NotImplementedError(f"oracle: op '{op}' is outside the elementwise path")
         if outs:
             env[outs[0]] = result
+            if whole or op == "broadcast_to" or op in _TENSOR_ALIAS:
+                whole_values.add(outs[0])
 
 
 # ---------------------------------------------------------------------------------------------

@@ -4,7 +4,9 @@
 Usage (only where an upstream checkout exists; the fixtures it writes are
 committed so tests never need the checkout):
 
-    python tests/golden/make_golden.py /path/to/upstream/src
+    python tests/golden/make_golden.py /path/to/upstream/src            # the hand-listed cases
+    python tests/golden/make_golden.py /path/to/upstream/src --sweep    # the table in tests/golden/sweep.py
+    python tests/golden/make_golden.py /path/to/upstream/src --only padded_,accumulate_   # hand-listed cases by prefix
 
 What it writes
 --------------
@@ -33,7 +35,9 @@ from pathlib import Path
 import numpy as np
 
 HERE = Path(__file__).resolve().parent
-sys.path.insert(0, str(HERE.parent))
+sys.path.insert(0, str(HERE.parent))        # tests/ (sweep table lives beside this file)
+sys.path.insert(0, str(HERE))
+sys.path.insert(0, str(HERE.parents[1]))   # the repository root, for baybridge_b200.samples
 
 
 def bf16_round(x: np.ndarray) -> np.ndarray:
@@ -52,7 +56,12 @@ ROUNDERS = {"f32": lambda x: np.asarray(x, dtype=np.float32), "bf16": bf16_round
 
 
 def main() -> None:
-    upstream_src = sys.argv[1] if len(sys.argv) > 1 else str(HERE.parents[2] / "reference" / "src")  # a checkout next to this repository
+    arguments = [a for a in sys.argv[1:] if not a.startswith("--")]
+    sweep_only = "--sweep" in sys.argv
+    only = tuple(sys.argv[sys.argv.index("--only") + 1].split(",")) if "--only" in sys.argv else ()
+    if only:
+        arguments = [a for a in arguments if a != ",".join(only)]
+    upstream_src = arguments[0] if arguments else str(HERE.parents[2] / "reference" / "src")  # a checkout next to this repository
     sys.path.insert(0, upstream_src)
     import baybridge as bb  # noqa: E402  (upstream)
     from baybridge.compiler import _cache_key, _trace_cache_payload  # noqa: E402
@@ -73,7 +82,12 @@ def main() -> None:
     def out_array(t) -> np.ndarray:
         return np.asarray(t.tolist(), dtype=np.float64)
 
+    def wanted(case: str) -> bool:
+        return not only or case.startswith(only)
+
     def dump_ir(case: str, kernel, *sample_args) -> None:
+        if not wanted(case):
+            return
         artifact = bb.compile(kernel, *sample_args, backend="portable", cache_dir=cache, target=target)
         payload = {
             "case": case,
@@ -84,6 +98,8 @@ def main() -> None:
 
     def run_case(case: str, kernel, arrays: dict[str, tuple[np.ndarray, str]], outputs: list[str], extra=()) -> None:
         """Trace + execute on the upstream CPU runtime; store inputs and outputs."""
+        if not wanted(case):
+            return
         tensors = {name: rt(value, dtype) for name, (value, dtype) in arrays.items()}
         args = list(tensors.values()) + list(extra)
         dump_ir(case, kernel, *args)
@@ -91,12 +107,58 @@ def main() -> None:
         artifact = bb.compile(kernel, *args, backend="portable", cache_dir=cache, target=target)
         artifact(*args)
         elapsed = time.perf_counter() - started
-        blob = {f"in_{name}": np.asarray(value) for name, (value, _) in arrays.items() if name not in outputs}
+        # an output that starts from given contents (a read-modify-write kernel) is stored as an input too
+        blob = {f"in_{name}": np.asarray(value) for name, (value, _) in arrays.items() if name not in outputs or np.any(value)}
         for name in outputs:
             blob[f"out_{name}"] = out_array(tensors[name])
         np.savez_compressed(HERE / f"vec_{case}.npz", **blob)
         print(f"{case}: upstream CPU runtime {elapsed:.2f}s")
 
+    if sweep_only:
+        run_sweep(bb, zoo, rt, out_array, dump_ir, cache, target)
+        return
+    if only:
+        print("writing only the cases that start with", only)
+    else:
+        run_config_1(bb, zoo, rt, out_array, dump_ir, cache, target)
+    run_listed_cases(bb, zoo, rt, out_array, dump_ir, run_case)
+    print("golden fixtures written to", HERE)
+
+
+def run_sweep(bb, zoo, rt, out_array, dump_ir, cache, target) -> None:
+    """Every case of ``sweep.CASES`` on upstream's CPU runtime → ``ir_sw_<name>.json`` + ``vec_sw_<name>.npz``."""
+    from sweep import CASES
+
+    failures = []
+    for case in CASES:
+        inputs = case.inputs()
+        try:
+            kernel = case.kernel(zoo)
+            operands, tensors = [], {}
+            for argument in case.arguments:
+                if argument.shape is None:  # an i32 scalar must be typed, a bare Python int traces as an index
+                    operands.append(bb.Int32(argument.fill) if argument.dtype == "i32" else argument.fill)
+                else:
+                    tensors[argument.name] = rt(inputs[argument.name], argument.dtype)
+                    operands.append(tensors[argument.name])
+            dump_ir(f"sw_{case.name}", kernel, *operands)
+            artifact = bb.compile(kernel, *operands, backend="portable", cache_dir=cache, target=target)
+            artifact(*operands)
+        except Exception as error:  # noqa: BLE001 - the table may hold forms upstream's own tracer or runtime declines
+            failures.append((case.name, f"{type(error).__name__}: {error}"))
+            for stale in (HERE / f"ir_sw_{case.name}.json", HERE / f"vec_sw_{case.name}.npz"):
+                stale.unlink(missing_ok=True)
+            continue
+        blob = {f"in_{a.name}": np.asarray(inputs[a.name]) for a in case.arguments if a.shape is not None and a.role != "out"}
+        for name in case.outputs:
+            blob[f"out_{name}"] = out_array(tensors[name])
+        np.savez_compressed(HERE / f"vec_sw_{case.name}.npz", **blob)
+    print(f"sweep: {len(CASES) - len(failures)} fixtures written, {len(failures)} declined by upstream")
+    for name, why in failures:
+        print(f"  declined  {name}: {why}")
+
+
+def run_config_1(bb, zoo, rt, out_array, dump_ir, cache, target) -> None:
     # ---------------- config 1: 256x256 f32 indexed add (full size) ----------------------------
     rng = np.random.default_rng(1001)
     a = rng.uniform(-1, 1, (256, 256)).astype(np.float32)
@@ -118,6 +180,9 @@ def main() -> None:
         input_sha256=np.array(digest),
     )
 
+
+
+def run_listed_cases(bb, zoo, rt, out_array, dump_ir, run_case) -> None:
     # ---------------- config 2 (reduced): fused a*b+a, bf16, both IR forms -----------------------
     rng = np.random.default_rng(1002)
     n = 4096
@@ -410,7 +475,13 @@ def main() -> None:
         *[ShapeOnly((16, 4096, 32, 128), "bfloat16") for _ in range(4)],
         ShapeOnly((16, 32, 1, 4096), "float32"),
     )
-    print("golden fixtures written to", HERE)
+    # ---------------- forms added after the first generation (regenerate alone with --only padded_,accumulate_) ----------
+    rng = np.random.default_rng(2002)
+    run_case("padded_increment_1024v512_f32", zoo.make_indexed_padded_increment(1024, 512),
+             {"src": (rng.uniform(-1, 1, 512).astype(np.float32), "f32"), "dst": (np.zeros(1024), "f32")}, ["dst"])
+    start = rng.uniform(-1, 1, 1024).astype(np.float32)
+    run_case("accumulate_1024_f32", zoo.make_indexed_accumulate(1024),
+             {"src": (rng.uniform(-1, 1, 1024).astype(np.float32), "f32"), "dst": (start, "f32")}, ["dst"])
 
 
 if __name__ == "__main__":

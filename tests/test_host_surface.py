@@ -10,7 +10,7 @@ import sys
 from pathlib import Path
 
 import pytest
-from conftest import GOLDEN, gemm_zoo_kernel, golden_ir
+from conftest import GOLDEN, golden_ir, sample_scalar, zoo_kernel
 
 import baybridge_b200 as cute
 from baybridge_b200.backend.matcher import match
@@ -41,54 +41,15 @@ class FakeCudaTensor:
         return self._stride
 
 
-def _carriers(ir: dict):
+def _carriers(ir: dict, case: str = ""):
     names = {"f32": "float32", "bf16": "bfloat16", "f16": "float16", "i32": "int32", "i1": "bool"}
     out = []
     for argument in ir["arguments"]:
         if argument["kind"] == "scalar":
-            out.append(0.75)
+            out.append(sample_scalar(cute, case, argument))
         else:
             out.append(FakeCudaTensor(argument["spec"]["shape"], names[argument["spec"]["dtype"]]))
     return out
-
-
-def _zoo_kernel(case: str, zoo):
-    parts = case.split("_")
-    table = {
-        "c1": lambda: zoo.make_indexed_add_2d(256, 256),
-        "c3": lambda: zoo.gemm_abt,
-        "c4": lambda: zoo.make_rmsnorm(1e-6),
-        "clamp": lambda: zoo.make_indexed_clamp_scale(512),
-        "masked": lambda: zoo.make_indexed_masked_add(1000),
-        "bin": lambda: zoo.make_indexed_binary(parts[1], int(parts[2])),
-        "un": lambda: zoo.make_indexed_unary(parts[1], int(parts[2])),
-        "rmsnorm": lambda: zoo.make_rmsnorm(None),
-        "layernorm": lambda: zoo.layernorm_kernel,
-    }
-    if case.startswith("reduce_"):
-        return {"row": zoo.row_sum_of_squares, "col": zoo.column_max, "total": zoo.total_sum}[parts[1]]
-    if case.startswith("c2_fused_indexed"):
-        return zoo.make_fused_mul_add_indexed(2**28 if "2p28" in case else int(parts[3]))
-    if case.startswith("c2_fused_ssa"):
-        return zoo.fused_mul_add_ssa
-    if case.startswith("ssa_"):
-        return getattr(zoo, "_".join(parts[:-2]))
-    if case.startswith(("c5_", "attn_")):
-        return zoo.attention_causal if "causal" in case else zoo.attention_full
-    families = {
-        "bitwise": lambda: zoo.make_indexed_bitwise(parts[1], int(parts[2])), "cmpsel": lambda: zoo.make_indexed_compare_select(int(parts[1])),
-        "ext1_indexed": lambda: zoo.make_indexed_extent1_scalar(int(parts[2])), "ext1_ssa": lambda: zoo.ssa_extent1_scalar,
-        "bcast_rowcol": lambda: zoo.ssa_broadcast_row_col, "factory_bundle": lambda: zoo.factory_bundle,
-        "rbundle_xor": lambda: zoo.reduce_bundle_xor, "rbundle_add": lambda: zoo.reduce_bundle_add, "rarg_max": lambda: zoo.reduce_argument_max,
-    }
-    for prefix, make in families.items():
-        if case.startswith(prefix + "_"):
-            return make()
-    if case.startswith("api_"):
-        return next(getattr(zoo, name) for name in ("api_vector_copy", "api_tile_mma", "api_topology") if case.startswith(name))
-    if case.startswith("gemm_"):
-        return gemm_zoo_kernel(case, golden_ir(case)["ir"], zoo)
-    return table[parts[0]]()
 
 
 ALL_IR_CASES = sorted(path.stem[3:] for path in GOLDEN.glob("ir_*.json"))
@@ -98,7 +59,7 @@ ALL_IR_CASES = sorted(path.stem[3:] for path in GOLDEN.glob("ir_*.json"))
 def test_traced_ir_and_cache_key_equal_upstream(case, zoo, tmp_path):
     """Same kernel body traced here and by upstream → identical IR dict and identical sha256 cache key."""
     golden = golden_ir(case)
-    artifact = cute.compile(_zoo_kernel(case, zoo), *_carriers(golden["ir"]), backend="portable", cache_dir=tmp_path, target=TARGET)
+    artifact = cute.compile(zoo_kernel(case, zoo), *_carriers(golden["ir"], case), backend="portable", cache_dir=tmp_path, target=TARGET)
     assert json.loads(json.dumps(artifact.ir.to_dict())) == golden["ir"]
     assert cache_key_for(artifact.ir, TARGET, "b200") == golden["cache_key_b200_sm100a"]
     assert PortableKernelIR.from_dict(golden["ir"]).to_dict() == golden["ir"]
@@ -126,6 +87,12 @@ def test_matcher_classifies_every_listing(case):
         assert plan.kind == "reduction" and plan.form == {"row": "rows", "col": "cols", "total": "all"}[case.split("_")[1]]
     elif case.startswith(("c5_", "attn_")):
         assert plan.kind == "attention"
+    elif case.startswith("padded_"):
+        # a guarded load feeding an unguarded store: elements past the bound receive f(else_value), which the
+        # `i < bound` flat form would leave unwritten, so the body is lowered thread by thread
+        assert plan.kind == "elementwise" and plan.mode == "literal"
+    elif case.startswith("sw_reduce_"):
+        assert plan.kind == "reduction" and plan.form == case.split("_")[2]
     else:
         assert plan.kind == "elementwise" and plan.mode == "flat"  # every zoo body is an index bijection
 

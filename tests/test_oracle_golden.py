@@ -5,7 +5,8 @@ import hashlib
 
 import numpy as np
 import pytest
-from conftest import golden_cases, golden_ir, golden_vec, mma_attrs
+from conftest import golden_cases, golden_ir, golden_vec, mma_attrs, sample_scalar
+from sweep import BY_NAME
 
 from oracle import cpu_runtime as oracle
 
@@ -43,7 +44,10 @@ def test_traced_kernel_interpreter_matches_upstream(case: str):
     for argument in ir["arguments"]:
         name = argument["name"]
         if argument["kind"] == "scalar":
-            arguments[name] = 0.75  # the only scalar-argument fixture (clamp_scale) was generated with alpha=0.75
+            value = sample_scalar(None, case, argument) if not case.startswith("sw_") else None
+            if value is None:
+                value = next(a for a in BY_NAME[case[3:]].arguments if a.name == name).fill
+            arguments[name] = value
         elif f"in_{name}" in vec:
             arguments[name] = np.array(vec[f"in_{name}"], dtype=np.float64)
         else:
