@@ -138,6 +138,8 @@ def _expression(node: Node, compute: str, dtype_of) -> str:
         return f"fabs{fn_suffix}({args[0]})" if node.dtype in FLOATS else f"({args[0]} < 0 ? -{args[0]} : {args[0]})"
     if op == "bitnot":
         return f"(~{args[0]})"
+    if op == "lognot":
+        return f"(!{args[0]})"
     if op == "cast":
         if node.dtype == "i1":
             return f"({args[0]} != 0)"

@@ -1002,6 +1002,8 @@ def _match_ssa_elementwise(ir) -> ElementwisePlan:
         elif op.op in TENSOR_OP_ALIASES or op.op in UNARY_OPS or op.op in BINARY_OPS or op.op == "select":
             base = TENSOR_OP_ALIASES.get(op.op, op.op)
             result = op.attrs["result"]
+            if op.op == "tensor_bitnot" and result.get("dtype") == "i1":
+                base = "lognot"  # upstream inverts an i1 TENSOR logically (runtime.py:615-625); scalars and integers take ~
             if result.get("kind") != "tensor":
                 raise _unsupported(f"scalar op '{op.op}' inside a tensor-SSA body")
             element_shape(tuple(result["shape"]))

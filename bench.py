@@ -179,6 +179,7 @@ class Context:
         self.stream = torch.cuda.current_stream().cuda_stream
         self.peaks, self.peak_source = load_peaks()
         self.traffic = load_traffic()
+        self.placement = host_placement(self.local_rank) if os.environ.get("BB200_BENCH_NUMA", "1") != "0" else {}
 
     def barrier(self) -> None:
         if self.dist is not None:
@@ -232,6 +233,53 @@ class Context:
             self.barrier()
             total = begin.elapsed_time(end)
         return self.slowest(total) / steps
+
+
+def host_placement(device_index: int) -> dict:
+    """Where this rank's host side sits relative to its GPU: the GPU's NUMA node (sysfs), the CPUs and memory nodes the
+    process may use, and — when the GPU's node is among the allowed memory nodes — a preferred-node memory policy set
+    before the pinned buffers are allocated, so the copies do not cross the socket interconnect.  Read-only apart from
+    this process's own memory policy."""
+    record: dict = {}
+    try:
+        import torch
+
+        bus = torch.cuda.get_device_properties(device_index).pci_bus_id
+        domain = getattr(torch.cuda.get_device_properties(device_index), "pci_domain_id", 0)
+        device = getattr(torch.cuda.get_device_properties(device_index), "pci_device_id", 0)
+        node_file = Path(f"/sys/bus/pci/devices/{domain:04x}:{bus:02x}:{device:02x}.0/numa_node")
+        record["gpu_numa_node"] = int(node_file.read_text().strip()) if node_file.exists() else None
+    except Exception as error:  # noqa: BLE001
+        record["gpu_numa_node"] = None
+        record["gpu_numa_error"] = f"{type(error).__name__}: {error}"[:120]
+    try:
+        status = Path("/proc/self/status").read_text()
+        for key, label in (("Cpus_allowed_list", "cpus_allowed"), ("Mems_allowed_list", "mems_allowed")):
+            record[label] = next(line.split(":", 1)[1].strip() for line in status.splitlines() if line.startswith(key))
+    except Exception:  # noqa: BLE001
+        pass
+    node = record.get("gpu_numa_node")
+    record["preferred_node_policy"] = "not attempted"
+    if node is not None and node >= 0:
+        allowed: set[int] = set()
+        for part in str(record.get("mems_allowed", "")).split(","):
+            if "-" in part:
+                low, high = part.split("-")
+                allowed.update(range(int(low), int(high) + 1))
+            elif part.strip().isdigit():
+                allowed.add(int(part))
+        if node in allowed and len(allowed) > 1:
+            try:
+                libc = ctypes.CDLL(None, use_errno=True)
+                mask = ctypes.c_ulong(1 << node)
+                MPOL_PREFERRED, SYS_set_mempolicy = 1, 238  # x86-64
+                result = libc.syscall(SYS_set_mempolicy, MPOL_PREFERRED, ctypes.byref(mask), ctypes.c_ulong(64))
+                record["preferred_node_policy"] = "set" if result == 0 else f"refused (errno {ctypes.get_errno()})"
+            except Exception as error:  # noqa: BLE001
+                record["preferred_node_policy"] = f"unavailable ({type(error).__name__})"
+        else:
+            record["preferred_node_policy"] = "single memory node allowed" if len(allowed) <= 1 else "gpu node not allowed"
+    return record
 
 
 def spread(total: int, world: int, per_rank: int, width: int) -> list[tuple[int, int]]:
@@ -1028,7 +1076,7 @@ def reference_arm(args, names: list[str]) -> None:
         if args.small:
             workload.shrink()
         steps = max(1, min(args.steps, 20 if index == 0 else 3))
-        warmup = min(args.warmup, 2 if index == 0 else 1)
+        warmup = min(args.warmup, 5 if index == 0 else 1)
         result = (run_reference_runtime(workload, workload.reference_arm_size, steps, warmup)
                   if use_reference and workload.reference_arm_size else {"error": "oracle/_ref is absent"})
         if "error" not in result:
@@ -1121,6 +1169,12 @@ def copy_breakdown(ctx: Context, workload: Workload, pipeline_ms: float) -> dict
         record["host_cpus_visible_to_rank0"] = len(os.sched_getaffinity(0))
     except AttributeError:
         pass
+    if ctx.dist is not None:
+        placements = [None] * ctx.world
+        ctx.dist.all_gather_object(placements, ctx.placement)
+        record["host_placement_per_rank"] = placements
+    else:
+        record["host_placement_per_rank"] = [ctx.placement]
     return record
 
 

@@ -88,6 +88,9 @@ def _worker(rank: int, world: int, port: int, rows: int, failures) -> None:
 
 @pytest.mark.parametrize("world,rows", [(2, 64), (3, 65)])  # the second case is ragged: shards of 22, 22, 21 rows
 def test_shard_run_allgather_over_gloo(world, rows):
+    """Host-side multi-rank plumbing only: shard bounds, the (ragged) all-gather of row shards and the max-over-ranks
+    reduction, over gloo on CPU.  No kernel runs here — the oracle fills in each rank's rows; the kernels' own
+    multi-rank results are compared with the oracle on GPUs by ``bench.py`` (``parity`` of the gathered output)."""
     import torch.multiprocessing as mp
 
     context = mp.get_context("spawn")
