@@ -1,0 +1,69 @@
+// mufu_issue.cu — stand-alone microbenchmark, not part of libbb200.so.
+//
+//   nvcc -gencode arch=compute_100a,code=sm_100a -O3 -o mufu_issue mufu_issue.cu && ./mufu_issue
+//
+// Question: does an `ex2.approx` hold the warp scheduler's dispatch for its 8 cycles, or can FMA-pipe instructions
+// issue underneath it?  Each element runs one ex2 (or a Cody-Waite cubic on the FMA pipe) plus one dependent fma and
+// K independent filler fmas; the program prints cycles per element per warp for 1, 2 and 4 warps per scheduler.
+// The attention kernel's softmax schedule was sized from these numbers.
+#include <cstdio>
+#include <cstdint>
+#include <cuda_runtime.h>
+__device__ __forceinline__ float fast_exp2(float x) { float y; asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
+template <int K, int MODE>
+__global__ void __launch_bounds__(512, 1) kern(const float* in, float* out, long long* clocks, int reps) {
+  float v[32], acc[8];
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = in[(threadIdx.x * 32 + i) & 1023];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = in[i] * 0.001f;
+  __syncthreads();
+  const long long start = clock64();
+  for (int r = 0; r < reps; ++r) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      if (MODE == 0) v[i] = fast_exp2(v[i]) * 0.0f + v[i];  // 1 ex2 + 1 ffma per element (dependent, but 32 independent chains)
+      if (MODE == 1) {  // scalar polynomial exp2: no MUFU
+        float x = v[i];
+        const float t = x + 12582912.0f;
+        const float f = x - (t - 12582912.0f);
+        float p = fmaf(0.05520550534129143f, f, 0.24261397123336792f);
+        p = fmaf(p, f, 0.6932547688484192f);
+        p = fmaf(p, f, 0.9999276995658875f);
+        const float e = __uint_as_float(__float_as_uint(p) + (__float_as_uint(t) << 23));
+        v[i] = e * 0.0f + v[i];
+      }
+#pragma unroll
+      for (int k = 0; k < K; ++k) acc[(i + k) & 7] = fmaf(acc[(i + k) & 7], 1.0001f, 0.5f);  // independent FMA-pipe filler
+    }
+  }
+  const long long end = clock64();
+  float s = 0;
+#pragma unroll
+  for (int i = 0; i < 32; ++i) s += v[i];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) s += acc[i];
+  out[blockIdx.x * blockDim.x + threadIdx.x] = s;
+  if (threadIdx.x == 0 && blockIdx.x == 0) clocks[0] = end - start;
+}
+template <int K, int MODE> void run(const float* in, float* out, long long* clocks, int threads) {
+  const int reps = 2000;
+  for (int it = 0; it < 2; ++it) kern<K, MODE><<<148, threads>>>(in, out, clocks, reps);
+  cudaDeviceSynchronize();
+  long long host; cudaMemcpy(&host, clocks, 8, cudaMemcpyDeviceToHost);
+  printf("mode %d (%s) filler FFMA per element %d  warps/scheduler %d : %6.2f clk per element per warp\n", MODE, MODE ? "polynomial" : "ex2", K, threads / 128,
+         (double)host / reps / 32);
+}
+int main() {
+  float* in; float* out; long long* clocks;
+  cudaMalloc(&in, 1024 * 4); cudaMalloc(&out, 148 * 512 * 4); cudaMalloc(&clocks, 8);
+  float host[1024]; for (int i = 0; i < 1024; ++i) host[i] = -(float)((i * 37) % 101) * 0.05f;
+  cudaMemcpy(in, host, sizeof(host), cudaMemcpyHostToDevice);
+  for (int threads : {128, 256, 512}) {
+    run<0, 0>(in, out, clocks, threads); run<1, 0>(in, out, clocks, threads); run<2, 0>(in, out, clocks, threads); run<3, 0>(in, out, clocks, threads);
+    run<4, 0>(in, out, clocks, threads); run<6, 0>(in, out, clocks, threads); run<8, 0>(in, out, clocks, threads);
+    run<0, 1>(in, out, clocks, threads); run<3, 1>(in, out, clocks, threads);
+  }
+  printf("%s\n", cudaGetErrorString(cudaGetLastError()));
+  return 0;
+}
