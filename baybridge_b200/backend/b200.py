@@ -31,7 +31,7 @@ from ..host_values import DLPACK_CUDA, RuntimeScalar, RuntimeTensor, TensorHandl
 from ..portable_ir import row_major_stride
 from ..scalar_types import DEVICE_NUMPY, byte_width, normalize_dtype_name
 from . import native
-from .elementwise import THREADS, UNROLL, compile_cubin, render
+from .elementwise import THREADS, UNROLL, compile_cubin, debug_bounds_enabled, render
 from . import reduction as reduction_lowering
 from .matcher import (AttentionPlan, ElementwisePlan, GemmPlan, LayerNormPlan, ReductionBundlePlan, ReductionPlan, RmsNormPlan,
                       adopt, match)
@@ -103,8 +103,9 @@ class B200Backend:
         plan = match(ir)
         record: dict[str, Any] = {"backend": self.name, "kernel": ir.name, "plan": plan.kind, "target": arch}
         if isinstance(plan, ElementwisePlan):
-            rendered = render(plan, ir)
+            rendered = render(plan, ir, debug_bounds=plan.mode == "literal" and debug_bounds_enabled())
             record.update(
+                debug_bounds=rendered.debug_bounds,
                 mode=rendered.mode, compute=rendered.compute, vector_elements=rendered.vec, extent=plan.extent,
                 entry=rendered.entry, tensor_order=list(rendered.tensor_order), scalar_order=list(rendered.scalar_order),
                 scalar_ctypes=list(rendered.scalar_ctypes), source=rendered.source,
@@ -137,6 +138,8 @@ class B200Backend:
         ir = adopt(ir)
         plan = match(ir)
         record = json.loads(lowered_module.text)
+        if isinstance(plan, ElementwisePlan) and plan.mode == "literal" and bool(record.get("debug_bounds")) != debug_bounds_enabled():
+            record = json.loads(self.lower(ir, target).text)  # a cached lowering from the other build flavour
         state: dict[str, Any] = {"slots": {}}
         runner = {
             "elementwise": self._elementwise_runner, "reduction": self._reduction_runner,
@@ -148,7 +151,9 @@ class B200Backend:
         expected = [(tuple(a.spec.shape), a.spec.dtype, row_major_stride(a.spec.shape)) if a.kind == "tensor" else None for a in arguments]
         tensor_positions = [position for position, a in enumerate(arguments) if a.kind == "tensor"]
         all_tensors = len(tensor_positions) == len(arguments)
-        waits_on_device = plan.kind in ("gemm", "attention")  # the kernels with mbarrier pipelines (bounded waits)
+        # kernels that can record a code in the device status word: the mbarrier pipelines (bounded waits) and the
+        # bounds-checking debug build of thread-by-thread elementwise kernels
+        waits_on_device = plan.kind in ("gemm", "attention") or bool(record.get("debug_bounds"))
 
         def launcher(*args: Any, **kwargs: Any) -> None:
             stream = kwargs.pop("stream", None)
@@ -344,6 +349,8 @@ class B200Backend:
                 for position in aligned_positions:
                     misaligned |= pointers[position]
                 vector_flag.value = 0 if misaligned & 15 else 1
+            if debug_bounds:
+                native.call("bb200_device_status_address", ctypes.byref(status_slot))  # the current device's word
             native.call("bb200_launch", function, grid, block, cluster, 0, stream_handle, params)
 
         functions: dict[int, Any] = state.setdefault("functions", {})
@@ -352,7 +359,9 @@ class B200Backend:
         scalar_slots = [ctype() for ctype in scalar_ctypes]
         vector_flag = ctypes.c_int(0)
         aligned_positions = [position for position in tensor_order if position not in gathers]
-        slots: list[Any] = tensor_slots + scalar_slots + ([ctypes.c_size_t(extent), vector_flag] if flat else [])
+        debug_bounds = bool(record.get("debug_bounds"))
+        status_slot = ctypes.c_void_p()
+        slots: list[Any] = tensor_slots + scalar_slots + ([ctypes.c_size_t(extent), vector_flag] if flat else []) + ([status_slot] if debug_bounds else [])
         params = (ctypes.c_void_p * len(slots))(*[ctypes.cast(ctypes.byref(slot), ctypes.c_void_p) for slot in slots])
         state["params"] = (slots, params)  # keep the ctypes objects alive with the launcher
         return run

@@ -68,6 +68,7 @@ class RenderedKernel:
     scalar_ctypes: tuple[str, ...]
     compute: str
     relaxed: tuple[int, ...] = ()  # tensor positions only read element by element: no 16-byte alignment needed
+    debug_bounds: bool = False     # literal mode: a trailing `int* bounds_status` parameter records out-of-range accesses
 
 
 def _ident(name: str) -> str:
@@ -199,7 +200,20 @@ def broadcast_offset(source_shape, target_shape, index: str) -> str:
 MAX_FANOUT = 8  # destinations per stored tensor in the fan-out form (one per GPU of a box)
 
 
-def render(plan: ElementwisePlan, ir, entry: str = "bb200_elementwise_kernel", fanout: int = 0) -> RenderedKernel:
+#: status-word codes of the bounds-checking debug build (kernels' wait codes start at 100, the self-test uses 99)
+BOUNDS_LOAD_CODE, BOUNDS_STORE_CODE = 301, 302
+
+
+def debug_bounds_enabled() -> bool:
+    """``BB200_DEBUG_BOUNDS=1`` at compile() time: thread-by-thread ("literal") kernels record an access whose traced
+    index falls outside its tensor in the device status word instead of skipping it silently, and the synchronising
+    launcher raises.  The role ``compute-sanitizer`` would play, without a tool attached; the fast flat form needs no
+    such check (its extent never exceeds a tensor)."""
+    return os.environ.get("BB200_DEBUG_BOUNDS", "0") not in ("", "0")
+
+
+def render(plan: ElementwisePlan, ir, entry: str = "bb200_elementwise_kernel", fanout: int = 0,
+           debug_bounds: bool = False) -> RenderedKernel:
     """``fanout == 0``: the ordinary kernel.  ``fanout >= 1`` (flat plans only): every stored tensor is written to
     ``fanout`` destination buffers at ``shard_offset + i`` instead of to its argument — the form a rank uses to put
     its output shard straight into every rank's gathered output (peer memory) while it computes.  The pointer
@@ -356,7 +370,7 @@ def render(plan: ElementwisePlan, ir, entry: str = "bb200_elementwise_kernel", f
                               relaxed)
 
     # ---- literal mode: one device thread per traced thread, traced index arithmetic, guarded accesses
-    signature = ", ".join(pointer_params + scalar_params)
+    signature = ", ".join(pointer_params + scalar_params + (["int* bounds_status"] if debug_bounds else []))
     code = [f'extern "C" __global__ void {entry}({signature}) {{']
 
     def guarded_offset(indices, shape, stride) -> tuple[str, str]:
@@ -378,6 +392,8 @@ def render(plan: ElementwisePlan, ir, entry: str = "bb200_elementwise_kernel", f
             predicate = f"{_ident(node.attrs['predicate'])} && " if node.attrs["predicate"] else ""
             code.append(f"  {rtype} {ident} = {fallback};")
             code.append(f"  if ({predicate}{inside}) {ident} = {_widen(node.dtype, compute, f'p{tensor}[{offset}]')};")
+            if debug_bounds:
+                code.append(f"  else if ({predicate}true) atomicExch(bounds_status, {BOUNDS_LOAD_CODE});")
         else:
             code.append(f"  const {rtype} {ident} = {_expression(node, compute, dtype_of)};")
     for tensor, value, indices, predicate, shape, stride in plan.stores:
@@ -385,6 +401,8 @@ def render(plan: ElementwisePlan, ir, entry: str = "bb200_elementwise_kernel", f
         guard = f"{_ident(predicate)} && " if predicate else ""
         dtype = arguments[tensor].spec.dtype
         code.append(f"  if ({guard}{inside}) p{tensor}[{offset}] = {_narrow(dtype, compute, _ident(value))};")
+        if debug_bounds:
+            code.append(f"  else if ({guard}true) atomicExch(bounds_status, {BOUNDS_STORE_CODE});")
     code.append("}")
     # literal bodies interleave loads and stores in program order only when a store feeds a later
     # load of the same tensor; such bodies are rejected below rather than silently reordered
@@ -395,7 +413,8 @@ def render(plan: ElementwisePlan, ir, entry: str = "bb200_elementwise_kernel", f
             "(other threads' stores could be observed)"
         )
     lines.extend(code)
-    return RenderedKernel("\n".join(lines) + "\n", entry, "literal", 1, tuple(tensors_used), scalar_order, scalar_ctypes, compute)
+    return RenderedKernel("\n".join(lines) + "\n", entry, "literal", 1, tuple(tensors_used), scalar_order, scalar_ctypes, compute,
+                          debug_bounds=debug_bounds)
 
 
 def _skeleton_digest() -> str:

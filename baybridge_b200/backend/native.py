@@ -155,6 +155,7 @@ PROTOTYPES: dict[str, list[Any]] = {
     "bb200_attention_fwd_gather": [P, P, P, ctypes.POINTER(P), ctypes.POINTER(P), I, I, I, I, I, I, I, I, P],
     "bb200_take_device_status": [P, ctypes.POINTER(I)],
     "bb200_selftest_bounded_wait": [ctypes.c_uint, P],
+    "bb200_device_status_address": [PP],
     "bb200_graph_capture_begin": [P],
     "bb200_graph_capture_end": [P, ctypes.POINTER(P)],
     "bb200_graph_launch": [P, P],

@@ -573,6 +573,14 @@ int bb200_take_device_status(void* stream, int* status_out) {
   return BB200_OK;
 }
 
+int bb200_device_status_address(void** address_out) {
+  if (!address_out) return fail(BB200_E_INVALID_ARGUMENT, "bb200_device_status_address: output is null");
+  int* word = device_status_word();
+  if (!word) return fail(BB200_E_NO_DRIVER, "device status word is not addressable (no CUDA device?)");
+  *address_out = word;
+  return BB200_OK;
+}
+
 int bb200_selftest_bounded_wait(unsigned limit_us, void* stream) {
   if (limit_us == 0 || limit_us > 10000) return fail(BB200_E_INVALID_ARGUMENT, "bb200_selftest_bounded_wait: limit must be 1..10000 us");
   int* word = device_status_word();

@@ -297,6 +297,20 @@ def build_zoo(cute) -> SimpleNamespace:
 
     zoo.make_indexed_padded_increment = make_indexed_padded_increment
 
+    # reversed copy from an over-provisioned, unguarded grid: threads past n index outside both tensors
+    def make_indexed_reverse(n: int, block: int = 128):
+        @cute.kernel(launch=cute.LaunchConfig(grid=((n + block - 1) // block, 1, 1), block=(block, 1, 1)))
+        def indexed_reverse_kernel(src: cute.Tensor, dst: cute.Tensor):
+            tidx, _, _ = cute.arch.thread_idx()
+            bidx, _, _ = cute.arch.block_idx()
+            bdim, _, _ = cute.arch.block_dim()
+            idx = bidx * bdim + tidx
+            dst[n - 1 - idx] = src[idx]
+
+        return indexed_reverse_kernel
+
+    zoo.make_indexed_reverse = make_indexed_reverse
+
     # read-modify-write of one tensor: dst[i] = dst[i] + src[i]
     def make_indexed_accumulate(n: int, block: int = 128):
         @cute.kernel(launch=cute.LaunchConfig(grid=((n + block - 1) // block, 1, 1), block=(block, 1, 1)))

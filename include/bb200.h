@@ -298,6 +298,13 @@ int bb200_attention_fwd_gather(const void* q, const void* k, const void* v, void
  * `stream` first.  No upstream counterpart (its generated kernels never wait on one another). */
 int bb200_take_device_status(void* stream, int* status_out);
 
+/* Device address of the current device's status word, for kernels that are loaded through bb200_module_load and want
+ * to record a code there themselves (the bounds-checking debug build of generated elementwise kernels does: codes 301 /
+ * 302 = a load / a store whose traced index fell outside its tensor).  No upstream counterpart: upstream's generated
+ * kernels skip out-of-range accesses silently (src/baybridge/backends/ptx_bridge.py:5846-5847) and its CPU runtime
+ * raises IndexError. */
+int bb200_device_status_address(void** address_out);
+
 /* Status-word code written by the self-test below (kernels use codes 100 and up). */
 #define BB200_WAIT_SELFTEST 99
 

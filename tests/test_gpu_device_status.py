@@ -66,3 +66,25 @@ def test_synchronising_launcher_raises_on_a_recorded_give_up_and_recovers(zoo, t
         staged(*host)
     staged(*host)
     assert oracle.rel_l2(np.asarray(host[2].tolist(), dtype=np.float64), oracle.gemm(a_host, b_host, transpose_b=True)) <= 1e-2
+
+
+def test_debug_bounds_build_reports_out_of_range_accesses(zoo, tmp_path, monkeypatch):
+    """``BB200_DEBUG_BOUNDS=1``: a thread-by-thread kernel whose grid overshoots its tensors raises instead of skipping the
+    stray accesses silently (upstream's CPU runtime raises IndexError there; its generated kernels skip, as the default
+    build here does).  Nothing faults: the checked access is never performed."""
+    import baybridge_b200 as cute
+
+    n = 1000  # 8 blocks of 128 threads: 24 threads index past the end of both tensors
+    src_host = np.arange(n, dtype=np.float32)
+    src, dst = to_device(src_host, "f32"), to_device(np.zeros(n, dtype=np.float32), "f32")
+    quiet = cute.compile(zoo.make_indexed_reverse(n), src, dst, backend="b200", cache_dir=tmp_path / "quiet")
+    quiet(src, dst)
+    assert np.array_equal(to_host(dst), src_host[::-1].astype(np.float64))
+    monkeypatch.setenv("BB200_DEBUG_BOUNDS", "1")
+    checked = cute.compile(zoo.make_indexed_reverse(n), src, dst, backend="b200", cache_dir=tmp_path / "checked", use_cache=False)
+    with pytest.raises(RuntimeError, match=r"device status 30[12]"):
+        checked(src, dst)
+    assert np.array_equal(to_host(dst), src_host[::-1].astype(np.float64))  # in-range work is unaffected
+    exact = cute.compile(zoo.make_indexed_reverse(1024), to_device(np.arange(1024, dtype=np.float32), "f32"),
+                         to_device(np.zeros(1024, dtype=np.float32), "f32"), backend="b200", cache_dir=tmp_path / "exact", use_cache=False)
+    exact(to_device(np.arange(1024, dtype=np.float32), "f32"), to_device(np.zeros(1024, dtype=np.float32), "f32"))  # no stray access: no error
