@@ -292,9 +292,13 @@ def render(plan: ElementwisePlan, ir, entry: str = "bb200_elementwise_kernel", f
             body.append("    int unused;")
         body.append("  };")
         body.append("  __device__ __forceinline__ void load(size_t base, Regs& r) const {")
+        bounds = {node.attrs["tensor"]: node.attrs["bound"] for node in plan.nodes if node.op == "input" and "bound" in node.attrs}
         for position in plan.inputs:
             ctype = STORAGE_CTYPE[arguments[position].spec.dtype]
-            body.append(f"    r.r{position} = bb200::load_stream<{ctype}, VEC>(p{position} + base);")
+            if position in bounds:
+                body.append(f"    r.r{position} = bb200::load_stream_guarded<{ctype}, VEC>(p{position}, base, (size_t){bounds[position]}ULL);")
+            else:
+                body.append(f"    r.r{position} = bb200::load_stream<{ctype}, VEC>(p{position} + base);")
         for name, (tensor, ctype, offset) in row_like.items():
             body.append(f"    r.g{_ident(name)} = bb200::load_shared_operand<{ctype}, VEC>(p{tensor} + {offset});")
         for name, (tensor, ctype, offset) in per_step.items():
@@ -311,6 +315,11 @@ def render(plan: ElementwisePlan, ir, entry: str = "bb200_elementwise_kernel", f
                     code.append(f"{indent}const {rtype} {ident} = {_widen(node.dtype, compute, f'r.g{ident}.v[j]')};")
                 elif staged and node.name in per_step:
                     code.append(f"{indent}const {rtype} {ident} = {_widen(node.dtype, compute, f'r.g{ident}')};")
+                elif node.op == "input" and "bound" in node.attrs:
+                    # defined below the bound only; past it the traced fallback value stands in (and nothing is read)
+                    loaded = _widen(node.dtype, compute, read(node.attrs["tensor"]))
+                    code.append(f"{indent}const {rtype} {ident} = (size_t)({index}) < (size_t){node.attrs['bound']}ULL ? {loaded} : "
+                                f"({rtype}){_ident(node.operands[0])};")
                 elif node.op == "input":
                     code.append(f"{indent}const {rtype} {ident} = {_widen(node.dtype, compute, read(node.attrs['tensor']))};")
                 elif node.op == "uniform_input":

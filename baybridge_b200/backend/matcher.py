@@ -615,7 +615,9 @@ class _Elementwise:
         }
         self.accesses.append(record)
         if is_load:
-            self.add(Node(op.outputs[0], "load", spec.dtype, attrs={"access": len(self.accesses) - 1}))
+            # the fallback of a guarded load is an operand: it must stay alive wherever the load's value is used
+            self.add(Node(op.outputs[0], "load", spec.dtype, (fallback,) if fallback is not None else (),
+                          attrs={"access": len(self.accesses) - 1}))
         if predicate is not None:
             bound = self._predicate_bound(predicate)
             if bound is None:
@@ -648,8 +650,20 @@ class _Elementwise:
         indexed = [access for access in self.accesses if access["kind"] != "uniform"]
         # the flat form runs `i < bound` only, which is the kernel's behaviour only when every store carries that guard:
         # a masked load feeding an unguarded store writes `f(fallback)` to the elements at and past the bound
+        self.padded = False
         if self.bound is not None and any(access["kind"] == "store" and access["predicate"] is None for access in indexed):
-            self.not_flat("a guarded load feeding a store that is not guarded by the same bound")
+            # zero padding: guarded loads, unguarded stores.  Still one flat map over the stored extent when no store is
+            # guarded, every guarded tensor is read nowhere unguarded, and each holds the elements below the bound;
+            # past the bound the load yields its fallback value
+            guarded = {access["tensor"] for access in indexed if access["kind"] == "load" and access["predicate"] is not None}
+            clean = (all(access["predicate"] is None for access in indexed if access["kind"] == "store")
+                     and all(access["predicate"] is not None for access in indexed if access["tensor"] in guarded)
+                     and all(access["fallback"] is not None and access["numel"] >= min(self.bound, threads)
+                             for access in indexed if access["tensor"] in guarded))
+            if clean:
+                self.padded = True
+            else:
+                self.not_flat("guarded and unguarded accesses that do not form a zero-padding map")
         identity = self.flat_ok and self.one_d and all(
             access["offset"] is not None and access["offset"].equals_linear_id(threads) for access in indexed)
         if identity:
@@ -680,8 +694,13 @@ class _Elementwise:
         return covered is not None and covered == threads and all(access["numel"] == covered for access in accesses)
 
     def _flat_plan(self, threads: int, scalars: tuple[int, ...]) -> ElementwisePlan:
-        extent = min([threads] + [access["numel"] for access in self.accesses if access["kind"] != "uniform"]
-                     + ([self.bound] if self.bound is not None else []))
+        padded = getattr(self, "padded", False)
+        if padded:  # the stored extent; guarded inputs may be shorter and are read below the bound only
+            extent = min([threads] + [access["numel"] for access in self.accesses
+                                      if access["kind"] == "store" or (access["kind"] == "load" and access["predicate"] is None)])
+        else:
+            extent = min([threads] + [access["numel"] for access in self.accesses if access["kind"] != "uniform"]
+                         + ([self.bound] if self.bound is not None else []))
         current: dict[int, str] = {}  # tensor position → value name that a later load must observe
         alias: dict[str, str] = {}
         inputs: list[int] = []
@@ -719,6 +738,9 @@ class _Elementwise:
                 access = self.accesses[node.attrs["access"]]
                 if access["kind"] == "uniform":
                     nodes.append(Node(name, "uniform_input", node.dtype, attrs={"tensor": access["tensor"], "offset": access["offset"].const}))
+                elif padded and access["predicate"] is not None:
+                    nodes.append(Node(name, "input", node.dtype, (resolve(access["fallback"]),),
+                                      attrs={"tensor": access["tensor"], "bound": int(self.bound)}))
                 else:
                     nodes.append(Node(name, "input", node.dtype, attrs={"tensor": access["tensor"]}))
             elif node.op == "index":

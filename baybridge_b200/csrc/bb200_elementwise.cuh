@@ -95,6 +95,17 @@ template <typename T, int VEC> __device__ __forceinline__ Pack<T, VEC> load_stre
   return out;
 }
 
+// A vector step of an input that is only defined for elements below `bound` (a guarded load feeding zero padding):
+// whole steps below the bound are ordinary vector loads, the step that straddles it reads its in-range elements one by
+// one, steps past it read nothing.  Out-of-range lanes hold zero; the body substitutes the traced fallback value.
+template <typename T, int VEC> __device__ __forceinline__ Pack<T, VEC> load_stream_guarded(const T* __restrict__ p, size_t base, size_t bound) {
+  if (base + VEC <= bound) return load_stream<T, VEC>(p + base);
+  Pack<T, VEC> out;
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) out.v[i] = base + i < bound ? p[base + i] : T();
+  return out;
+}
+
 // The same access without the streaming hint, for small operands that many elements share (a row vector
 // broadcast over the rows): they should stay in cache.
 template <typename T, int VEC> __device__ __forceinline__ Pack<T, VEC> load_shared_operand(const T* __restrict__ p) {

@@ -88,9 +88,11 @@ def test_matcher_classifies_every_listing(case):
     elif case.startswith(("c5_", "attn_")):
         assert plan.kind == "attention"
     elif case.startswith("padded_"):
-        # a guarded load feeding an unguarded store: elements past the bound receive f(else_value), which the
-        # `i < bound` flat form would leave unwritten, so the body is lowered thread by thread
-        assert plan.kind == "elementwise" and plan.mode == "literal"
+        # a guarded load feeding an unguarded store: elements past the bound receive f(else_value), so the flat map runs
+        # over the stored extent (not `i < bound`) and the guarded input carries its bound and fallback
+        assert plan.kind == "elementwise" and plan.mode == "flat" and plan.extent == 1024
+        (guarded,) = [node for node in plan.nodes if node.op == "input"]
+        assert guarded.attrs["bound"] == 512 and len(guarded.operands) == 1
     elif case.startswith("sw_reduce_"):
         assert plan.kind == "reduction" and plan.form == case.split("_")[2]
     else:
@@ -346,3 +348,18 @@ print("drop-in ok")
 """
     done = subprocess.run([sys.executable, "-c", script], capture_output=True, text=True, timeout=300)
     assert done.returncode == 0 and "drop-in ok" in done.stdout, done.stderr[-2000:]
+
+
+def test_debug_bounds_build_changes_only_thread_by_thread_kernels(zoo, monkeypatch, tmp_path):
+    """``BB200_DEBUG_BOUNDS=1`` adds a status-word parameter and a recorded code per guarded access to literal-mode
+    kernels; flat kernels (whose extent never exceeds a tensor) are rendered exactly as before."""
+    carriers = [FakeCudaTensor((1000,), "float32"), FakeCudaTensor((1000,), "float32")]
+    plain = json.loads(cute.B200Backend().lower(cute.compile(zoo.make_indexed_reverse(1000), *carriers, backend="portable").ir, TARGET).text)
+    assert plain["mode"] == "literal" and plain["debug_bounds"] is False and "bounds_status" not in plain["source"]
+    flat_ir = cute.compile(zoo.make_indexed_binary("add", 1024), *[FakeCudaTensor((1024,), "float32")] * 3, backend="portable").ir
+    flat_before = json.loads(cute.B200Backend().lower(flat_ir, TARGET).text)
+    monkeypatch.setenv("BB200_DEBUG_BOUNDS", "1")
+    checked = json.loads(cute.B200Backend().lower(cute.compile(zoo.make_indexed_reverse(1000), *carriers, backend="portable").ir, TARGET).text)
+    assert checked["debug_bounds"] is True and "int* bounds_status" in checked["source"]
+    assert checked["source"].count("atomicExch(bounds_status, 301)") == 1 and checked["source"].count("atomicExch(bounds_status, 302)") == 1
+    assert json.loads(cute.B200Backend().lower(flat_ir, TARGET).text) == flat_before
