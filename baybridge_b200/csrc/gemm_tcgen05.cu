@@ -565,6 +565,219 @@ gemm_abt_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   }
 }
 
+// ---- wide CTA-pair kernel: 512 x 256 tiles, K-major operands ------------------------------------------
+// The same pair structure with each CTA holding TWO 128-row blocks of A per stage (256 rows) next to its half
+// of the B tile: per k-block a pair moves 96 KB for 16.8 MFLOP — a quarter less shared-memory fill and L2 traffic per
+// flop than the 256 x 256 pair tile, which under the power cap is worth more clock than anything else left in this
+// kernel (measured on one box against the library GEMM, which uses this tile: 9.6 GB against 5.4 GB through L2 per
+// 8192^3 product, tensor pipe 98 % against 96 % busy, SM clock 1.37 against 1.47 GHz).  The two accumulators of a CTA
+// (rows 0-127 and 128-255 of its 256) take all 512 TMEM columns, so the epilogue of a tile is not hidden behind the
+// next tile's MMAs as in the narrower kernels — about 3 % of a tile's time — while the producer keeps prefetching.
+// CTA c of the pair owns rows [c*256, c*256 + 256) of the tile; MMA h of a k-step multiplies row block h of both CTAs.
+constexpr int WIDE_STAGES = 4;
+constexpr int WIDE_THREADS = 64 + 8 * 32;  // TMA warp, MMA warp, eight epilogue warps (one per accumulator and lane quadrant)
+
+// One warp's 32 rows x 256 columns of one accumulator straight from registers into the single local C: a lane owns a
+// row and writes it 64 bytes (bf16) or 128 bytes (f32) at a time while the next 32 columns are already on their way
+// out of TMEM.  No staging: the wide kernel's shared memory is all ring, and local L2 merges the 16-byte pieces.
+template <typename OutT>
+__device__ __forceinline__ void store_accumulator_rows_direct(OutT* c, uint32_t taddr, int row, int m, int n, int col0) {
+  constexpr int CHUNKS = BN / 32;
+  uint32_t acc[2][32];
+  tmem_ld_32x32b_x32(taddr, acc[0]);
+#pragma unroll
+  for (int chunk = 0; chunk < CHUNKS; ++chunk) {
+    tmem_ld_wait();
+    if (chunk + 1 < CHUNKS) tmem_ld_32x32b_x32(taddr + (uint32_t)((chunk + 1) * 32), acc[(chunk + 1) & 1]);
+    const int col = col0 + chunk * 32;
+    if (row < m && col < n) store_chunk<OutT>(c + (size_t)row * n + col, acc[chunk & 1], n - col);
+  }
+}
+constexpr int WIDE_A_BYTES = 2 * A_TILE_BYTES;                 // 32 KB: two [128, 64] blocks
+constexpr int WIDE_STAGE_BYTES = WIDE_A_BYTES + PAIR_B_BYTES;  // 48 KB
+constexpr int WIDE_SMEM_BYTES = WIDE_STAGES * WIDE_STAGE_BYTES + 1024 + 256;
+constexpr int WIDE_BM = 4 * BM;                                // 512 rows per pair tile
+
+// bf16 output: the whole 256-column row of a lane fits in 128 registers once it is rounded, so the accumulator can be
+// read out completely — and handed back to the MMA issuer — BEFORE the first global store is issued; the stores then
+// drain underneath the next tile's MMAs.  (The stores, not the TMEM reads, are what an exposed epilogue costs: with the
+// stores taken out the kernel ran 5 % faster, with the reads taken out no faster.)
+__device__ __forceinline__ void load_row_packed_bf16(uint32_t taddr, uint32_t (&packed)[BN / 2]) {
+  // 16 columns at a time, two loads in flight: 32 transient registers next to the 128 that hold the rounded row
+  constexpr int CHUNKS = BN / 16;
+  uint32_t acc[2][16];
+  tmem_ld_32x32b_x16(taddr, acc[0]);
+#pragma unroll
+  for (int chunk = 0; chunk < CHUNKS; ++chunk) {
+    tmem_ld_wait();
+    if (chunk + 1 < CHUNKS) tmem_ld_32x32b_x16(taddr + (uint32_t)((chunk + 1) * 16), acc[(chunk + 1) & 1]);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const __nv_bfloat162 pair = __floats2bfloat162_rn(__uint_as_float(acc[chunk & 1][2 * j]), __uint_as_float(acc[chunk & 1][2 * j + 1]));
+      packed[chunk * 8 + j] = *reinterpret_cast<const uint32_t*>(&pair);
+    }
+  }
+}
+
+// n is a multiple of 8 and C is 16-byte aligned here (the launcher sends other shapes to the narrower kernels), so a
+// 16-byte piece is either whole or absent.
+__device__ __forceinline__ void store_row_packed_bf16(__nv_bfloat16* c, int row, int m, int n, int col0, const uint32_t (&packed)[BN / 2]) {
+  if (row >= m) return;
+  uint4* row_ptr = reinterpret_cast<uint4*>(c + (size_t)row * n + col0);
+#pragma unroll
+  for (int piece = 0; piece < BN / 8; ++piece)
+    if (col0 + piece * 8 < n) row_ptr[piece] = make_uint4(packed[piece * 4], packed[piece * 4 + 1], packed[piece * 4 + 2], packed[piece * 4 + 3]);
+}
+
+template <typename OutT>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(WIDE_THREADS, 1)
+gemm_abt_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ Destinations dst,
+                     int m, int n, int k, int group_m, int* status_word) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_addr(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_aligned = smem_raw + (smem_base - smem_addr(smem_raw));
+  uint64_t* barriers = reinterpret_cast<uint64_t*>(smem_aligned + WIDE_STAGES * WIDE_STAGE_BYTES);
+  const uint32_t bar_base = smem_base + WIDE_STAGES * WIDE_STAGE_BYTES;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (WIDE_STAGES + s); };
+  const uint32_t acc_full_bar = bar_base + 8u * (2 * WIDE_STAGES);
+  const uint32_t acc_empty_bar = bar_base + 8u * (2 * WIDE_STAGES + 1);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(barriers + 2 * WIDE_STAGES + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t cta_rank = cluster_cta_rank();
+  const bool leader = cta_rank == 0;
+  const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+  const int m_blocks = (m + WIDE_BM - 1) / WIDE_BM, n_blocks = (n + BN - 1) / BN;
+  const int tiles = m_blocks * n_blocks;
+  const int k_blocks = (k + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < WIDE_STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    mbar_init(acc_full_bar, 1);
+    mbar_init(acc_empty_bar, 16);  // one arrival per epilogue warp of either CTA
+    *abort_flag = 0;
+    fence_barrier_init();
+    fence_proxy_async();
+  }
+  cluster_arrive();  // the peer's barriers must exist before anything of this CTA can signal them
+  cluster_wait();
+  if (warp == 1) tmem_alloc_pair(smem_addr(tmem_slot), TMEM_COLUMNS);
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer (both CTAs) ----------------
+    if (elect_one()) {
+      prefetch_tensormap(&map_a);
+      prefetch_tensormap(&map_b);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = pair; ok && tile < tiles; tile += pairs) {
+        const TileCoord coord = tile_coord(tile, m_blocks, n_blocks, group_m);
+        const int a_row = coord.m_block * WIDE_BM + (int)cta_rank * (2 * BM);
+        const int b_row = coord.n_block * BN + (int)cta_rank * PAIR_B_ROWS;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!(ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, status_word, kWaitEmpty))) break;
+          const uint32_t a_dst = smem_base + stage * WIDE_STAGE_BYTES;
+          const uint32_t signal = leader_cta_address(full_bar(stage));
+          if (leader) mbar_arrive_expect_tx(full_bar(stage), 2 * WIDE_STAGE_BYTES);
+          tma_load_2d_pair(a_dst, &map_a, signal, kb * BK, a_row);
+          tma_load_2d_pair(a_dst + A_TILE_BYTES, &map_a, signal, kb * BK, a_row + BM);
+          tma_load_2d_pair(a_dst + WIDE_A_BYTES, &map_b, signal, kb * BK, b_row);
+          if (++stage == WIDE_STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer (CTA 0 only) ----------------
+    if (leader && elect_one()) {
+      constexpr uint32_t idesc = umma_idesc_bf16_f32(PAIR_BM, BN, false, false);
+      int stage = 0;
+      uint32_t phase = 0;
+      int local_tile = 0;
+      bool ok = true;
+      for (int tile = pair; ok && tile < tiles; tile += pairs, ++local_tile) {
+        // both accumulators of both CTAs must have been read by the previous tile's epilogue
+        if (!(ok = mbar_wait(acc_empty_bar, ((uint32_t)local_tile & 1u) ^ 1u, abort_flag, status_word, kWaitAccEmpty))) break;
+        tcgen05_fence_after();
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!(ok = mbar_wait(full_bar(stage), phase, abort_flag, status_word, kWaitFull))) break;
+          tcgen05_fence_after();
+          const uint32_t a_src = smem_base + stage * WIDE_STAGE_BYTES;
+          const uint64_t desc_a0 = umma_desc_k_major_sw128(a_src);
+          const uint64_t desc_a1 = umma_desc_k_major_sw128(a_src + A_TILE_BYTES);
+          const uint64_t desc_b = umma_desc_k_major_sw128(a_src + WIDE_A_BYTES);
+          // the four k-steps of one accumulator back to back, then the other's: consecutive MMAs into the same
+          // accumulator chain inside the tensor core, alternating accumulators every instruction does not
+#pragma unroll
+          for (int half = 0; half < 2; ++half)
+#pragma unroll
+            for (int kk = 0; kk < BK / UMMA_K; ++kk)
+              umma_bf16_ss_pair(tmem_base + (uint32_t)(half * ACC_COLUMNS), umma_desc_advance_k(half ? desc_a1 : desc_a0, kk * UMMA_K * 2),
+                                umma_desc_advance_k(desc_b, kk * UMMA_K * 2), idesc, (kb | kk) != 0 ? 1u : 0u);
+          umma_commit_pair(empty_bar(stage), 0x3);
+          if (++stage == WIDE_STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) umma_commit_pair(acc_full_bar, 0x3);
+      }
+    }
+  } else {
+    // ---------------- epilogue (warps 2..9 of both CTAs; warp = one lane quadrant of one accumulator) ----------------
+    const int quadrant = warp & 3;          // TMEM lanes [32*quadrant, +32) are the ones this warp may touch
+    const int half = (warp - 2) >> 2;       // which of the CTA's two accumulators (row blocks)
+    OutT* c = static_cast<OutT*>(dst.p[0]) + (size_t)dst.row_offset * n;
+    int local_tile = 0;
+    bool ok = true;
+    for (int tile = pair; ok && tile < tiles; tile += pairs, ++local_tile) {
+      const TileCoord coord = tile_coord(tile, m_blocks, n_blocks, group_m);
+      ok = mbar_wait(acc_full_bar, (uint32_t)local_tile & 1u, abort_flag, status_word, kWaitAccFull);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tcgen05_fence_after();
+      const uint32_t taddr = tmem_base + ((uint32_t)(quadrant * 32) << 16) + (uint32_t)(half * ACC_COLUMNS);
+      const int row = coord.m_block * WIDE_BM + (int)cta_rank * (2 * BM) + half * BM + quadrant * 32 + lane;
+      if constexpr (sizeof(OutT) == 2) {
+        uint32_t packed[BN / 2];
+        load_row_packed_bf16(taddr, packed);
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_remote(acc_empty_bar, 0);  // the accumulator is in registers: the next tile may start
+        store_row_packed_bf16(c, row, m, n, coord.n_block * BN, packed);
+      } else {
+        store_accumulator_rows_direct<OutT>(c, taddr, row, m, n, coord.n_block * BN);
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_remote(acc_empty_bar, 0);
+      }
+    }
+  }
+
+  // ---------------- teardown ----------------
+  tcgen05_fence_before();
+  __syncthreads();
+  if (*abort_flag != 0) {
+    const unsigned long long started = global_timer_ns();
+    while (global_timer_ns() - started < 2000000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  cluster_arrive();  // neither CTA may release its TMEM or shared memory while the other can still signal or read it
+  cluster_wait();
+  if (warp == 1) {
+    __syncwarp();
+    tcgen05_fence_after();
+    tmem_dealloc_pair(tmem_base, TMEM_COLUMNS);
+  }
+}
+
 // ---- tiled transpose (brings other operand layouts to the native K-contiguous form) ------------------
 __global__ void transpose_bf16_kernel(const __nv_bfloat16* __restrict__ src, __nv_bfloat16* __restrict__ dst, int rows, int cols) {
   __shared__ __nv_bfloat16 tile[32][33];
@@ -626,7 +839,7 @@ int raster_group_m() {
 bool use_pair_kernel(int m, int n, int sms) {
   static const int forced = [] {
     const char* text = getenv("BB200_GEMM_PAIR");
-    return text ? (atoi(text) != 0 ? 1 : 0) : -1;
+    return text ? (atoi(text) != 0 ? 1 : 0) : -1;  // 1 and 2 (the wide tile) both mean a CTA-pair kernel
   }();
   if (forced >= 0) return forced == 1;
   const long tiles = (long)((m + PAIR_BM - 1) / PAIR_BM) * ((n + BN - 1) / BN);
@@ -657,6 +870,44 @@ int launch_pair(const void* a_operand, const void* b, const Destinations& dst, i
   gemm_abt_pair_kernel<OutT, A_MN, B_MN><<<2 * pairs, THREADS, PAIR_SMEM_BYTES, stream>>>(map_a, map_b, dst, m, n, k, raster_group_m() / 2 > 0 ? raster_group_m() / 2 : 1,
                                                                              device_status_word());
   return check_launch("gemm pair kernel launch");
+}
+
+template <typename OutT>
+int launch_wide(const void* a, const void* b, const Destinations& dst, int m, int n, int k, int device, int sms, cudaStream_t stream) {
+  alignas(64) CUtensorMap map_a, map_b;
+  if (int status = encode_tensormap_2d(&map_a, BB200_BF16, a, (uint64_t)m, (uint64_t)k, (uint64_t)k * 2, BM, BK, 3)) return status;
+  if (int status = encode_tensormap_2d(&map_b, BB200_BF16, b, (uint64_t)n, (uint64_t)k, (uint64_t)k * 2, PAIR_B_ROWS, BK, 3)) return status;
+  static std::atomic<bool> configured[kMaxDevices];
+  if (!configured[device]) {
+    if (int status = check_runtime(cudaFuncSetAttribute(gemm_abt_wide_kernel<OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize, WIDE_SMEM_BYTES),
+                                   "cudaFuncSetAttribute(gemm wide smem)"))
+      return status;
+    configured[device] = true;
+  }
+  const int tiles = ((m + WIDE_BM - 1) / WIDE_BM) * ((n + BN - 1) / BN);
+  const int pairs = tiles < sms / 2 ? tiles : sms / 2;
+  const int group = raster_group_m() / 4 > 0 ? raster_group_m() / 4 : 1;  // the same rows per raster group as the narrower kernels
+  gemm_abt_wide_kernel<OutT><<<2 * pairs, WIDE_THREADS, WIDE_SMEM_BYTES, stream>>>(map_a, map_b, dst, m, n, k, group, device_status_word());
+  return check_launch("gemm wide kernel launch");
+}
+
+// The wide tile wins whenever it wastes no more of the machine than the 256-row pair tile does: the fraction of tile
+// area inside the matrix times the fraction of the last wave that is occupied, with a few per cent of credit for the
+// lower traffic.  BB200_GEMM_PAIR=2 forces it, 1 forces the 256-row pair tile (tuning and tests).
+bool use_wide_kernel(int m, int n, int sms) {
+  static const int forced = [] {
+    const char* text = getenv("BB200_GEMM_PAIR");
+    return text ? atoi(text) : -1;
+  }();
+  if (forced == 2) return true;
+  if (forced >= 0) return false;
+  auto efficiency = [&](int tile_rows) {
+    const long m_blocks = (m + tile_rows - 1) / tile_rows, n_blocks = (n + BN - 1) / BN;
+    const long tiles = m_blocks * n_blocks, pairs = sms / 2;
+    const long waves = (tiles + pairs - 1) / pairs;
+    return ((double)m * n / ((double)m_blocks * tile_rows * n_blocks * BN)) * ((double)tiles / (double)(waves * pairs));
+  };
+  return m >= WIDE_BM && efficiency(WIDE_BM) * 1.03 >= efficiency(PAIR_BM);
 }
 
 // A_MN: A is stored [k, m] (m contiguous) and consumed as an MN-major operand; otherwise [m, k].
@@ -759,7 +1010,13 @@ int launch_native(const void* a_operand, const void* b, const Destinations& dst,
   if (device < 0) return fail(BB200_E_NO_DRIVER, "gemm: no CUDA device is current");
   const int sms = cached_sm_count(device);
   if (sms <= 0) return fail(BB200_E_NO_DRIVER, "gemm: could not query the SM count");
-  if (use_pair_kernel(m, n, sms)) return launch_pair<OutT, A_MN, B_MN>(a_operand, b, dst, m, n, k, device, sms, stream);
+  if (use_pair_kernel(m, n, sms)) {
+    if constexpr (!A_MN && !B_MN) {
+      // the wide kernel writes one local C in whole 16-byte pieces
+      if (dst.count == 1 && (n % 8) == 0 && aligned16(dst.p[0]) && use_wide_kernel(m, n, sms)) return launch_wide<OutT>(a_operand, b, dst, m, n, k, device, sms, stream);
+    }
+    return launch_pair<OutT, A_MN, B_MN>(a_operand, b, dst, m, n, k, device, sms, stream);
+  }
   switch (single_cta_tile_n(m, n, sms)) {
     case 256: return launch_single<OutT, A_MN, B_MN, 256>(a_operand, b, dst, m, n, k, device, sms, may_split, stream);
     case 128: return launch_single<OutT, A_MN, B_MN, 128>(a_operand, b, dst, m, n, k, device, sms, may_split, stream);
