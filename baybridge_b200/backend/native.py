@@ -13,6 +13,7 @@ The ctypes layer plays the role of upstream's ``cuda_driver.py:104-245``
 from __future__ import annotations
 
 import ctypes
+import fcntl
 import hashlib
 import os
 import shutil
@@ -68,12 +69,16 @@ def library_is_current() -> bool:
 
 def build_library(force: bool = False, verbose: bool = False) -> Path:
     """Compile ``csrc/*.cu`` into ``libbb200.so`` for sm_100a (cross-compiles without a GPU)."""
-    with _lock:
+    build_dir = PACKAGE_DIR / "build"
+    build_dir.mkdir(exist_ok=True)
+    # one builder at a time across threads AND processes (ranks of one job share the tree): the others wait on the
+    # file lock and then find the library current; the link goes to a temporary name and is renamed into place, so a
+    # concurrent reader never maps a half-written file
+    with _lock, open(build_dir / ".lock", "w") as lock_file:
+        fcntl.flock(lock_file, fcntl.LOCK_EX)
         if not force and library_is_current():
             return LIBRARY_PATH
         objects: list[Path] = []
-        build_dir = PACKAGE_DIR / "build"
-        build_dir.mkdir(exist_ok=True)
         procs = []
         for source in _sources():
             obj = build_dir / (source.stem + ".o")
@@ -88,10 +93,13 @@ def build_library(force: bool = False, verbose: bool = False) -> Path:
                 print(output)
             if proc.returncode:
                 raise BackendNotImplementedError(f"nvcc failed on {source.name}:\n{output}")
-        link = [nvcc_path(), *GENCODE, "-shared", "-cudart", "static", "-o", str(LIBRARY_PATH), *map(str, objects), "-ldl"]
+        staged = build_dir / f"libbb200.{os.getpid()}.so"
+        link = [nvcc_path(), *GENCODE, "-shared", "-cudart", "static", "-o", str(staged), *map(str, objects), "-ldl"]
         done = subprocess.run(link, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
         if done.returncode:
             raise BackendNotImplementedError(f"linking libbb200.so failed:\n{done.stdout}")
+        STAMP_PATH.unlink(missing_ok=True)
+        os.replace(staged, LIBRARY_PATH)
         STAMP_PATH.write_text(source_digest() + "\n")
         return LIBRARY_PATH
 
