@@ -4,19 +4,37 @@
 //
 // Question: does an `ex2.approx` hold the warp scheduler's dispatch for its 8 cycles, or can FMA-pipe instructions
 // issue underneath it?  Each element runs one ex2 (or a Cody-Waite cubic on the FMA pipe) plus one dependent fma and
-// K independent filler fmas; the program prints cycles per element per warp for 1, 2 and 4 warps per scheduler.
+// K independent filler instructions; the program prints cycles per element per warp for 1, 2 and 4 warps per
+// scheduler.  FILL selects the filler: 0 `fma.rn.f32`, 1 `fma.rn.f32x2` (one packed instruction = two fmas), 2 `add.f32x2`,
+// 3 three-input `max.f32` and 4 `cvt.rn.bf16x2.f32` (both on the ALU pipe).
 // The attention kernel's softmax schedule was sized from these numbers.
 #include <cstdio>
 #include <cstdint>
 #include <cuda_runtime.h>
 __device__ __forceinline__ float fast_exp2(float x) { float y; asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
-template <int K, int MODE>
+__device__ __forceinline__ unsigned long long fma2(unsigned long long a, unsigned long long b, unsigned long long c) {
+  unsigned long long d; asm volatile("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c)); return d;
+}
+__device__ __forceinline__ unsigned long long add2(unsigned long long a, unsigned long long b) {
+  unsigned long long d; asm volatile("add.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b)); return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) { float d; asm volatile("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c)); return d; }
+__device__ __forceinline__ unsigned pack_bf16x2(float a, float b) { unsigned d; asm volatile("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(b), "f"(a)); return d; }
+template <int K, int MODE, int FILL>
 __global__ void __launch_bounds__(512, 1) kern(const float* in, float* out, long long* clocks, int reps) {
   float v[32], acc[8];
+  unsigned long long wide[8];
+  unsigned packed[8];
 #pragma unroll
   for (int i = 0; i < 32; ++i) v[i] = in[(threadIdx.x * 32 + i) & 1023];
 #pragma unroll
-  for (int i = 0; i < 8; ++i) acc[i] = in[i] * 0.001f;
+  for (int i = 0; i < 8; ++i) {
+    acc[i] = in[i] * 0.001f;
+    wide[i] = ((unsigned long long)__float_as_uint(acc[i]) << 32) | __float_as_uint(acc[i] + 1.0f);
+    packed[i] = 0;
+  }
+  const unsigned long long scale2 = ((unsigned long long)__float_as_uint(1.0001f) << 32) | __float_as_uint(1.0001f);
+  const unsigned long long half2 = ((unsigned long long)__float_as_uint(0.5f) << 32) | __float_as_uint(0.5f);
   __syncthreads();
   const long long start = clock64();
   for (int r = 0; r < reps; ++r) {
@@ -34,7 +52,14 @@ __global__ void __launch_bounds__(512, 1) kern(const float* in, float* out, long
         v[i] = e * 0.0f + v[i];
       }
 #pragma unroll
-      for (int k = 0; k < K; ++k) acc[(i + k) & 7] = fmaf(acc[(i + k) & 7], 1.0001f, 0.5f);  // independent FMA-pipe filler
+      for (int k = 0; k < K; ++k) {  // independent filler
+        const int a = (i + k) & 7;
+        if (FILL == 0) acc[a] = fmaf(acc[a], 1.0001f, 0.5f);
+        if (FILL == 1) wide[a] = fma2(wide[a], scale2, half2);
+        if (FILL == 2) wide[a] = add2(wide[a], half2);
+        if (FILL == 3) acc[a] = max3(acc[a], acc[(a + 1) & 7], acc[(a + 2) & 7]);
+        if (FILL == 4) packed[a] ^= pack_bf16x2(acc[a], acc[(a + 1) & 7]);
+      }
     }
   }
   const long long end = clock64();
@@ -42,17 +67,18 @@ __global__ void __launch_bounds__(512, 1) kern(const float* in, float* out, long
 #pragma unroll
   for (int i = 0; i < 32; ++i) s += v[i];
 #pragma unroll
-  for (int i = 0; i < 8; ++i) s += acc[i];
+  for (int i = 0; i < 8; ++i) s += acc[i] + __uint_as_float((unsigned)(wide[i] >> 32)) + __uint_as_float((unsigned)wide[i]) + (float)packed[i];
   out[blockIdx.x * blockDim.x + threadIdx.x] = s;
   if (threadIdx.x == 0 && blockIdx.x == 0) clocks[0] = end - start;
 }
-template <int K, int MODE> void run(const float* in, float* out, long long* clocks, int threads) {
+template <int K, int MODE, int FILL = 0> void run(const float* in, float* out, long long* clocks, int threads) {
   const int reps = 2000;
-  for (int it = 0; it < 2; ++it) kern<K, MODE><<<148, threads>>>(in, out, clocks, reps);
+  for (int it = 0; it < 2; ++it) kern<K, MODE, FILL><<<148, threads>>>(in, out, clocks, reps);
   cudaDeviceSynchronize();
   long long host; cudaMemcpy(&host, clocks, 8, cudaMemcpyDeviceToHost);
-  printf("mode %d (%s) filler FFMA per element %d  warps/scheduler %d : %6.2f clk per element per warp\n", MODE, MODE ? "polynomial" : "ex2", K, threads / 128,
-         (double)host / reps / 32);
+  static const char* const kFillers[] = {"fma.f32", "fma.f32x2", "add.f32x2", "max3.f32", "cvt.bf16x2"};
+  printf("mode %d (%s) filler %s per element %d  warps/scheduler %d : %6.2f clk per element per warp\n", MODE, MODE ? "polynomial" : "ex2",
+         kFillers[FILL], K, threads / 128, (double)host / reps / 32);
 }
 int main() {
   float* in; float* out; long long* clocks;
@@ -63,6 +89,10 @@ int main() {
     run<0, 0>(in, out, clocks, threads); run<1, 0>(in, out, clocks, threads); run<2, 0>(in, out, clocks, threads); run<3, 0>(in, out, clocks, threads);
     run<4, 0>(in, out, clocks, threads); run<6, 0>(in, out, clocks, threads); run<8, 0>(in, out, clocks, threads);
     run<0, 1>(in, out, clocks, threads); run<3, 1>(in, out, clocks, threads);
+    run<1, 0, 1>(in, out, clocks, threads); run<2, 0, 1>(in, out, clocks, threads); run<4, 0, 1>(in, out, clocks, threads);
+    run<1, 0, 2>(in, out, clocks, threads); run<2, 0, 2>(in, out, clocks, threads); run<4, 0, 2>(in, out, clocks, threads);
+    run<1, 0, 3>(in, out, clocks, threads); run<2, 0, 3>(in, out, clocks, threads); run<4, 0, 3>(in, out, clocks, threads);
+    run<1, 0, 4>(in, out, clocks, threads); run<2, 0, 4>(in, out, clocks, threads); run<4, 0, 4>(in, out, clocks, threads);
   }
   printf("%s\n", cudaGetErrorString(cudaGetLastError()));
   return 0;
