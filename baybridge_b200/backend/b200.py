@@ -74,9 +74,12 @@ class B200Backend:
     name = "b200"
     artifact_extension = ".b200.json"
 
-    def __init__(self, *, device: int = 0, synchronize: bool = True):
+    def __init__(self, *, device: int = 0, synchronize: bool = True, overlap_launches: bool = True):
         self.device = device
         self.synchronize = synchronize
+        # flat elementwise kernels are launched with programmatic stream serialisation (``bb200_launch_dependent``):
+        # stream order is kept by the kernel's own ``griddepcontrol.wait``; False takes the plain launch
+        self.overlap_launches = overlap_launches
 
     # -- contract: capability probes ---------------------------------------------------------------
     def available(self, target: Any = None) -> bool:
@@ -351,7 +354,11 @@ class B200Backend:
                 vector_flag.value = 0 if misaligned & 15 else 1
             if debug_bounds:
                 native.call("bb200_device_status_address", ctypes.byref(status_slot))  # the current device's word
-            native.call("bb200_launch", function, grid, block, cluster, 0, stream_handle, params)
+            # the flat kernels wait (griddepcontrol.wait) for the kernel before them before they touch memory, so their
+            # CTAs may be placed while that kernel drains; a recording stream takes the plain launch
+            overlapped = flat and self.overlap_launches and not native.recording()
+            native.call("bb200_launch_dependent" if overlapped else "bb200_launch", function, grid, block, cluster, 0,
+                        stream_handle, params)
 
         functions: dict[int, Any] = state.setdefault("functions", {})
         # the parameter block is built once; a call only rewrites the values (launchers are not thread-safe, like upstream's)

@@ -132,6 +132,7 @@ PROTOTYPES: dict[str, list[Any]] = {
     "bb200_get_function": [P, ctypes.c_char_p, PP],
     "bb200_function_set_dynamic_smem": [P, ctypes.c_uint],
     "bb200_launch": [P, U3, U3, U3, ctypes.c_uint, P, PP],
+    "bb200_launch_dependent": [P, U3, U3, U3, ctypes.c_uint, P, PP],
     "bb200_device_synchronize": [],
     "bb200_stream_synchronize": [P],
     "bb200_stream_create": [PP],

@@ -371,13 +371,13 @@ int bb200_function_set_dynamic_smem(void* function, unsigned bytes) {
                       "cuFuncSetAttribute(MAX_DYNAMIC_SHARED_SIZE_BYTES)");
 }
 
-int bb200_launch(void* function, const unsigned grid[3], const unsigned block[3], const unsigned cluster[3],
-                 unsigned dynamic_smem_bytes, void* stream, void** params) {
-  if (!function || !grid || !block) return fail(BB200_E_INVALID_ARGUMENT, "bb200_launch: null function or dimensions");
+static int launch_with(void* function, const unsigned grid[3], const unsigned block[3], const unsigned cluster[3],
+                       unsigned dynamic_smem_bytes, void* stream, void** params, bool dependent, const char* what) {
+  if (!function || !grid || !block) return fail(BB200_E_INVALID_ARGUMENT, "%s: null function or dimensions", what);
   for (int axis = 0; axis < 3; ++axis)
-    if (!grid[axis] || !block[axis]) return fail(BB200_E_INVALID_ARGUMENT, "bb200_launch: zero grid/block extent");
+    if (!grid[axis] || !block[axis]) return fail(BB200_E_INVALID_ARGUMENT, "%s: zero grid/block extent", what);
   if ((uint64_t)block[0] * block[1] * block[2] > 1024)
-    return fail(BB200_E_INVALID_ARGUMENT, "bb200_launch: more than 1024 threads per block");
+    return fail(BB200_E_INVALID_ARGUMENT, "%s: more than 1024 threads per block", what);
   BB200_DRIVER_OR_RETURN(api);
   CUlaunchConfig config;
   memset(&config, 0, sizeof(config));
@@ -385,22 +385,40 @@ int bb200_launch(void* function, const unsigned grid[3], const unsigned block[3]
   config.blockDimX = block[0]; config.blockDimY = block[1]; config.blockDimZ = block[2];
   config.sharedMemBytes = dynamic_smem_bytes;
   config.hStream = static_cast<CUstream>(stream);
-  CUlaunchAttribute attribute;
-  const bool clustered = cluster && (cluster[0] * cluster[1] * cluster[2] > 1);
-  if (clustered) {
+  CUlaunchAttribute attributes[2];
+  memset(attributes, 0, sizeof(attributes));
+  unsigned count = 0;
+  if (cluster && (cluster[0] * cluster[1] * cluster[2] > 1)) {
     for (int axis = 0; axis < 3; ++axis)
       if (!cluster[axis] || grid[axis] % cluster[axis])
-        return fail(BB200_E_INVALID_ARGUMENT, "bb200_launch: grid must be a multiple of the cluster on every axis");
-    memset(&attribute, 0, sizeof(attribute));
-    attribute.id = CU_LAUNCH_ATTRIBUTE_CLUSTER_DIMENSION;
-    attribute.value.clusterDim.x = cluster[0];
-    attribute.value.clusterDim.y = cluster[1];
-    attribute.value.clusterDim.z = cluster[2];
-    config.attrs = &attribute;
-    config.numAttrs = 1;
+        return fail(BB200_E_INVALID_ARGUMENT, "%s: grid must be a multiple of the cluster on every axis", what);
+    attributes[count].id = CU_LAUNCH_ATTRIBUTE_CLUSTER_DIMENSION;
+    attributes[count].value.clusterDim.x = cluster[0];
+    attributes[count].value.clusterDim.y = cluster[1];
+    attributes[count].value.clusterDim.z = cluster[2];
+    ++count;
+  }
+  if (dependent) {
+    attributes[count].id = CU_LAUNCH_ATTRIBUTE_PROGRAMMATIC_STREAM_SERIALIZATION;
+    attributes[count].value.programmaticStreamSerializationAllowed = 1;
+    ++count;
+  }
+  if (count) {
+    config.attrs = attributes;
+    config.numAttrs = count;
   }
   return check_driver(api, api->cuLaunchKernelEx(&config, static_cast<CUfunction>(function), params, nullptr),
                       "cuLaunchKernelEx");
+}
+
+int bb200_launch(void* function, const unsigned grid[3], const unsigned block[3], const unsigned cluster[3],
+                 unsigned dynamic_smem_bytes, void* stream, void** params) {
+  return launch_with(function, grid, block, cluster, dynamic_smem_bytes, stream, params, false, "bb200_launch");
+}
+
+int bb200_launch_dependent(void* function, const unsigned grid[3], const unsigned block[3], const unsigned cluster[3],
+                           unsigned dynamic_smem_bytes, void* stream, void** params) {
+  return launch_with(function, grid, block, cluster, dynamic_smem_bytes, stream, params, true, "bb200_launch_dependent");
 }
 
 int bb200_device_synchronize(void) {

@@ -160,6 +160,11 @@ template <int UNROLL, typename Body> __device__ __forceinline__ void flat_map(co
   constexpr int VEC = Body::VEC;
   const size_t tile = (size_t)blockDim.x * VEC * UNROLL;
   const size_t tile_base = (size_t)blockIdx.x * tile;
+  // Launched with programmatic stream serialisation, the next kernel of the stream may place its CTAs on SMs this
+  // grid has left while this grid's last CTAs still run; such a CTA stops at `griddepcontrol.wait` until the grid before
+  // it has completed and its writes are visible.  Without that launch attribute both instructions do nothing.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   if (tile_base >= n) return;
   if (vector_ok && tile_base + tile <= n) {
     typename Body::Regs regs[UNROLL];

@@ -17,6 +17,38 @@ int check_runtime(cudaError_t err, const char* what);
 // After a kernel launch: pick up launch-configuration errors without synchronising.
 inline int check_launch(const char* what) { return check_runtime(cudaGetLastError(), what); }
 
+// Launch `kernel` with programmatic stream serialisation: its CTAs may be placed while the kernel before it on `stream`
+// drains.  ONLY for kernels that run `dependent_launch_prologue()` (below) before their first global-memory access.
+// A capturing stream takes the ordinary launch.
+template <typename... Params, typename... Args>
+inline void launch_dependent(void (*kernel)(Params...), dim3 grid, dim3 block, size_t dynamic_smem, cudaStream_t stream, Args... args) {
+  cudaStreamCaptureStatus capture = cudaStreamCaptureStatusNone;
+  const bool capturing = cudaStreamIsCapturing(stream, &capture) != cudaSuccess || capture != cudaStreamCaptureStatusNone;
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = dynamic_smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute = {};
+  attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute.val.programmaticStreamSerializationAllowed = 1;
+  if (!capturing) {
+    config.attrs = &attribute;
+    config.numAttrs = 1;
+  }
+  cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);  // the caller reads the status with check_launch()
+}
+
+#ifdef __CUDACC__
+// First statement of a kernel launched with launch_dependent(): lets the kernel behind this one be placed early in its
+// turn, then waits until the kernel before this one has completed and its writes are visible.  Without the launch
+// attribute both instructions do nothing.
+__device__ __forceinline__ void dependent_launch_prologue() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+#endif
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 inline size_t dtype_bytes(bb200_dtype t) {

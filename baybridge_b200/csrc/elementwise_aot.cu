@@ -61,7 +61,7 @@ template <typename T, Fused OP> int launch(const void* a, const void* b, void* c
   BinaryBody<T, OP> body{static_cast<const T*>(a), static_cast<const T*>(b), static_cast<T*>(c)};
   const bool vector_ok = aligned16(a) && aligned16(b) && aligned16(c);
   const unsigned grid = flat_map_grid(n, kThreads, BinaryBody<T, OP>::VEC, kUnroll);
-  binary_kernel<T, OP><<<grid, kThreads, 0, stream>>>(body, n, vector_ok);
+  launch_dependent(binary_kernel<T, OP>, dim3(grid), dim3(kThreads), 0, stream, body, n, vector_ok);  // flat_map waits for the kernel before
   return check_launch("elementwise kernel launch");
 }
 

@@ -49,6 +49,7 @@ layernorm_rows(const T* __restrict__ x, const T* __restrict__ residual, const T*
   T* __restrict__ out = static_cast<T*>(dst.out[0]);
   T* __restrict__ out_resid = static_cast<T*>(dst.out_resid[0]);
   __shared__ float scratch[32];
+  dependent_launch_prologue();
   const size_t row = blockIdx.x;
   if (row >= rows) return;
   const size_t offset = row * (size_t)hidden;
@@ -125,9 +126,10 @@ template <typename T, int THREADS, int VPT>
 int launch(const void* x, const void* residual, const void* weight, const void* bias, const LayerNormDestinations& dst, size_t rows,
            size_t hidden, int weight_is_full, int bias_is_full, float epsilon, cudaStream_t stream) {
   if (dst.count == 1 && dst.row_offset == 0) {
-    layernorm_rows<T, THREADS, VPT, false><<<(unsigned)rows, THREADS, 0, stream>>>(
-        static_cast<const T*>(x), static_cast<const T*>(residual), static_cast<const T*>(weight), static_cast<const T*>(bias), dst,
-        rows, (int)hidden, weight_is_full ? hidden : 0, bias_is_full ? hidden : 0, epsilon);
+    launch_dependent(layernorm_rows<T, THREADS, VPT, false>, dim3((unsigned)rows), dim3(THREADS), 0, stream,
+                     static_cast<const T*>(x), static_cast<const T*>(residual), static_cast<const T*>(weight),
+                     static_cast<const T*>(bias), dst, rows, (int)hidden, (size_t)(weight_is_full ? hidden : 0),
+                     (size_t)(bias_is_full ? hidden : 0), epsilon);
   } else {
     layernorm_rows<T, THREADS, VPT, true><<<(unsigned)rows, THREADS, 0, stream>>>(
         static_cast<const T*>(x), static_cast<const T*>(residual), static_cast<const T*>(weight), static_cast<const T*>(bias), dst,

@@ -48,6 +48,7 @@ rmsnorm_rows(const T* __restrict__ x, const T* __restrict__ gamma, const __grid_
              size_t gamma_row_stride, float epsilon) {
   constexpr int VEC = 16 / sizeof(T);
   __shared__ float scratch[32];
+  dependent_launch_prologue();
   const size_t row = blockIdx.x;
   if (row >= rows) return;
   const T* __restrict__ xr = x + row * (size_t)hidden;
@@ -115,8 +116,9 @@ template <typename T, int THREADS, int VPT, bool CACHED>
 int launch(const void* x, const void* gamma, const RowDestinations& out, size_t rows, size_t hidden, int gamma_is_full, float epsilon,
            cudaStream_t stream) {
   if (out.count == 1 && out.row_offset == 0)
-    rmsnorm_rows<T, THREADS, VPT, CACHED, false><<<(unsigned)rows, THREADS, 0, stream>>>(
-        static_cast<const T*>(x), static_cast<const T*>(gamma), out, rows, (int)hidden, gamma_is_full ? hidden : 0, epsilon);
+    launch_dependent(rmsnorm_rows<T, THREADS, VPT, CACHED, false>, dim3((unsigned)rows), dim3(THREADS), 0, stream,
+                     static_cast<const T*>(x), static_cast<const T*>(gamma), out, rows, (int)hidden,
+                     (size_t)(gamma_is_full ? hidden : 0), epsilon);
   else
     rmsnorm_rows<T, THREADS, VPT, CACHED, true><<<(unsigned)rows, THREADS, 0, stream>>>(
         static_cast<const T*>(x), static_cast<const T*>(gamma), out, rows, (int)hidden, gamma_is_full ? hidden : 0, epsilon);

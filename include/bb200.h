@@ -117,6 +117,18 @@ int bb200_function_set_dynamic_smem(void* function, unsigned bytes);
 int bb200_launch(void* function, const unsigned grid[3], const unsigned block[3], const unsigned cluster[3],
                  unsigned dynamic_smem_bytes, void* stream, void** params);
 
+/* bb200_launch with programmatic stream serialisation (CU_LAUNCH_ATTRIBUTE_PROGRAMMATIC_STREAM_SERIALIZATION): the
+ * kernel's CTAs may be placed on SMs that the kernel before it on `stream` has already left, while that kernel's last
+ * CTAs still run, which hides the launch latency and the ramp of a short kernel (1.6 us per launch measured).  ONLY for
+ * kernels that execute `griddepcontrol.wait` before their first global-memory access — the wait returns once the kernel
+ * before has completed and its writes are visible, so stream order is kept; the generated flat elementwise kernels do
+ * (csrc/bb200_elementwise.cuh), and they execute `griddepcontrol.launch_dependents` first so that a dependent kernel
+ * behind them may start early in turn.  After anything that is not a kernel (a copy, a memset, an event wait) the
+ * launch is an ordinary one.  No upstream counterpart (upstream launches and synchronises one kernel at a time,
+ * src/baybridge/cuda_driver.py:377-419). */
+int bb200_launch_dependent(void* function, const unsigned grid[3], const unsigned block[3], const unsigned cluster[3],
+                           unsigned dynamic_smem_bytes, void* stream, void** params);
+
 /* Replaces CudaDriver.synchronize / synchronize_stream (src/baybridge/cuda_driver.py:302-325). */
 int bb200_device_synchronize(void);
 int bb200_stream_synchronize(void* stream);

@@ -131,15 +131,19 @@ CUresult cuFuncSetAttribute(CUfunction function, CUfunction_attribute attribute,
 CUresult cuLaunchKernelEx(const CUlaunchConfig* config, CUfunction function, void** params, void** extra) {
   (void)params, (void)extra;
   unsigned cluster[3] = {1, 1, 1};
-  for (unsigned i = 0; i < config->numAttrs; ++i)
+  int dependent = 0;
+  for (unsigned i = 0; i < config->numAttrs; ++i) {
     if (config->attrs[i].id == CU_LAUNCH_ATTRIBUTE_CLUSTER_DIMENSION) {
       cluster[0] = config->attrs[i].value.clusterDim.x;
       cluster[1] = config->attrs[i].value.clusterDim.y;
       cluster[2] = config->attrs[i].value.clusterDim.z;
     }
-  ENTER(cuLaunchKernelEx, "function=%p grid=%u,%u,%u block=%u,%u,%u cluster=%u,%u,%u smem=%u stream=%p", (void*)function,
-        config->gridDimX, config->gridDimY, config->gridDimZ, config->blockDimX, config->blockDimY, config->blockDimZ,
-        cluster[0], cluster[1], cluster[2], config->sharedMemBytes, (void*)config->hStream);
+    if (config->attrs[i].id == CU_LAUNCH_ATTRIBUTE_PROGRAMMATIC_STREAM_SERIALIZATION)
+      dependent = config->attrs[i].value.programmaticStreamSerializationAllowed;
+  }
+  ENTER(cuLaunchKernelEx, "function=%p grid=%u,%u,%u block=%u,%u,%u cluster=%u,%u,%u smem=%u dependent=%d stream=%p",
+        (void*)function, config->gridDimX, config->gridDimY, config->gridDimZ, config->blockDimX, config->blockDimY,
+        config->blockDimZ, cluster[0], cluster[1], cluster[2], config->sharedMemBytes, dependent, (void*)config->hStream);
   return CUDA_SUCCESS;
 }
 

@@ -111,6 +111,8 @@ def test_module_load_get_function_and_launch_forward_their_arguments(fake_driver
         stream = ctypes.c_void_p(0x1234)
         native.call("bb200_launch", function, native.U3(296, 1, 1), native.U3(192, 1, 1), native.U3(2, 1, 1), 200 * 1024, stream, params)
         native.call("bb200_launch", function, native.U3(5, 6, 7), native.U3(32, 2, 1), native.U3(1, 1, 1), 0, None, params)
+        native.call("bb200_launch_dependent", function, native.U3(9, 1, 1), native.U3(256, 1, 1), native.U3(1, 1, 1), 0, stream, params)
+        native.call("bb200_launch_dependent", function, native.U3(8, 1, 1), native.U3(64, 1, 1), native.U3(4, 1, 1), 1024, stream, params)
         native.call("bb200_stream_synchronize", stream)
         native.call("bb200_device_synchronize")
         native.call("bb200_module_unload", module)
@@ -121,8 +123,11 @@ def test_module_load_get_function_and_launch_forward_their_arguments(fake_driver
     assert calls(log, "cuModuleGetFunction") == ["cuModuleGetFunction module=0xa001 name=my_kernel"]
     assert calls(log, "cuFuncSetAttribute") == [f"cuFuncSetAttribute function=0x1a001 attribute=8 value={200 * 1024}"]
     assert calls(log, "cuLaunchKernelEx") == [
-        f"cuLaunchKernelEx function=0x1a001 grid=296,1,1 block=192,1,1 cluster=2,1,1 smem={200 * 1024} stream=0x1234",
-        "cuLaunchKernelEx function=0x1a001 grid=5,6,7 block=32,2,1 cluster=1,1,1 smem=0 stream=(nil)",
+        f"cuLaunchKernelEx function=0x1a001 grid=296,1,1 block=192,1,1 cluster=2,1,1 smem={200 * 1024} dependent=0 stream=0x1234",
+        "cuLaunchKernelEx function=0x1a001 grid=5,6,7 block=32,2,1 cluster=1,1,1 smem=0 dependent=0 stream=(nil)",
+        # programmatic stream serialisation reaches the driver as a launch attribute, next to the cluster when there is one
+        "cuLaunchKernelEx function=0x1a001 grid=9,1,1 block=256,1,1 cluster=1,1,1 smem=0 dependent=1 stream=0x1234",
+        "cuLaunchKernelEx function=0x1a001 grid=8,1,1 block=64,1,1 cluster=4,1,1 smem=1024 dependent=1 stream=0x1234",
     ]
     assert calls(log, "cuStreamSynchronize") == ["cuStreamSynchronize stream=0x1234"]
     assert calls(log, "cuCtxSynchronize") == ["cuCtxSynchronize "]
@@ -141,9 +146,14 @@ def test_launch_validates_before_it_reaches_the_driver(fake_driver, tmp_path):
                 outcomes.append("ok")
             except CudaDriverError as error:
                 outcomes.append(error.name)
+            try:
+                native.call("bb200_launch_dependent", function, native.U3(*grid), native.U3(*block), native.U3(*cluster), 0, None, params)
+                outcomes.append("ok")
+            except CudaDriverError as error:
+                outcomes.append(error.name)
         result = {"outcomes": outcomes}
     """)
-    assert result["outcomes"] == ["BB200_E_INVALID_ARGUMENT"] * 3
+    assert result["outcomes"] == ["BB200_E_INVALID_ARGUMENT"] * 6
     assert not calls(log, "cuLaunchKernelEx")
 
 
@@ -229,6 +239,21 @@ def test_launcher_forwards_the_stream_and_synchronises_it(fake_driver, tmp_path)
     assert "positional arguments" in result["kwarg"] and "expects 3 arguments, got 1" in result["arity"]
 
 
+def test_flat_elementwise_launches_are_dependent_launches_unless_switched_off(fake_driver, tmp_path):
+    """The flat elementwise kernels keep stream order themselves (``griddepcontrol.wait``), so their launcher asks for
+    programmatic stream serialisation; ``B200Backend(overlap_launches=False)`` takes the plain launch, and so does a
+    thread-by-thread (literal) kernel, which has no such wait."""
+    _, log = run_child(fake_driver, tmp_path, ELEMENTWISE_CHILD + """
+    tensors = [FakeCudaTensor((n,), "float32", 0x10000 * (i + 1)) for i in range(3)]
+    cute.compile(zoo.make_indexed_binary("add", n), *tensors, backend=B200Backend(), cache_dir=%r)(*tensors)
+    cute.compile(zoo.make_indexed_binary("add", n), *tensors, backend=B200Backend(overlap_launches=False), cache_dir=%r)(*tensors)
+    cute.compile(zoo.make_indexed_reverse(n), *tensors[:2], backend=B200Backend(), cache_dir=%r)(*tensors[:2])
+    result = {}
+    """ % (str(tmp_path / "cache"), str(tmp_path / "cache"), str(tmp_path / "cache")))
+    launches = calls(log, "cuLaunchKernelEx")
+    assert ["dependent=1" in line for line in launches] == [True, False, False]
+
+
 def test_launcher_keeps_one_module_per_device(fake_driver, tmp_path):
     _, log = run_child(fake_driver, tmp_path, ELEMENTWISE_CHILD + """
     artifact = None
@@ -260,7 +285,7 @@ def test_a_failed_launch_raises_and_releases_the_staged_copies(fake_driver, tmp_
     except CudaDriverError as error:
         result = {"raised": True, "op": error.op, "status": error.status}
     """ % str(tmp_path / "cache"), fail="cuLaunchKernelEx=719")
-    assert result == {"raised": True, "op": "bb200_launch", "status": 719}
+    assert result == {"raised": True, "op": "bb200_launch_dependent", "status": 719}
     allocated = [line.split("pointer=")[1] for line in calls(log, "cuMemAlloc.result")]
     freed = [line.split("pointer=")[1] for line in calls(log, "cuMemFree")]
     assert len(allocated) == 3 and sorted(allocated) == sorted(freed)

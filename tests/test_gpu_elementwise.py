@@ -4,7 +4,7 @@ from __future__ import annotations
 import numpy as np
 import pytest
 from conftest import golden_cases, golden_ir, golden_vec
-from gpu_util import current_stream, device_zeros, expect_rounded, to_device, to_host, void_p
+from gpu_util import current_stream, device_zeros, expect_rounded, to_device, to_host, torch_module, void_p
 
 from oracle import cpu_runtime as oracle
 
@@ -366,3 +366,77 @@ def test_flat_lowering_rank3_digits_and_in_place_update(tmp_path):
 
     plan = match(artifact.ir)
     assert plan.mode == "flat" and plan.extent == total  # (i//160, (i//16)%10, i%16) on [6,10,16] is proved to be offset i
+
+
+def test_back_to_back_dependent_launches_keep_stream_order(zoo, tmp_path):
+    """Flat elementwise kernels are launched with programmatic stream serialisation: a kernel's CTAs may be placed
+    while the kernel before it drains, and ``griddepcontrol.wait`` holds them until its writes are visible.  A chain of
+    adds in which every launch reads what the launch before wrote (no synchronisation in between, buffers much larger
+    than what one wave of CTAs covers), with a library kernel of another framework in the middle of the chain, must
+    give exactly the serial result."""
+    import baybridge_b200 as cute
+    from baybridge_b200 import B200Backend
+
+    torch = torch_module()
+    n = 1 << 23
+    rng = np.random.default_rng(77)
+    start = rng.integers(-64, 64, n).astype(np.float32)
+    step = rng.integers(-8, 8, n).astype(np.float32)
+    g_step = to_device(step, "f32")
+    ping, pong = to_device(start, "f32"), device_zeros((n,), "f32")
+    kernel = zoo.make_indexed_binary("add", n)
+    artifact = cute.compile(kernel, ping, g_step, pong, backend=B200Backend(synchronize=False), cache_dir=tmp_path)
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+    launches = 24
+    with torch.cuda.stream(stream):
+        handles = {id(t): cute.from_dlpack(t) for t in (ping, pong, g_step)}
+        source, destination = ping, pong
+        for index in range(launches):
+            artifact(handles[id(source)], handles[id(g_step)], handles[id(destination)], stream=stream.cuda_stream)
+            source, destination = destination, source
+            if index == launches // 2 - 1:
+                source.add_(1.0)  # a torch kernel between two of ours, on the same stream
+    stream.synchronize()
+    expected = start + launches * step + 1.0  # small integers: every partial sum is exact in f32
+    assert np.array_equal(source.cpu().numpy(), expected)
+
+
+def test_dependent_launches_see_a_cached_operand_rewritten_by_the_kernel_before(zoo, tmp_path):
+    """The row vector of a broadcast is fetched with ordinary cached loads (it is shared by every row).  Alternate a
+    kernel that uses it with a kernel that rewrites it, back to back and unsynchronised: every use must see the value
+    the launch before it stored, although its CTAs may have been placed before that launch had finished."""
+    import baybridge_b200 as cute
+    from baybridge_b200 import B200Backend
+
+    torch = torch_module()
+    rows, cols = 2048, 4096
+    rng = np.random.default_rng(78)
+    a = rng.integers(-16, 16, (rows, cols)).astype(np.float32)
+    row = rng.integers(-4, 4, (1, cols)).astype(np.float32)
+    col = np.ones((rows, 1), dtype=np.float32)
+    one = np.ones((1, cols), dtype=np.float32)
+    g_a, g_row, g_col, g_one = (to_device(v, "f32") for v in (a, row, col, one))
+    g_next, g_out = device_zeros((1, cols), "f32"), device_zeros((rows, cols), "f32")
+    backend = B200Backend(synchronize=False)
+    use = cute.compile(zoo.ssa_broadcast_row_col, g_a, g_row, g_col, g_out, backend=backend, cache_dir=tmp_path)
+
+    @cute.kernel
+    def bump(src: cute.Tensor, step: cute.Tensor, dst: cute.Tensor):
+        dst.store(src.load() + step.load())
+
+    bump_artifact = cute.compile(bump, g_row, g_one, g_next, backend=backend, cache_dir=tmp_path)
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+    handle = {id(t): cute.from_dlpack(t) for t in (g_a, g_row, g_col, g_one, g_next, g_out)}
+    rounds = 10
+    with torch.cuda.stream(stream):
+        current, spare = g_row, g_next
+        for _ in range(rounds):
+            use(handle[id(g_a)], handle[id(current)], handle[id(g_col)], handle[id(g_out)], stream=stream.cuda_stream)
+            bump_artifact(handle[id(current)], handle[id(g_one)], handle[id(spare)], stream=stream.cuda_stream)
+            current, spare = spare, current
+        use(handle[id(g_a)], handle[id(current)], handle[id(g_col)], handle[id(g_out)], stream=stream.cuda_stream)
+    stream.synchronize()
+    assert np.array_equal(g_out.cpu().numpy(), a + (row + rounds))
+    assert np.array_equal(current.cpu().numpy(), row + rounds)

@@ -86,3 +86,39 @@ def test_config4_full_size_rmsnorm(zoo, tmp_path):
     artifact(x * 2, doubled, w)
     # at most one bf16 unit in the last place apart (8 significant bits)
     assert bool(((doubled.float() - out.float()).abs() <= out.float().abs() * 2.0 ** -7).all())
+
+
+def test_back_to_back_norm_launches_keep_stream_order():
+    """The single-destination RMSNorm and LayerNorm kernels are launched with programmatic stream serialisation (their
+    CTAs may be placed while the kernel before drains; ``griddepcontrol.wait`` holds them until its writes are visible).
+    A chain in which every launch reads the rows the launch before wrote, without synchronisation, must give bit for bit
+    what the same chain gives with a device synchronise after every launch."""
+    import torch
+
+    from baybridge_b200.backend import native
+
+    rows, hidden = 16384, 2048  # 64 MB per tensor: many waves of CTAs per launch
+    generator = torch.Generator(device="cuda").manual_seed(4242)
+    x = torch.randn((rows, hidden), device="cuda", generator=generator).to(torch.bfloat16)
+    weight = (1.0 + 0.25 * torch.randn((hidden,), device="cuda", generator=generator)).to(torch.bfloat16)
+    bias = (0.1 * torch.randn((hidden,), device="cuda", generator=generator)).to(torch.bfloat16)
+    residual = (0.5 * torch.randn((rows, hidden), device="cuda", generator=generator)).to(torch.bfloat16)
+    code = native.DTYPE_CODES["bf16"]
+
+    def chain(synchronise: bool):
+        ping, pong, summed = x.clone(), torch.empty_like(x), torch.empty_like(x)
+        torch.cuda.synchronize()
+        stream = current_stream()
+        for index in range(12):
+            if index % 3 == 2:
+                native.call("bb200_layernorm", code, void_p(ping), void_p(residual), void_p(weight), void_p(bias), void_p(pong),
+                            void_p(summed), rows, hidden, 0, 0, 1e-5, stream)
+            else:
+                native.call("bb200_rmsnorm", code, void_p(ping), void_p(weight), void_p(pong), rows, hidden, 0, 1e-6, stream)
+            if synchronise:
+                torch.cuda.synchronize()
+            ping, pong = pong, ping
+        torch.cuda.synchronize()
+        return ping
+
+    assert torch.equal(chain(False), chain(True))
