@@ -157,6 +157,7 @@ class B200Backend:
         # kernels that can record a code in the device status word: the mbarrier pipelines (bounded waits) and the
         # bounds-checking debug build of thread-by-thread elementwise kernels
         waits_on_device = plan.kind in ("gemm", "attention") or bool(record.get("debug_bounds"))
+        checked: dict[tuple[int, int], Any] = {}  # (argument position, id of handle) -> handle already validated there
 
         def launcher(*args: Any, **kwargs: Any) -> None:
             stream = kwargs.pop("stream", None)
@@ -173,10 +174,17 @@ class B200Backend:
                 device_id = None
                 for position in tensor_positions:
                     value = args[position]
-                    shape, dtype, stride = expected[position]
-                    if (type(value) is not TensorHandle or value.device_type != DLPACK_CUDA or tuple(value.shape) != shape
-                            or normalize_dtype_name(value.dtype) != dtype or (value.stride is not None and tuple(value.stride) != stride)
-                            or (device_id is not None and value.device_id != device_id)):
+                    known = checked.get((position, id(value)))
+                    if known is not value:
+                        # a handle is immutable: its shape, dtype and strides are compared once per argument position
+                        shape, dtype, stride = expected[position]
+                        if (type(value) is not TensorHandle or value.device_type != DLPACK_CUDA or tuple(value.shape) != shape
+                                or normalize_dtype_name(value.dtype) != dtype or (value.stride is not None and tuple(value.stride) != stride)):
+                            break
+                        if len(checked) >= 256:
+                            checked.clear()
+                        checked[(position, id(value))] = value  # keeps the handle alive, so its id cannot be reused
+                    if device_id is not None and value.device_id != device_id:
                         break
                     device_id = value.device_id
                     pointer = value.data_ptr() or value.raw_address
@@ -357,10 +365,11 @@ class B200Backend:
             # the flat kernels wait (griddepcontrol.wait) for the kernel before them before they touch memory, so their
             # CTAs may be placed while that kernel drains; a recording stream takes the plain launch
             overlapped = flat and self.overlap_launches and not native.recording()
-            native.call("bb200_launch_dependent" if overlapped else "bb200_launch", function, grid, block, cluster, 0,
-                        stream_handle, params)
+            native.call_resolved(launch_dependent if overlapped else launch_plain, "bb200_launch_dependent" if overlapped else "bb200_launch",
+                                 function, grid, block, cluster, 0, stream_handle, params)
 
         functions: dict[int, Any] = state.setdefault("functions", {})
+        launch_plain, launch_dependent = native.entry_point("bb200_launch"), native.entry_point("bb200_launch_dependent")
         # the parameter block is built once; a call only rewrites the values (launchers are not thread-safe, like upstream's)
         tensor_slots = [ctypes.c_void_p() for _ in tensor_order]
         scalar_slots = [ctype() for ctype in scalar_ctypes]

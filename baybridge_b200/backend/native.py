@@ -205,6 +205,19 @@ def call(name: str, *args: Any) -> None:
         raise CudaDriverError(name, status, ERROR_NAMES.get(status, "CUDA_ERROR" if status > 0 else "BB200_ERROR"), message)
 
 
+def entry_point(name: str) -> Any:
+    """The prototyped C function ``name``, for callers on a hot path that do not want the lookup per call."""
+    return getattr(library(), name)
+
+
+def call_resolved(function: Any, name: str, *args: Any) -> None:
+    """``call`` for a function obtained from ``entry_point``."""
+    status = function(*args)
+    if status != 0:
+        message = (library().bb200_last_error() or b"").decode("utf-8", "replace")
+        raise CudaDriverError(name, status, ERROR_NAMES.get(status, "CUDA_ERROR" if status > 0 else "BB200_ERROR"), message)
+
+
 def take_device_status(stream: ctypes.c_void_p) -> int:
     """Synchronise ``stream``, then read and clear the device status word (0 = no bounded wait gave up)."""
     status = ctypes.c_int(0)

@@ -26,7 +26,7 @@ from pathlib import Path
 from typing import Any, Callable
 
 from .errors import BackendNotImplementedError, CompilationError
-from .host_values import infer_runtime_spec, normalize_runtime_argument
+from .host_values import TensorHandle, infer_runtime_spec, normalize_runtime_argument
 from .portable_ir import PortableKernelIR, ScalarSpec, TensorSpec
 from .targets import B200, AMDTarget, NvidiaTarget
 from .trace import IRBuilder, ScalarValue, TensorValue, tracing
@@ -215,7 +215,14 @@ class CompiledKernel:
                 f"backend '{self.backend_name}' produced IR only; compile with backend='b200' to get a launchable artifact "
                 "(baybridge_b200 has no CPU runtime)"
             )
-        stream = kwargs.get("stream")
+        stream = kwargs.get("stream") if kwargs else None
+        for arg in args:
+            if type(arg) is not TensorHandle:
+                break
+        else:
+            # the hot call: device tensor handles only (plus stream=) need no normalisation
+            if not kwargs or (len(kwargs) == 1 and "stream" in kwargs):
+                return self.runtime_callable(*args, **kwargs)
         args = tuple(normalize_runtime_argument(arg, stream=stream) for arg in args)
         kwargs = {
             name: value if name == "stream" else normalize_runtime_argument(value, stream=stream)
@@ -268,7 +275,11 @@ def _bind_user_arguments(definition, backend_launcher: Callable[..., Any], bindi
     def launcher(*args: Any, **kwargs: Any) -> Any:
         if direct and len(args) == len(positional) and (not kwargs or (len(kwargs) == 1 and "stream" in kwargs)):
             stream = kwargs.get("stream") if kwargs else None
-            leaves = [normalize_runtime_argument(args[index], stream=stream) for index in order]
+            leaves = [args[index] for index in order]
+            for leaf in leaves:
+                if type(leaf) is not TensorHandle:
+                    leaves = [normalize_runtime_argument(value, stream=stream) for value in leaves]
+                    break
             return backend_launcher(*leaves) if stream is None else backend_launcher(*leaves, stream=stream)
         stream = None if "stream" in signature.parameters else kwargs.pop("stream", None)
         bound = signature.bind_partial(*args, **kwargs).arguments
