@@ -41,6 +41,20 @@ __global__ void __launch_bounds__(512, 1) kern(const float* in, float* out, long
 #pragma unroll
     for (int i = 0; i < 32; ++i) {
       if (MODE == 0) v[i] = fast_exp2(v[i]) * 0.0f + v[i];  // 1 ex2 + 1 ffma per element (dependent, but 32 independent chains)
+      if (MODE == 2 && (i & 1) == 0) {  // one packed bf16x2 ex2 for elements i and i+1 (inputs packed first, result left packed)
+        unsigned packed_in, packed_out;
+        asm volatile("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(packed_in) : "f"(v[i + 1]), "f"(v[i]));
+        asm volatile("ex2.approx.ftz.bf16x2 %0, %1;" : "=r"(packed_out) : "r"(packed_in));
+        v[i] = __uint_as_float(packed_out << 16) * 0.0f + v[i];
+        v[i + 1] = __uint_as_float(packed_out & 0xffff0000u) * 0.0f + v[i + 1];
+      }
+      if (MODE == 3 && (i & 1) == 0) {  // the same with f16x2
+        unsigned packed_in, packed_out;
+        asm volatile("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(packed_in) : "f"(v[i + 1]), "f"(v[i]));
+        asm volatile("ex2.approx.f16x2 %0, %1;" : "=r"(packed_out) : "r"(packed_in));
+        v[i] = __uint_as_float(packed_out << 16) * 0.0f + v[i];
+        v[i + 1] = __uint_as_float(packed_out & 0xffff0000u) * 0.0f + v[i + 1];
+      }
       if (MODE == 1) {  // scalar polynomial exp2: no MUFU
         float x = v[i];
         const float t = x + 12582912.0f;
@@ -77,7 +91,7 @@ template <int K, int MODE, int FILL = 0> void run(const float* in, float* out, l
   cudaDeviceSynchronize();
   long long host; cudaMemcpy(&host, clocks, 8, cudaMemcpyDeviceToHost);
   static const char* const kFillers[] = {"fma.f32", "fma.f32x2", "add.f32x2", "max3.f32", "cvt.bf16x2"};
-  printf("mode %d (%s) filler %s per element %d  warps/scheduler %d : %6.2f clk per element per warp\n", MODE, MODE ? "polynomial" : "ex2",
+  printf("mode %d (%s) filler %s per element %d  warps/scheduler %d : %6.2f clk per element per warp\n", MODE, MODE == 0 ? "ex2" : MODE == 1 ? "polynomial" : MODE == 2 ? "ex2.bf16x2" : "ex2.f16x2",
          kFillers[FILL], K, threads / 128, (double)host / reps / 32);
 }
 int main() {
@@ -89,6 +103,7 @@ int main() {
     run<0, 0>(in, out, clocks, threads); run<1, 0>(in, out, clocks, threads); run<2, 0>(in, out, clocks, threads); run<3, 0>(in, out, clocks, threads);
     run<4, 0>(in, out, clocks, threads); run<6, 0>(in, out, clocks, threads); run<8, 0>(in, out, clocks, threads);
     run<0, 1>(in, out, clocks, threads); run<3, 1>(in, out, clocks, threads);
+    run<0, 2>(in, out, clocks, threads); run<2, 2>(in, out, clocks, threads); run<0, 3>(in, out, clocks, threads); run<2, 3>(in, out, clocks, threads);
     run<1, 0, 1>(in, out, clocks, threads); run<2, 0, 1>(in, out, clocks, threads); run<4, 0, 1>(in, out, clocks, threads);
     run<1, 0, 2>(in, out, clocks, threads); run<2, 0, 2>(in, out, clocks, threads); run<4, 0, 2>(in, out, clocks, threads);
     run<1, 0, 3>(in, out, clocks, threads); run<2, 0, 3>(in, out, clocks, threads); run<4, 0, 3>(in, out, clocks, threads);
