@@ -896,7 +896,7 @@ int launch_wide(const void* a, const void* b, const Destinations& dst, int m, in
 // The wide tile wins whenever it wastes no more of the machine than the 256-row pair tile does: the fraction of tile
 // area inside the matrix times the fraction of the last wave that is occupied, with a few per cent of credit for the
 // lower traffic.  BB200_GEMM_PAIR=2 forces it, 1 forces the 256-row pair tile (tuning and tests).
-bool use_wide_kernel(int m, int n, int sms) {
+bool use_wide_kernel(int m, int n, int k, int sms) {
   static const int forced = [] {
     const char* text = getenv("BB200_GEMM_PAIR");
     return text ? atoi(text) : -1;
@@ -909,7 +909,11 @@ bool use_wide_kernel(int m, int n, int sms) {
     const long waves = (tiles + pairs - 1) / pairs;
     return ((double)m * n / ((double)m_blocks * tile_rows * n_blocks * BN)) * ((double)tiles / (double)(waves * pairs));
   };
-  return m >= WIDE_BM && efficiency(WIDE_BM) * 1.03 >= efficiency(PAIR_BM);
+  // Both accumulators of a CTA belong to one tile, so the read-out of a tile is not hidden behind the next tile's products
+  // as in the narrower kernels: the wide tile pays off only when the products of a tile are long enough (measured at
+  // 8192 x 8192 x K, one cold launch each: K = 1024 / 2048 / 4096 117 / 183 / 335 us against 102 / 164 / 328 for the 256-row
+  // tile, K = 6144 / 8192 504 / 654 against 510 / 678).
+  return k >= 6144 && m >= WIDE_BM && efficiency(WIDE_BM) * 1.03 >= efficiency(PAIR_BM);
 }
 
 // A_MN: A is stored [k, m] (m contiguous) and consumed as an MN-major operand; otherwise [m, k].
@@ -956,6 +960,31 @@ int split_k_count(int tiles, int k_blocks, int sms) {
   return splits < 2 ? 1 : splits;
 }
 
+// Split-K workspaces come from a pool of this library's own that keeps what is freed (release threshold = everything):
+// the device's default pool hands memory back at every synchronisation, and a caller that synchronises between two GEMMs
+// would then pay a fresh allocation (≈ 130 us) for every call.
+cudaMemPool_t workspace_pool(int device) {
+  static std::mutex guard;
+  static cudaMemPool_t pools[kMaxDevices] = {};
+  std::lock_guard<std::mutex> lock(guard);
+  if (!pools[device]) {
+    cudaMemPoolProps props = {};
+    props.allocType = cudaMemAllocationTypePinned;
+    props.handleTypes = cudaMemHandleTypeNone;
+    props.location.type = cudaMemLocationTypeDevice;
+    props.location.id = device;
+    cudaMemPool_t created = nullptr;
+    if (cudaMemPoolCreate(&created, &props) != cudaSuccess) {
+      cudaGetLastError();
+      return nullptr;
+    }
+    unsigned long long keep_everything = ~0ull;
+    cudaMemPoolSetAttribute(created, cudaMemPoolAttrReleaseThreshold, &keep_everything);
+    pools[device] = created;
+  }
+  return pools[device];
+}
+
 template <typename OutT, bool A_MN, bool B_MN, int TN>
 int launch_single(const void* a_operand, const void* b, const Destinations& dst, int m, int n, int k, int device, int sms, bool may_split,
                   cudaStream_t stream) {
@@ -984,8 +1013,10 @@ int launch_single(const void* a_operand, const void* b, const Destinations& dst,
     const int kb_per_split = (k_blocks + splits - 1) / splits;
     const int used_splits = (k_blocks + kb_per_split - 1) / kb_per_split;  // no empty K ranges
     float* partial = nullptr;
-    if (int status = check_runtime(cudaMallocAsync(reinterpret_cast<void**>(&partial), (size_t)used_splits * m * n * sizeof(float), stream),
-                                   "cudaMallocAsync(gemm split-K workspace)"))
+    cudaMemPool_t pool = workspace_pool(device);
+    if (!pool) return fail(BB200_E_NO_DRIVER, "gemm: could not create the split-K workspace pool");
+    if (int status = check_runtime(cudaMallocFromPoolAsync(reinterpret_cast<void**>(&partial), (size_t)used_splits * m * n * sizeof(float), pool, stream),
+                                   "cudaMallocFromPoolAsync(gemm split-K workspace)"))
       return status;
     const Destinations workspace = single_destination(partial);
     const int work_items = tiles * used_splits;
@@ -1015,7 +1046,7 @@ int launch_native(const void* a_operand, const void* b, const Destinations& dst,
   if (use_pair_kernel(m, n, sms)) {
     if constexpr (!A_MN && !B_MN) {
       // the wide kernel writes one local C in whole 16-byte pieces
-      if (dst.count == 1 && (n % 8) == 0 && aligned16(dst.p[0]) && use_wide_kernel(m, n, sms)) return launch_wide<OutT>(a_operand, b, dst, m, n, k, device, sms, stream);
+      if (dst.count == 1 && (n % 8) == 0 && aligned16(dst.p[0]) && use_wide_kernel(m, n, k, sms)) return launch_wide<OutT>(a_operand, b, dst, m, n, k, device, sms, stream);
     }
     return launch_pair<OutT, A_MN, B_MN>(a_operand, b, dst, m, n, k, device, sms, stream);
   }
