@@ -34,7 +34,11 @@ STORAGE_CTYPE = {
 STORAGE_BYTES = {"f32": 4, "bf16": 2, "f16": 2, "i32": 4, "i64": 8, "index": 8, "i8": 1, "i1": 1}
 FLOATS = ("f32", "bf16", "f16")
 THREADS = 256
-UNROLL = 4
+# 16-byte vectors per thread and stream.  One: with 8 CTAs of 256 threads resident per SM the loads in flight already cover
+# the memory latency, and small CTAs (2048 bf16 elements) leave the shortest tail — measured with back-to-back launches,
+# unroll 1 / 2 / 4 / 8: bf16 a*b+a 2^28 elements 228.5 / 229.1 / 232.9 / 230.4 us, 2^25 31.1 / 31.0 / 31.8 / 31.3, 2^24 16.9 / 16.8 /
+# 17.4 / 17.4; f32 add 2^27 227.6 / 230.6 / 231.3 / 230.2, 2^24 30.4 / 30.9 / 31.2 / 31.6
+UNROLL = 1
 
 JIT_CACHE_ENV = "BAYBRIDGE_B200_KERNEL_CACHE"
 

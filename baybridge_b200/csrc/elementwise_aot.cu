@@ -50,7 +50,7 @@ template <typename T, Fused OP> struct BinaryBody {
 };
 
 constexpr int kThreads = 256;
-constexpr int kUnroll = 4;
+constexpr int kUnroll = 1;  // as the generated kernels: one 16-byte vector per thread and stream measured fastest
 
 template <typename T, Fused OP>
 __global__ void __launch_bounds__(kThreads) binary_kernel(BinaryBody<T, OP> body, size_t n, bool vector_ok) {
