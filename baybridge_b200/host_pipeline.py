@@ -22,6 +22,24 @@ from .driver import trace
 from .sharding import ShardSpec, shard_bounds, shard_spec
 
 
+def _ramped(rows: int, chunks: int) -> list[tuple[int, int]]:
+    """``chunks`` equal parts of ``range(rows)``, the first cut into 1/8, 1/8, 1/4, 1/2 of itself and the last into the
+    mirror image — when the parts are long enough to be cut into pieces that keep 16-byte alignment for every dtype."""
+    bounds = [shard_bounds(rows, chunks, index) for index in range(chunks)]
+    first, last = bounds[0][1] - bounds[0][0], bounds[-1][1] - bounds[-1][0]
+    if chunks < 4 or first % 128 or last % 128 or first < 1024 or last < 1024:
+        return bounds
+    head = [first // 8, first // 8, first // 4, first // 2]
+    tail = [last // 2, last // 4, last // 8, last // 8]
+    pieces = head + [stop - start for start, stop in bounds[1:-1]] + tail
+    out, start = [], 0
+    for size in pieces:
+        out.append((start, start + size))
+        start += size
+    assert start == rows
+    return out
+
+
 class HostPipeline:
     """``pipeline = HostPipeline(kernel_for, host_args, chunks=8); pipeline.run()``.
 
@@ -29,11 +47,13 @@ class HostPipeline:
     entries along the shard axis (kernels whose launch grid depends on the size need this; pass
     ``lambda rows: kernel`` otherwise).  ``host_args`` are the kernel's arguments in order: pinned (or
     pageable) CPU ``torch`` tensors for tensor arguments, Python numbers for scalars.  Outputs are
-    written back into the given host tensors.
+    written back into the given host tensors.  With ``ramp`` (the default) the first and the last of the ``chunks``
+    equal chunks are cut into pieces of 1/8, 1/8, 1/4 and 1/2 of a chunk (mirrored at the end): nothing overlaps the
+    first host→device copy and the last device→host copy, so they should be short.
     """
 
     def __init__(self, kernel_for: Callable[[int], Any], host_args: Sequence[Any], *, chunks: int = 8, device: int | None = None,
-                 cache_dir: str | None = None):
+                 cache_dir: str | None = None, ramp: bool = True):
         import torch
 
         self.torch = torch
@@ -61,7 +81,8 @@ class HostPipeline:
         else:
             self.chunks = max(1, min(int(chunks), full_rows))
             self.sharded = {position for position, _ in self.spec.sharded}
-        self.bounds = [shard_bounds(full_rows, self.chunks, index) for index in range(self.chunks)]
+        self.bounds = _ramped(full_rows, self.chunks) if ramp else [shard_bounds(full_rows, self.chunks, index) for index in range(self.chunks)]
+        self.chunks = len(self.bounds)
         longest = max(stop - start for start, stop in self.bounds)
         backend = B200Backend(device=self.device.index or 0, synchronize=False)
         # device storage: two slots per sharded argument, one full copy per other argument

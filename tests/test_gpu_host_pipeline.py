@@ -27,6 +27,19 @@ def test_pipeline_matches_one_shot_elementwise_and_gemm(zoo, tmp_path):
         assert oracle.rel_l2(c.double().numpy(), reference) <= 2e-3
         assert pipeline.h2d_bytes == 2 * n * 2 and pipeline.d2h_bytes == n * 2
 
+    # chunks long enough to be ramped: the first and the last of the 8 become 1/8, 1/8, 1/4, 1/2 pieces (14 chunks, 4 lengths)
+    n2 = 1 << 21
+    a2r = torch.from_numpy(oracle.bf16_round(rng.standard_normal(n2, dtype=np.float32))).to(torch.bfloat16).pin_memory()
+    b2r = torch.from_numpy(oracle.bf16_round(rng.standard_normal(n2, dtype=np.float32))).to(torch.bfloat16).pin_memory()
+    for ramp in (True, False):
+        c2r = torch.zeros(n2, dtype=torch.bfloat16).pin_memory()
+        pipeline = HostPipeline(lambda rows: zoo.make_fused_mul_add_indexed(rows), [a2r, b2r, c2r], chunks=8, cache_dir=tmp_path, ramp=ramp)
+        assert pipeline.chunks == (14 if ramp else 8) and len(pipeline.artifacts) == (4 if ramp else 1)
+        assert pipeline.bounds[0] == (0, (n2 // 8) // (8 if ramp else 1)) and pipeline.bounds[-1][1] == n2
+        pipeline.run()
+        reference = a2r.double().numpy() * b2r.double().numpy() + a2r.double().numpy()
+        assert np.array_equal(c2r.double().numpy(), oracle.bf16_round(reference.astype(np.float32)).astype(np.float64))
+
     m, nn, k = 1000, 512, 256  # M sharded in ragged chunks, B replicated
     a2 = torch.from_numpy(oracle.bf16_round((rng.standard_normal((m, k)) / 16).astype(np.float32))).to(torch.bfloat16).pin_memory()
     b2 = torch.from_numpy(oracle.bf16_round((rng.standard_normal((nn, k)) / 16).astype(np.float32))).to(torch.bfloat16).pin_memory()
